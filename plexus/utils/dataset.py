@@ -1,0 +1,8 @@
+from plexus_b200.utils.dataset import (  # noqa: F401
+    mtx_to_pyg,
+    partition_graph_2d,
+    preprocess_graph,
+    print_nnz_stats,
+    tsv_to_pyg,
+    write_to_mtx,
+)

@@ -1,0 +1,76 @@
+"""GCN models: the 3D-parallel ``Net`` and a serial single-process oracle.
+
+``Net`` mirrors the example model of the reference (reference:
+examples/train.py:55-79: ``num_gcn_layers`` GCNConv layers with ReLU between
+them) with the layers registered in a ``ModuleList`` so that
+``model.parameters()`` and ``state_dict()`` see the weights.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .gcn_conv import GCNConv, GCNStackFunction, init_full_weight
+
+
+class Net(torch.nn.Module):
+    def __init__(self, num_gcn_layers, input_size, hidden_size, output_size, fuse_layers: bool = True,
+                 seed: Optional[int] = None):
+        super().__init__()
+        self.num_gcn_layers = num_gcn_layers
+        self.fuse_layers = fuse_layers
+        dims = [input_size] + [hidden_size] * (num_gcn_layers - 1) + [output_size]
+        self.dims = dims
+        self.layers = torch.nn.ModuleList(
+            GCNConv(dims[i], dims[i + 1], i, seed=seed) for i in range(num_gcn_layers)
+        )
+
+    def forward(self, x, edge_index_shards):
+        L = self.num_gcn_layers
+        if self.fuse_layers:
+            specs, adjs = [], []
+            for i, layer in enumerate(self.layers):
+                pair = edge_index_shards[i % len(edge_index_shards)]
+                specs.append(layer.spec(pair[0], relu=(i != L - 1)))
+                adjs.append(pair)
+            return GCNStackFunction.apply(specs, adjs, x, *[l.weight for l in self.layers])
+        for i, layer in enumerate(self.layers):
+            x = layer(x, edge_index_shards)
+            if i != L - 1:
+                x = F.relu(x)
+        return x
+
+
+class SerialGCN(torch.nn.Module):
+    """Single-process dense-weight GCN used as the numerical oracle.
+
+    Uses the same weight initialisation as :class:`GCNConv`, so a parallel
+    run with the same seed starts from the same parameters.
+    """
+
+    def __init__(self, num_gcn_layers, input_size, hidden_size, output_size, seed: Optional[int] = None,
+                 dtype=torch.float32):
+        super().__init__()
+        dims = [input_size] + [hidden_size] * (num_gcn_layers - 1) + [output_size]
+        self.weights = torch.nn.ParameterList(
+            torch.nn.Parameter(init_full_weight(dims[i], dims[i + 1], i, seed).to(dtype))
+            for i in range(num_gcn_layers)
+        )
+
+    def forward(self, x, adjs: List[torch.Tensor]):
+        """``adjs[l % len(adjs)]`` is the (square, unsharded) adjacency used at layer ``l``."""
+        L = len(self.weights)
+        for l, w in enumerate(self.weights):
+            A = adjs[l % len(adjs)]
+            x = torch.sparse.mm(A, x) @ w
+            if l != L - 1:
+                x = torch.relu(x)
+        return x
+
+
+def serial_loss(logits, labels, num_nodes):
+    """Sum of cross-entropy over rows with a non-negative label, divided by ``num_nodes``."""
+    return F.cross_entropy(logits, labels, ignore_index=-1, reduction="sum") / num_nodes

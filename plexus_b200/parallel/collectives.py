@@ -1,0 +1,99 @@
+"""Library-path collectives over ``torch.distributed`` (NCCL on GPU, gloo on CPU).
+
+These are the unfused versions of the collectives a 3D-parallel GCN layer
+needs: depth-axis all-gather, in-place SUM all-reduce and reduce-scatter.  A
+``None`` group (an axis of size 1) makes every call a no-op.  Each call is
+wrapped in a timer region named ``gather`` / ``all-reduce`` /
+``reduce-scatter`` so a log parser can sum the communication time
+(reference: examples/parse_results.py:46-54; the wrappers replace AxoNN's
+``_gather``, ``_all_reduce`` and ``_reduce_scatter`` used at
+plexus/gcn_conv.py:177-278).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..utils.timers import get_timers
+from .grid import group_size
+
+_bytes_moved = {"gather": 0, "all-reduce": 0, "reduce-scatter": 0}
+
+
+def bytes_moved(reset: bool = False):
+    """Payload bytes handed to each collective kind since the last reset."""
+    out = dict(_bytes_moved)
+    if reset:
+        for k in _bytes_moved:
+            _bytes_moved[k] = 0
+    return out
+
+
+def all_gather(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.Tensor:
+    """Concatenate every rank's ``t`` along ``dim`` (rank order)."""
+    p = group_size(process_group)
+    if p == 1:
+        return t
+    timers = get_timers()
+    timers.start("gather")
+    t = t.contiguous()
+    _bytes_moved["gather"] += t.numel() * t.element_size() * (p - 1)
+    if dim == 0:
+        out = torch.empty((p * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=process_group)
+    else:
+        parts = torch.empty((p,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(parts, t, group=process_group)
+        out = torch.cat(list(parts.unbind(0)), dim=dim)
+    timers.stop("gather")
+    return out
+
+
+def all_reduce(t: torch.Tensor, process_group=None, op=None) -> torch.Tensor:
+    """In-place SUM (or ``op``) all-reduce; returns ``t``."""
+    if group_size(process_group) == 1:
+        return t
+    timers = get_timers()
+    timers.start("all-reduce")
+    _bytes_moved["all-reduce"] += t.numel() * t.element_size()
+    if not t.is_contiguous():
+        tmp = t.contiguous()
+        dist.all_reduce(tmp, op=op or dist.ReduceOp.SUM, group=process_group)
+        t.copy_(tmp)
+    else:
+        dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=process_group)
+    timers.stop("all-reduce")
+    return t
+
+
+def reduce_scatter(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.Tensor:
+    """SUM-reduce ``t`` over the group and return this rank's 1/p slice along ``dim``."""
+    p = group_size(process_group)
+    if p == 1:
+        return t
+    if dim != 0:
+        raise NotImplementedError("reduce_scatter is only used along dim 0")
+    if t.shape[0] % p != 0:
+        raise ValueError(f"reduce_scatter: leading size {t.shape[0]} not divisible by {p}")
+    timers = get_timers()
+    timers.start("reduce-scatter")
+    t = t.contiguous()
+    _bytes_moved["reduce-scatter"] += t.numel() * t.element_size()
+    out = torch.empty((t.shape[0] // p,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    if t.device.type == "cpu":
+        # gloo has no reduce_scatter_tensor: all-reduce a copy and slice.
+        tmp = t.clone()
+        dist.all_reduce(tmp, group=process_group)
+        r = dist.get_rank(process_group)
+        out.copy_(tmp[r * out.shape[0] : (r + 1) * out.shape[0]])
+    else:
+        dist.reduce_scatter_tensor(out, t, group=process_group)
+    timers.stop("reduce-scatter")
+    return out
+
+
+# Names used by code written against AxoNN's intra-layer communication module.
+_gather = all_gather
+_all_reduce = all_reduce
+_reduce_scatter = reduce_scatter

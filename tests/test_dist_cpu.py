@@ -1,0 +1,94 @@
+"""3D-parallel GCN over gloo ranks on the CPU versus the serial dense oracle."""
+
+import pytest
+import torch
+
+from helpers import oracle, run_distributed, small_processed_graph
+
+
+def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, flags):
+    import plexus_b200 as plx
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net
+    from plexus_b200.utils.checkpoint import _cut_features, _cut_weight
+    from plexus_b200.utils.dataloader import DataLoader
+
+    torch.manual_seed(0)
+    plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
+             block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
+             tune_gemms=flags.get("tune", False))
+    if flags.get("block"):
+        from plexus_b200.models import gcn_conv
+        gcn_conv.MAX_ROWS_PER_CHUNK = 17
+    data, nc = small_processed_graph(n=n, e=4 * n, f=f, c=c, seed=5, double_perm=double_perm)
+    loader = DataLoader(None, num_layers, data=(data, nc), dtype=torch.float64)
+    adj, feats, labels, N, F, C = loader.load()
+    model = Net(num_layers, F, hidden, C, fuse_layers=fuse, seed=11).double()
+    out = model(feats, adj)
+    loss = parallel_cross_entropy(out, labels, num_layers, N, C)
+    loss.backward()
+
+    ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, num_layers, hidden, seed=11)
+    assert torch.allclose(loss.detach(), ref_loss, rtol=1e-9, atol=1e-11), (loss.item(), ref_loss.item())
+    for l, layer in enumerate(model.layers):
+        want = _cut_weight(layer, ref_gw[l])
+        got = layer.weight.grad
+        assert got.shape == want.shape
+        assert torch.allclose(got, want, rtol=1e-8, atol=1e-11), f"layer {l} weight grad"
+    want_x = _cut_features(ref_gx, feats)
+    assert torch.allclose(feats.grad, want_x, rtol=1e-8, atol=1e-11), "feature grad"
+
+
+GRIDS = [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2), (2, 1, 2), (4, 1, 1), (1, 1, 4)]
+
+
+@pytest.mark.parametrize("grid", GRIDS)
+def test_grids_three_layers(grid):
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, True, {})
+
+
+@pytest.mark.parametrize("grid", [(2, 2, 2), (4, 2, 1)])
+def test_eight_ranks(grid):
+    run_distributed(_worker, 8, grid, 3, True, 53, 9, 7, 8, True, {})
+
+
+@pytest.mark.parametrize("num_layers", [1, 2, 4])
+def test_layer_counts_cover_rotation(num_layers):
+    run_distributed(_worker, 4, (2, 1, 2), num_layers, True, 50, 6, 4, 8, True, {})
+
+
+def test_single_permutation_and_unfused_layers():
+    run_distributed(_worker, 4, (1, 2, 2), 3, False, 47, 7, 3, 8, False, {})
+
+
+def test_channel_alignment_padding():
+    run_distributed(_worker, 2, (1, 2, 1), 2, True, 40, 10, 5, 12, True, {"align": 8})
+
+
+def test_blocked_and_overlapped_aggregation():
+    run_distributed(_worker, 2, (2, 1, 1), 2, True, 64, 8, 4, 8, True, {"block": True})
+    run_distributed(_worker, 2, (2, 1, 1), 2, True, 64, 8, 4, 8, True, {"block": True, "overlap": True})
+
+
+def test_tuned_gemms():
+    run_distributed(_worker, 2, (1, 1, 2), 2, True, 40, 8, 4, 8, True, {"tune": True})
+
+
+def test_single_process_matches_oracle():
+    import plexus_b200 as plx
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net
+    from plexus_b200.utils.dataloader import DataLoader
+
+    plx.init(1, 1, 1, device="cpu", dtype=torch.float64, channel_align=1)
+    data, nc = small_processed_graph(n=70, e=300, f=9, c=4, seed=2)
+    adj, feats, labels, N, F, C = DataLoader(None, 3, data=(data, nc), dtype=torch.float64).load()
+    model = Net(3, F, 16, C, seed=4).double()
+    loss = parallel_cross_entropy(model(feats, adj), labels, 3, N, C)
+    loss.backward()
+    ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, 3, 16, seed=4)
+    assert torch.allclose(loss.detach(), ref_loss, rtol=1e-10)
+    assert torch.allclose(feats.grad.view(N, F), ref_gx, rtol=1e-8, atol=1e-12)
+    for l, layer in enumerate(model.layers):
+        assert torch.allclose(layer.weight.grad.view_as(ref_gw[l]), ref_gw[l], rtol=1e-8, atol=1e-12)

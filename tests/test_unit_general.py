@@ -1,0 +1,111 @@
+import pytest
+import torch
+
+from plexus_b200.parallel import grid as G
+from plexus_b200.parallel.sharding import (
+    block_range, depth_slice, extract_local_params_from_full_params, pad_dimension, padded_channels, shard_2d,
+)
+
+
+def test_pad_dimension():
+    assert pad_dimension(10, 4) == 12
+    assert pad_dimension(12, 4) == 12
+    assert pad_dimension(10, 2, 3) == 12
+    assert pad_dimension(13, 2, 3) == 18
+    assert pad_dimension(0, 4) == 0
+    assert pad_dimension(7, 1) == 7
+
+
+def test_padded_channels():
+    assert padded_channels(100, 2, 2, 8) == 112  # multiple of 2*lcm(2,8)=16
+    assert padded_channels(100, 2, 1, 1) == 100
+    assert padded_channels(47, 8, 1, 8) == 64
+    assert padded_channels(47, 2, 4, 1) == 48
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (2, 1, 1), (1, 2, 1), (2, 2, 2), (4, 2, 1), (2, 4, 8)])
+def test_rank_coords_roundtrip(shape):
+    X, Y, Z = shape
+    seen = set()
+    for r in range(X * Y * Z):
+        x, y, z = G.coords_of(r, X, Y, Z)
+        assert 0 <= x < X and 0 <= y < Y and 0 <= z < Z
+        assert G.rank_of(x, y, z, X, Y, Z) == r
+        assert r == z * X * Y + x * Y + y  # Y fastest, then X, then Z
+        seen.add((x, y, z))
+    assert len(seen) == X * Y * Z
+
+
+def test_line_ranks():
+    X, Y, Z = 2, 2, 2
+    assert G.line_ranks("y", 0, 0, 0, X, Y, Z) == [0, 1]
+    assert G.line_ranks("x", 0, 0, 0, X, Y, Z) == [0, 2]
+    assert G.line_ranks("z", 0, 0, 0, X, Y, Z) == [0, 4]
+    assert G.line_ranks("x", 1, 1, 1, X, Y, Z) == [5, 7]
+    with pytest.raises(ValueError):
+        G.line_ranks("w", 0, 0, 0, X, Y, Z)
+
+
+def test_axis_role_rotation():
+    assert G.axis_roles(0) == ("x", "y", "z")
+    assert G.axis_roles(1) == ("z", "x", "y")
+    assert G.axis_roles(2) == ("y", "z", "x")
+    assert G.axis_roles(3) == ("x", "y", "z")
+    # output layout of layer l (rows by depth, cols by outer) == input layout of l+1 (rows by outer, cols by inner)
+    for l in range(6):
+        o, i, d = G.axis_roles(l)
+        o2, i2, d2 = G.axis_roles(l + 1)
+        assert o2 == d and i2 == o and d2 == i
+
+
+def test_loss_axes():
+    assert G.loss_axes(1) == ("z", "x")
+    assert G.loss_axes(2) == ("y", "z")
+    assert G.loss_axes(3) == ("x", "y")
+    assert G.loss_axes(4) == ("z", "x")
+
+
+def test_grid_info_single_process():
+    g = G.ProcessGrid.build(1, 1, 1)
+    sizes, ranks, groups = g.info(("z", "x", "y"))
+    assert sizes == [1, 1, 1] and ranks == [0, 0, 0] and groups == [None, None, None]
+    with pytest.raises(AssertionError):
+        g.info(("x", "x"))
+    with pytest.raises(ValueError):
+        g.info(("q",))
+    with pytest.raises(ValueError):
+        G.ProcessGrid.build(2, 1, 1, rank=0, world_size=1)
+
+
+def test_comm_handle_names():
+    g = G.ProcessGrid(X=2, Y=3, Z=4, rank=2 * 6 + 1 * 3 + 2, world_size=24)
+    h = G.CommHandle(g)
+    assert (h.G_intra_r, h.G_intra_c, h.G_intra_d) == (2, 3, 4)
+    assert h.intra_layer_row_parallel_rank == 1
+    assert h.intra_layer_column_parallel_rank == 2
+    assert h.intra_layer_depth_parallel_rank == 2
+
+
+def test_shard_2d_matches_dense_slicing():
+    full = torch.arange(7 * 5, dtype=torch.float32).view(7, 5)
+    padded = torch.zeros(8, 6)
+    padded[:7, :5] = full
+    for ri in range(4):
+        for ci in range(3):
+            blk = shard_2d(full, 4, ri, 3, ci)
+            assert torch.equal(blk, padded[ri * 2:(ri + 1) * 2, ci * 2:(ci + 1) * 2])
+
+
+def test_block_range_and_depth_slice():
+    assert block_range(10, 4, 0) == (0, 3)
+    assert block_range(10, 4, 3) == (9, 12)
+    t = torch.arange(12)
+    assert torch.equal(depth_slice(t, 3, 1), torch.arange(4, 8))
+    with pytest.raises(ValueError):
+        depth_slice(torch.arange(10), 3, 0)
+
+
+def test_extract_local_params_single_rank():
+    w = torch.randn(6, 4)
+    flat = extract_local_params_from_full_params(w, None, None, None)
+    assert torch.equal(flat, w.reshape(-1))
