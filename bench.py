@@ -1,0 +1,362 @@
+"""Headline benchmark: full-graph GCN epoch time on N B200 GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...            # unmodified reference (baseline/_ref)
+
+Workload (fixed as N grows = strong scaling): 3-layer GCN, hidden 256, on a seeded synthetic
+power-law R-MAT graph with 2,449,029 nodes and ~124M nonzeros after symmetrisation and
+self-loops (mean degree ~50), symmetric-normalised, 100-dim N(0,1) features, 47 uniform
+classes; double permutation; AdamW lr 3e-3 over weights and input features.  A "step" is one
+epoch: zero_grad, forward, parallel cross-entropy, backward, optimizer step.
+
+Timing: W untimed warm-up epochs, then exactly K epochs between CUDA events, with a barrier
+and a device synchronize on both sides, max over ranks.  The inputs (>= 1 GB of adjacency and
+features per GPU) are far larger than L2, so no explicit L2 flush is needed between steps.
+The end-to-end figure repeats the K epochs through the public API with, per epoch, a
+host-to-device copy of the labels from pinned memory and a device-to-host read of the loss.
+Rank 0 prints one JSON line.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+CONFIG = dict(nodes=2_449_029, undirected_edges=60_634_000, features=100, hidden=256, classes=47,
+              layers=3)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    p.add_argument("--comm", type=str, default="auto", choices=["auto", "nccl", "fused"])
+    p.add_argument("--grid", type=str, default=None, help="XxYxZ (default: chosen by the cost models)")
+    p.add_argument("--seed", type=int, default=0)
+    # shrink the workload for smoke tests only (the headline uses the defaults)
+    p.add_argument("--nodes", type=int, default=CONFIG["nodes"])
+    p.add_argument("--edges", type=int, default=CONFIG["undirected_edges"])
+    p.add_argument("--features", type=int, default=CONFIG["features"])
+    p.add_argument("--hidden", type=int, default=CONFIG["hidden"])
+    p.add_argument("--classes", type=int, default=CONFIG["classes"])
+    p.add_argument("--layers", type=int, default=CONFIG["layers"])
+    p.add_argument("--no_e2e", action="store_true")
+    p.add_argument("--timers", action="store_true", help="print the per-region timer tree once")
+    return p.parse_args()
+
+
+# ----------------------------------------------------------------------------- plumbing
+def setup_distributed(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N>1")
+    return rank, world, local
+
+
+def pick_grid(args, world):
+    if args.grid:
+        return tuple(int(v) for v in args.grid.lower().split("x"))
+    from plexus_b200.perf.chooser import choose_grid
+
+    dims = [args.features] + [args.hidden] * (args.layers - 1) + [args.classes]
+    return choose_grid(world, args.nodes, 2 * args.edges + args.nodes, dims)[0]
+
+
+def max_over_ranks(v: float) -> float:
+    if not dist.is_initialized():
+        return v
+    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def barrier_sync():
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def make_graph(args, device):
+    """Seeded synthetic graph, normalised and double-permuted, in the processed-file layout."""
+    from plexus_b200.data.synthetic import synthetic_graph
+    from plexus_b200.utils.dataset import preprocess_data
+
+    raw, nc = synthetic_graph(args.nodes, args.edges, args.features, args.classes, seed=args.seed,
+                              kind="rmat", device=device)
+    data, _ = preprocess_data(raw, nc, double_perm=True, normalized=True, seed=args.seed)
+    del raw
+    torch.cuda.empty_cache()
+    return data
+
+
+def base_record(args, world, grid, nnz):
+    return {
+        "metric": "gcn_epoch_time",
+        "unit": "s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "higher_is_better": False,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "data": "synthetic (seeded R-MAT graph, N(0,1) features, uniform labels, random-init weights)",
+        "config": {
+            "model": f"{args.layers}-layer GCN, hidden {args.hidden}",
+            "nodes": args.nodes, "nonzeros": nnz, "features": args.features, "classes": args.classes,
+            "global_batch": "full graph", "seq_len": None,
+            "parallelism": f"3D tensor parallel X{grid[0]}Y{grid[1]}Z{grid[2]}",
+            "l2": "inputs (adjacency + features >= 1 GB per GPU) exceed the 126 MB L2; no flush",
+            "optimizer": "AdamW lr 3e-3 over weights and input features",
+        },
+    }
+
+
+# ----------------------------------------------------------------------------- this framework
+def run_ours(args):
+    rank, world, local = setup_distributed(args)
+    sys.path.insert(0, ROOT)
+    import plexus_b200 as plx
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.optim import FusedAdamW
+    from plexus_b200.utils.dataloader import DataLoader
+    from plexus_b200.utils.general import print_axonn_timer_data, set_seed
+    from plexus_b200.utils.timers import get_timers
+
+    set_seed(args.seed)
+    grid = pick_grid(args, world)
+    comm = args.comm
+    if comm == "auto":
+        comm = "fused" if world > 1 and os.environ.get("PLEXUS_COMM", "fused") == "fused" else "nccl"
+    plx.init(*grid, gpus_per_node=torch.cuda.device_count(), enable_internal_timers=args.timers, comm=comm)
+    device = torch.device("cuda", local)
+
+    data = make_graph(args, device)
+    nnz = int(data.edge_index.shape[1])
+    adj, features, labels, N, F, C = DataLoader(None, args.layers, data=(data, args.classes)).load()
+    del data
+    torch.cuda.empty_cache()
+    model = Net(args.layers, F, args.hidden, C, seed=args.seed)
+    opt = FusedAdamW(list(model.parameters()) + [features], lr=3e-3, weight_decay=0.0)
+
+    def step(lbl):
+        opt.zero_grad(set_to_none=True)
+        out = model(features, adj)
+        loss = parallel_cross_entropy(out, lbl, args.layers, N, C)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(args.warmup):
+        loss = step(labels)
+    opc.check_status()
+    if args.timers:
+        get_timers().get_times()
+
+    # ---- device-timed region
+    sampler = ClockSampler(local)
+    barrier_sync()
+    sampler.start()
+    launches0 = opc.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        loss = step(labels)
+    ev1.record()
+    barrier_sync()
+    clocks = sampler.stop()
+    launches = opc.launch_count - launches0
+    ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    opc.check_status()
+    if args.timers:
+        print_axonn_timer_data(get_timers().get_times()[0])
+
+    rec = base_record(args, world, grid, nnz)
+    rec.update({"impl": "plexus_b200", "value": ms / 1e3, "ms_per_step": ms, "dtype": "bf16",
+                "clocks": clocks, "gpu_launches": launches, "comm": comm, "final_loss": float(loss)})
+
+    # ---- end to end through the public API: H2D labels from pinned memory + D2H loss per epoch
+    if not args.no_e2e:
+        host_labels = labels.cpu().pin_memory()
+        dev_labels = torch.empty_like(labels)
+        barrier_sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            dev_labels.copy_(host_labels, non_blocking=True)
+            loss_host = step(dev_labels).item()
+        barrier_sync()
+        e2e = max_over_ranks((time.perf_counter() - t0) / args.steps)
+        rec["e2e"] = {"value": e2e, "unit": "s", "h2d_bytes_per_step": host_labels.numel() * 8,
+                      "d2h_bytes_per_step": 4, "last_loss": loss_host}
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "plexus")):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "baseline/_ref is missing (reference not installed)"}))
+        return
+    rank, world, local = setup_distributed(args)
+    sys.path.insert(0, ROOT)
+    # shard construction uses this repository's data pipeline (the reference's own loader needs
+    # torch_geometric / ogb datasets); everything inside the timed step is reference code
+    from plexus_b200.parallel import grid as pgrid
+    from plexus_b200 import runtime as prt
+    from plexus_b200.utils.dataloader import DataLoader as ShardBuilder
+
+    grid = pick_grid(args, world)
+    device = torch.device("cuda", local)
+    pgrid.set_grid(pgrid.ProcessGrid.build(*grid, create_groups=False))
+    prt.flags.dtype, prt.flags.channel_align = torch.float32, 1
+    data = make_graph(args, device)
+    nnz = int(data.edge_index.shape[1])
+    adj32, features, labels, N, F, C = ShardBuilder(None, args.layers, data=(data, args.classes),
+                                                    dtype=torch.float32).load()
+    del data
+    # the reference builds CSR shards with torch's default int64 indices
+    adj = []
+    for A, At in adj32:
+        adj.append(tuple(
+            torch.sparse_csr_tensor(M.crow_indices().long(), M.col_indices().long(), M.values(), size=M.shape)
+            for M in (A, At)))
+    del adj32
+    torch.cuda.empty_cache()
+
+    # from here on: the installed reference and the stand-ins for its two missing imports
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "standins"))
+    sys.path.insert(0, ref_dir)
+    for m in [m for m in sys.modules if m == "plexus" or m.startswith("plexus.")]:
+        del sys.modules[m]
+    from plexus import plexus as plx  # reference
+    from plexus_examples.train import Net, train  # reference examples/train.py
+    from plexus.utils.general import set_seed
+
+    set_seed(args.seed)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=0, world_size=1)
+    plx.init(G_intra_r=grid[0], G_intra_c=grid[1], G_intra_d=grid[2],
+             gpus_per_node=torch.cuda.device_count(), enable_internal_timers=False)
+    model = Net(args.layers, F, args.hidden, C).to(device)
+    optimizer = torch.optim.AdamW(list(model.parameters()) + [features], lr=3e-3, weight_decay=0.0)
+
+    def step(lbl):
+        # stock call of the reference's train(); like its example, the same label tensor is
+        # passed every epoch (its loss relabels it in place, which does not change the work done)
+        return train(model, optimizer, features, adj, lbl, N, C)
+
+    for _ in range(args.warmup):
+        loss = step(labels)
+    sampler = ClockSampler(local)
+    barrier_sync()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        loss = step(labels)
+    ev1.record()
+    barrier_sync()
+    clocks = sampler.stop()
+    ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    rec = base_record(args, world, grid, nnz)
+    rec.update({"impl": "reference", "value": ms / 1e3, "ms_per_step": ms, "dtype": "fp32",
+                "clocks": clocks, "gpu_launches": 0, "final_loss": float(loss),
+                "note": "reference example keeps its layers in a plain list, so its optimizer "
+                        "updates only the input features"})
+    if not args.no_e2e:
+        host_labels = labels.cpu().pin_memory()
+        dev_labels = torch.empty_like(labels)
+        barrier_sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            dev_labels.copy_(host_labels, non_blocking=True)
+            loss_host = step(dev_labels).item()
+        barrier_sync()
+        e2e = max_over_ranks((time.perf_counter() - t0) / args.steps)
+        rec["e2e"] = {"value": e2e, "unit": "s", "h2d_bytes_per_step": host_labels.numel() * 8,
+                      "d2h_bytes_per_step": 4, "last_loss": loss_host}
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

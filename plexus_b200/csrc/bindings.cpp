@@ -1,0 +1,239 @@
+// Python bindings of the sm_100a kernels (module plexus_b200._C): tensor checks, then the plain
+// launchers declared in include/plexus_kernels.h on the current CUDA stream.
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cmath>
+
+#include "include/plexus_kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+int dtype_of(const Tensor& t) {
+  if (t.scalar_type() == at::kBFloat16) return plx::DT_BF16;
+  TORCH_CHECK(t.scalar_type() == at::kFloat, "expected a bf16 or fp32 tensor");
+  return plx::DT_F32;
+}
+
+void check(const char* err) { TORCH_CHECK(err == nullptr, err ? err : ""); }
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream(); }
+
+int* status_ptr(const Tensor& status) {
+  if (!status.defined() || status.numel() == 0) return nullptr;
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 8);
+  return status.data_ptr<int>();
+}
+
+void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
+              const c10::optional<Tensor>& mask, int64_t row_begin, int64_t row_end,
+              const Tensor& long_rows) {
+  TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
+  TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
+              "spmm: int32 CSR indices required");
+  TORCH_CHECK(val.scalar_type() == at::kFloat, "spmm: fp32 CSR values required");
+  TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && val.is_contiguous());
+  TORCH_CHECK(H.dim() == 2 && out.dim() == 2 && H.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(out.scalar_type() == H.scalar_type(), "spmm: out dtype must match H");
+  TORCH_CHECK(0 <= row_begin && row_begin <= row_end && row_end < rowptr.numel());
+  const int64_t D = H.size(1);
+  TORCH_CHECK(out.size(1) == D && out.size(0) == row_end - row_begin, "spmm: bad output shape");
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == H.scalar_type() && mask->size(1) == D &&
+                mask->size(0) == out.size(0) && mask->stride(1) == 1, "spmm: bad mask");
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  const int n_long = static_cast<int>(long_rows.numel());
+  if (n_long) TORCH_CHECK(long_rows.is_cuda() && long_rows.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(H.device());
+  check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
+                             val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
+                             out.stride(0), mptr, ldm, static_cast<int>(D), static_cast<int>(row_begin),
+                             static_cast<int>(row_end), n_long ? long_rows.data_ptr<int>() : nullptr,
+                             n_long, stream()));
+}
+
+void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
+             int64_t max_stages, int64_t ctas_limit) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+              "gemm_nt: bf16 operands required");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
+  TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
+  c10::cuda::CUDAGuard guard(A.device());
+  check(plx::launch_gemm_nt(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(),
+                            C.stride(0), dtype_of(C), A.size(0), B.size(0), A.size(1), relu,
+                            status_ptr(status), static_cast<int>(max_stages),
+                            static_cast<int>(ctas_limit), stream()));
+}
+
+int64_t gemm_tn_parts(int64_t R) { return plx::gemm_tn_parts(R); }
+
+void gemm_tn(const Tensor& A, const Tensor& B, Tensor& out, Tensor& scratch, const Tensor& status) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && out.is_cuda() && scratch.is_cuda());
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+              "gemm_tn: bf16 operands required");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && scratch.scalar_type() == at::kFloat);
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(0) == B.size(0) && A.stride(1) == 1 &&
+              B.stride(1) == 1 && out.is_contiguous() && scratch.is_contiguous());
+  TORCH_CHECK(out.size(0) == A.size(1) && out.size(1) == B.size(1), "gemm_tn: bad output shape");
+  c10::cuda::CUDAGuard guard(A.device());
+  check(plx::launch_gemm_tn(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), out.data_ptr<float>(),
+                            scratch.data_ptr<float>(), scratch.numel(), A.size(0), A.size(1), B.size(1),
+                            status_ptr(status), stream()));
+}
+
+void xent_stats(const Tensor& logits, int64_t class_offset, int64_t num_classes, Tensor& rmax,
+                Tensor& rsum) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(rmax.scalar_type() == at::kFloat && rsum.scalar_type() == at::kFloat &&
+              rmax.numel() == logits.size(0) && rsum.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(plx::launch_xent_stats(dtype_of(logits), logits.data_ptr(), logits.stride(0),
+                               static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                               static_cast<int>(class_offset), static_cast<int>(num_classes),
+                               rmax.data_ptr<float>(), rsum.data_ptr<float>(), stream()));
+}
+
+void xent_loss(const Tensor& logits, const Tensor& target, const Tensor& gmax, const Tensor& gsum,
+               const c10::optional<Tensor>& weight, int64_t row_offset, int64_t class_offset,
+               int64_t num_nodes, Tensor& loss) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(target.scalar_type() == at::kLong && target.numel() == logits.size(0) &&
+              target.is_contiguous());
+  TORCH_CHECK(loss.scalar_type() == at::kFloat && gmax.scalar_type() == at::kFloat &&
+              gsum.scalar_type() == at::kFloat);
+  const float* w = nullptr;
+  if (weight.has_value() && weight->defined()) {
+    TORCH_CHECK(weight->scalar_type() == at::kFloat && weight->numel() == logits.size(0));
+    w = weight->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(plx::launch_xent_loss(dtype_of(logits), logits.data_ptr(), logits.stride(0),
+                              target.data_ptr<int64_t>(), gmax.data_ptr<float>(), gsum.data_ptr<float>(),
+                              w, static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                              row_offset, static_cast<int>(class_offset), num_nodes,
+                              loss.data_ptr<float>(), stream()));
+}
+
+void xent_grad(const Tensor& logits, const Tensor& target, const Tensor& gmax, const Tensor& gsum,
+               const Tensor& scale, int64_t row_offset, int64_t class_offset, int64_t num_nodes,
+               int64_t num_classes, Tensor& grad) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1);
+  TORCH_CHECK(grad.scalar_type() == logits.scalar_type() && grad.stride(1) == 1 &&
+              grad.sizes() == logits.sizes());
+  TORCH_CHECK(target.scalar_type() == at::kLong && target.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(plx::launch_xent_grad(dtype_of(logits), logits.data_ptr(), logits.stride(0),
+                              target.data_ptr<int64_t>(), gmax.data_ptr<float>(), gsum.data_ptr<float>(),
+                              scale.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                              static_cast<int>(logits.size(1)), row_offset,
+                              static_cast<int>(class_offset), num_nodes, static_cast<int>(num_classes),
+                              grad.data_ptr(), grad.stride(0), stream()));
+}
+
+void adam_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avgs,
+                std::vector<Tensor> exp_avg_sqs, std::vector<c10::optional<Tensor>> masters,
+                int64_t step, double lr, double beta1, double beta2, double eps, double weight_decay,
+                bool decoupled) {
+  const size_t n = params.size();
+  TORCH_CHECK(grads.size() == n && exp_avgs.size() == n && exp_avg_sqs.size() == n && masters.size() == n);
+  if (n == 0) return;
+  plx::AdamHyper h;
+  h.lr = static_cast<float>(lr);
+  h.beta1 = static_cast<float>(beta1);
+  h.beta2 = static_cast<float>(beta2);
+  h.eps = static_cast<float>(eps);
+  h.weight_decay = static_cast<float>(weight_decay);
+  h.bc1 = static_cast<float>(1.0 - std::pow(beta1, static_cast<double>(step)));
+  h.bc2 = static_cast<float>(1.0 - std::pow(beta2, static_cast<double>(step)));
+  h.decoupled = decoupled ? 1 : 0;
+  c10::cuda::CUDAGuard guard(params[0].device());
+  for (size_t first = 0; first < n; first += plx::ADAM_MAX_TENSORS) {
+    plx::AdamTensors t;
+    t.count = static_cast<int>(std::min<size_t>(plx::ADAM_MAX_TENSORS, n - first));
+    t.chunk_start[0] = 0;
+    for (int i = 0; i < t.count; ++i) {
+      const Tensor& p = params[first + i];
+      const Tensor& g = grads[first + i];
+      const Tensor& m = exp_avgs[first + i];
+      const Tensor& v = exp_avg_sqs[first + i];
+      TORCH_CHECK(p.is_cuda() && p.is_contiguous() && g.is_contiguous() && g.numel() == p.numel());
+      TORCH_CHECK(p.scalar_type() == g.scalar_type(), "adam: grad dtype must match param dtype");
+      TORCH_CHECK(p.scalar_type() == at::kFloat || p.scalar_type() == at::kBFloat16);
+      TORCH_CHECK(m.scalar_type() == at::kFloat && m.is_contiguous() && m.numel() == p.numel());
+      TORCH_CHECK(v.scalar_type() == at::kFloat && v.is_contiguous() && v.numel() == p.numel());
+      t.param[i] = p.data_ptr();
+      t.grad[i] = g.data_ptr();
+      t.exp_avg[i] = m.data_ptr<float>();
+      t.exp_avg_sq[i] = v.data_ptr<float>();
+      const auto& ms = masters[first + i];
+      t.master[i] = nullptr;
+      if (ms.has_value() && ms->defined()) {
+        TORCH_CHECK(ms->scalar_type() == at::kFloat && ms->is_contiguous() && ms->numel() == p.numel());
+        t.master[i] = ms->data_ptr<float>();
+      }
+      t.numel[i] = p.numel();
+      t.is_bf16[i] = p.scalar_type() == at::kBFloat16 ? 1 : 0;
+      t.chunk_start[i + 1] =
+          t.chunk_start[i] + static_cast<int>((p.numel() + plx::ADAM_CHUNK - 1) / plx::ADAM_CHUNK);
+    }
+    check(plx::launch_adam_multi(t, h, stream()));
+  }
+}
+
+void relu_bwd(const Tensor& grad, const Tensor& out, Tensor& res) {
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && out.is_contiguous() && res.is_contiguous());
+  TORCH_CHECK(grad.scalar_type() == out.scalar_type() && res.scalar_type() == grad.scalar_type() &&
+              grad.numel() == out.numel() && res.numel() == grad.numel());
+  c10::cuda::CUDAGuard guard(grad.device());
+  check(plx::launch_relu_bwd(dtype_of(grad), grad.data_ptr(), out.data_ptr(), res.data_ptr(),
+                             grad.numel(), stream()));
+}
+
+void prep_weight(const Tensor& W, const c10::optional<Tensor>& Wb, Tensor& WbT) {
+  TORCH_CHECK(W.is_cuda() && W.dim() == 2 && W.is_contiguous() && WbT.is_contiguous());
+  const int64_t K = W.size(0), N = W.size(1);
+  TORCH_CHECK(WbT.numel() == K * N && WbT.scalar_type() == at::kBFloat16);
+  void* wb = nullptr;
+  if (Wb.has_value() && Wb->defined()) {
+    TORCH_CHECK(Wb->is_contiguous() && Wb->scalar_type() == at::kBFloat16 && Wb->numel() == W.numel());
+    wb = Wb->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(W.device());
+  check(plx::launch_prep_weight(dtype_of(W), W.data_ptr(), wb, WbT.data_ptr(), static_cast<int>(K),
+                                static_cast<int>(N), stream()));
+}
+
+void wait_flag(const Tensor& flag, int64_t expected, int64_t max_polls, Tensor& status) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(flag.device());
+  check(plx::launch_wait_flag(flag.data_ptr<int>(), static_cast<int>(expected),
+                              static_cast<unsigned>(max_polls), status_ptr(status), stream()));
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("spmm_csr", &spmm_csr, "CSR SpMM, bf16/fp32 features, fp32 accumulate");
+  m.def("spmm_long_row_threshold", &plx::spmm_long_row_threshold);
+  m.def("gemm_nt", &gemm_nt, "C = A . B^T on tcgen05 (bf16 in, fp32 accumulate)");
+  m.def("gemm_tn_parts", &gemm_tn_parts, "number of row splits gemm_tn uses");
+  m.def("gemm_tn", &gemm_tn, "C = A^T . B on tcgen05 with split reduction");
+  m.def("xent_stats", &xent_stats);
+  m.def("xent_loss", &xent_loss);
+  m.def("xent_grad", &xent_grad);
+  m.def("adam_multi", &adam_multi);
+  m.def("relu_bwd", &relu_bwd);
+  m.def("prep_weight", &prep_weight);
+  m.def("wait_flag", &wait_flag);
+}

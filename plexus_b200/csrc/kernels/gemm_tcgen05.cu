@@ -1,0 +1,559 @@
+// Tall-skinny bf16 GEMMs of a GCN layer on the 5th-generation tensor cores.
+//
+//   gemm_nt :  C[M,N]  = A[M,K] . B[N,K]^T      (OUT = AGG.W with B = W^T; gradAGG = gradOUT.W^T
+//                                                with B = W).  Both operands K-major.
+//   gemm_tn :  C[Mw,Nw] = A[R,Mw]^T . B[R,Nw]   (gradW = AGG^T.gradOUT).  Both operands MN-major,
+//                                                split over R across CTAs, fp32 partials.
+//
+// M (or R) is millions of rows while K and N are at most a few hundred, so the kernels are
+// bandwidth bound: the design keeps the small operand resident in shared memory, streams the
+// tall operand once through a TMA ring, accumulates in TMEM and overlaps the epilogue of one
+// row tile with the MMAs of the next (two TMEM accumulators).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (each owns one 32-lane TMEM quadrant).
+// No TMA load uses cluster multicast.  Every mbarrier wait is bounded.
+//
+// Reference call sites replaced: plexus/gcn_conv.py:211 (OUT), :237 (gradW), :256 (gradAGG),
+// which go to cuBLAS SGEMM through torch.mm.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "../include/plexus_kernels.h"
+#include "../include/ptx_sm100.cuh"
+
+namespace plx {
+
+constexpr int GEMM_THREADS = 192;
+constexpr int BM = 128;
+constexpr int BK = 64;                    // one 128-byte swizzle atom of bf16
+constexpr int A_STAGE_BYTES = BM * 128;   // 16 KB
+constexpr int SMEM_LIMIT = 232448;        // 227 KB opt-in maximum per CTA
+constexpr int TMEM_COLS = 512;
+constexpr int KERNEL_ID_GEMM = 6;
+
+struct alignas(8) GemmBarriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t bfull;
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const uint32_t* r, bool relu);
+
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t* r,
+                                                      bool relu) {
+  uint32_t packed[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
+    if (relu) {
+      a = fmaxf(a, 0.f);
+      b = fmaxf(b, 0.f);
+    }
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    packed[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const uint32_t* r, bool relu) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] = __uint_as_float(r[i]);
+    if (relu) v[i] = fmaxf(v[i], 0.f);
+  }
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// ---------------------------------------------------------------------------------------
+// C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = 256-column block)
+// ---------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
+               int b_resident, int relu, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = (K + BK - 1) / BK;
+  const int n0 = blockIdx.y * 256;
+  const int n_valid = min(256, N - n0);
+  const int bn = (n_valid + 15) & ~15;  // UMMA N
+  const int b_blk_bytes = bn_box * 128;
+  const int num_tiles = (M + BM - 1) / BM;
+
+  uint8_t* b_res = smem;                                        // KB blocks when resident
+  uint8_t* ring = smem + (b_resident ? KB * b_blk_bytes : 0);   // stages
+  const int stage_bytes = A_STAGE_BYTES + (b_resident ? 0 : b_blk_bytes);
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(ring + stages * stage_bytes);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->bfull, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->tfull[b], 1);
+      mbar_init(&bars->tempty[b], 4);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if (b_resident) {
+        mbar_expect_tx(&bars->bfull, KB * b_blk_bytes);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(b_res + kb * b_blk_bytes, &tmB, &bars->bfull, kb * BK, n0);
+      }
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (*abort_flag || !mbar_wait(&bars->empty[s], ph ^ 1)) {
+            report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 0, s, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* st = ring + s * stage_bytes;
+          mbar_expect_tx(&bars->full[s], stage_bytes);
+          tma_load_2d(st, &tmA, &bars->full[s], kb * BK, tile * BM);
+          if (!b_resident) tma_load_2d(st + A_STAGE_BYTES, &tmB, &bars->full[s], kb * BK, n0);
+        }
+      }
+      if (!ok) {
+        // giving up: let the copies already issued land before the CTA exits
+        for (uint32_t j = it > (uint32_t)stages ? it - stages : 0; j < it; ++j)
+          mbar_wait(&bars->full[j % stages], (j / stages) & 1);
+        if (b_resident) mbar_wait(&bars->bfull, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, bn, false, false);
+      bool ok = true;
+      if (b_resident && !mbar_wait(&bars->bfull, 0)) {
+        report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 1, 0, 0);
+        *abort_flag = 1;
+        ok = false;
+      }
+      uint32_t it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        if (*abort_flag || !mbar_wait(&bars->tempty[buf], ((t >> 1) & 1) ^ 1)) {
+          report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 2, buf, t);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (*abort_flag || !mbar_wait(&bars->full[s], ph)) {
+            report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 3, s, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
+          const uint32_t b_addr = b_resident ? smem_u32(b_res + kb * b_blk_bytes)
+                                             : a_addr + A_STAGE_BYTES;
+          const int ksteps = min(4, (K - kb * BK + 15) / 16);
+          for (int k = 0; k < ksteps; ++k) {
+            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          umma_commit(&bars->empty[s]);  // stage reusable once these MMAs retire
+        }
+        if (ok) umma_commit(&bars->tfull[buf]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant owned by this warp
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      bool ok = !*abort_flag && mbar_wait(&bars->tfull[buf], (t >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 4, buf, t);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row = tile * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256;
+      OutT* crow = C + static_cast<size_t>(row) * ldc + n0;
+      for (int c0 = 0; c0 < bn; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        if (row < M) {
+          if (c0 + 8 <= n_valid) store8<OutT>(crow + c0, r, relu != 0);
+          if (c0 + 16 <= n_valid) store8<OutT>(crow + c0 + 8, r + 8, relu != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tempty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
+// partial[x][Mw,Nw] = A[rows_x, Mw]^T . B[rows_x, Nw]   (rows split over blockIdx.x)
+// blockIdx.y = 256-wide block of Mw, blockIdx.z = 256-wide block of Nw.
+// ---------------------------------------------------------------------------------------
+constexpr int KT = 64;                  // reduction rows per stage
+constexpr int ATOM_BYTES = KT * 128;    // 64 rows x 64 bf16 = 8 KB
+
+struct alignas(8) WgradBarriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               float* __restrict__ partial, int R, int Mw, int Nw, int tiles_per_cta, int stages,
+               int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * 256, n0 = blockIdx.z * 256;
+  const int m_valid = min(256, Mw - m0), n_valid = min(256, Nw - n0);
+  const int a_loaded = (m_valid + 63) / 64;       // atoms TMA fills
+  const int a_atoms = (a_loaded + 1) & ~1;        // atoms the MMAs read (pairs of 64 = M 128)
+  const int b_atoms = (n_valid + 63) / 64;
+  const int MB = a_atoms / 2;
+  const int bn = (n_valid + 15) & ~15;
+  const int stage_bytes = (a_atoms + b_atoms) * ATOM_BYTES;
+  const int total_tiles = (R + KT - 1) / KT;
+  const int tile_begin = blockIdx.x * tiles_per_cta;
+  const int tile_end = min(total_tiles, tile_begin + tiles_per_cta);
+  const int ntiles = max(0, tile_end - tile_begin);
+
+  WgradBarriers* bars = reinterpret_cast<WgradBarriers*>(smem + stages * stage_bytes);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  // The odd padding atom is never written by TMA: clear it so the MMAs read zeros.
+  if (a_atoms != a_loaded) {
+    for (int s = 0; s < stages; ++s) {
+      uint4* z = reinterpret_cast<uint4*>(smem + s * stage_bytes + a_loaded * ATOM_BYTES);
+      for (int i = threadIdx.x; i < ATOM_BYTES / 16; i += GEMM_THREADS) z[i] = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (*abort_flag || !mbar_wait(&bars->empty[s], ph ^ 1)) {
+          report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 10, s, it);
+          *abort_flag = 1;
+          // giving up: let the copies already issued land before the CTA exits
+          for (int j = it > stages ? it - stages : 0; j < it; ++j)
+            mbar_wait(&bars->full[j % stages], (j / stages) & 1);
+          break;
+        }
+        uint8_t* st = smem + s * stage_bytes;
+        const int r0 = (tile_begin + it) * KT;
+        mbar_expect_tx(&bars->full[s], (a_loaded + b_atoms) * ATOM_BYTES);
+        for (int a = 0; a < a_loaded; ++a)
+          tma_load_2d(st + a * ATOM_BYTES, &tmA, &bars->full[s], m0 + a * 64, r0);
+        for (int b = 0; b < b_atoms; ++b)
+          tma_load_2d(st + (a_atoms + b) * ATOM_BYTES, &tmB, &bars->full[s], n0 + b * 64, r0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, bn, true, true);
+      bool ok = true;
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (*abort_flag || !mbar_wait(&bars->full[s], ph)) {
+          report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 11, s, it);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * stage_bytes);
+        const uint32_t b_addr = a_addr + a_atoms * ATOM_BYTES;
+        for (int kk = 0; kk < KT / 16; ++kk) {
+          const uint64_t bd = make_smem_desc(b_addr + kk * 2048, ATOM_BYTES, 1024);
+          for (int mb = 0; mb < MB; ++mb) {
+            const uint64_t ad =
+                make_smem_desc(a_addr + mb * 2 * ATOM_BYTES + kk * 2048, ATOM_BYTES, 1024);
+            umma_bf16(tmem_base + mb * 256, ad, bd, idesc, (it | kk) != 0);
+          }
+        }
+        umma_commit(&bars->empty[s]);
+      }
+      if (ok) umma_commit(&bars->done);
+    }
+  } else {
+    const int q = warp & 3;
+    float* out = partial + static_cast<size_t>(blockIdx.x) * Mw * Nw;
+    if (ntiles > 0) {
+      bool ok = !*abort_flag && mbar_wait(&bars->done, 0);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(status, ST_TIMEOUT, KERNEL_ID_GEMM, 12, 0, 0);
+        *abort_flag = 1;
+      } else {
+        tc_fence_after();
+        for (int mb = 0; mb < MB; ++mb) {
+          const int m = m0 + mb * 128 + q * 32 + lane;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mb * 256;
+          for (int c0 = 0; c0 < bn; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c0, r);
+            tmem_ld_wait();
+            if (m < Mw && mb * 128 + q * 32 + lane < m_valid) {
+              float* dst = out + static_cast<size_t>(m) * Nw + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                if (c0 + j + 4 <= n_valid)
+                  *reinterpret_cast<float4*>(dst + j) =
+                      make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              }
+            }
+          }
+        }
+      }
+    } else {
+      // no rows for this CTA: its partial is zero
+      for (int i = (warp - 2) * 32 + lane; i < m_valid * n_valid; i += 128) {
+        const int m = i / n_valid, n = i % n_valid;
+        out[static_cast<size_t>(m0 + m) * Nw + n0 + n] = 0.f;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// Deterministic second stage of the split reduction: out[i] = sum_x partial[x][i].
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                       int parts, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < parts; ++p) acc += partial[static_cast<size_t>(p) * n + i];
+    out[i] = acc;
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+
+// Row-major bf16 matrix [rows, cols] with leading dimension ld (elements); box = box_rows x 64.
+static const char* make_tmap_bf16(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols,
+                                  int64_t ld, int box_rows) {
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return "gemm: TMA base must be 16-byte aligned";
+  if ((ld * 2) % 16) return "gemm: TMA row stride must be a multiple of 16 bytes";
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return "gemm: cuTensorMapEncodeTiled is not available from the driver";
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "gemm: cuTensorMapEncodeTiled failed";
+}
+
+static int num_sms() {
+  int dev = 0, n = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+// max_stages / ctas_limit select the launch variant (0 = default).
+const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
+                           int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
+                           int* status, int max_stages, int ctas_limit, cudaStream_t stream) {
+  if (K % 8 || N % 8 || lda % 8 || ldb % 8 || ldc % 8 || K <= 0)
+    return "gemm_nt: K, N and leading dimensions must be positive multiples of 8";
+  if (reinterpret_cast<uintptr_t>(C) % 16) return "gemm_nt: C must be 16-byte aligned";
+  if (M == 0 || N == 0) return nullptr;
+  const int KB = static_cast<int>((K + BK - 1) / BK);
+  const int bn_box = static_cast<int>(std::min<int64_t>(256, (N + 15) / 16 * 16));
+  const int b_blk = bn_box * 128;
+  const int bar_bytes = sizeof(GemmBarriers) + 1024;  // + alignment slack
+  int b_resident = 1, stages = 0;
+  {
+    int64_t left = SMEM_LIMIT - bar_bytes - static_cast<int64_t>(KB) * b_blk;
+    stages = left > 0 ? static_cast<int>(left / A_STAGE_BYTES) : 0;
+    if (stages < 3) {
+      b_resident = 0;
+      stages = (SMEM_LIMIT - bar_bytes) / (A_STAGE_BYTES + b_blk);
+    }
+  }
+  stages = std::min(stages, 8);
+  if (max_stages > 0) stages = std::min(stages, std::max(2, max_stages));
+  if (stages < 2) return "gemm_nt: tile does not fit in shared memory";
+  const int stage_bytes = A_STAGE_BYTES + (b_resident ? 0 : b_blk);
+  const size_t smem = (b_resident ? static_cast<size_t>(KB) * b_blk : 0) +
+                      static_cast<size_t>(stages) * stage_bytes + bar_bytes;
+
+  CUtensorMap tmA, tmB;
+  if (const char* e = make_tmap_bf16(&tmA, A, M, K, lda, BM)) return e;
+  if (const char* e = make_tmap_bf16(&tmB, B, N, K, ldb, bn_box)) return e;
+  const int tiles = static_cast<int>((M + BM - 1) / BM);
+  const int ctas = std::min(tiles, ctas_limit > 0 ? ctas_limit : num_sms());
+  dim3 grid(ctas, static_cast<unsigned>((N + 255) / 256));
+  if (c_dtype == DT_BF16) {
+    auto kern = gemm_nt_kernel<__nv_bfloat16>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
+                                               static_cast<int>(ldc), static_cast<int>(M),
+                                               static_cast<int>(N), static_cast<int>(K), bn_box, stages,
+                                               b_resident, relu ? 1 : 0, status);
+  } else if (c_dtype == DT_F32) {
+    auto kern = gemm_nt_kernel<float>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<float*>(C),
+                                               static_cast<int>(ldc), static_cast<int>(M),
+                                               static_cast<int>(N), static_cast<int>(K), bn_box, stages,
+                                               b_resident, relu ? 1 : 0, status);
+  } else {
+    return "gemm_nt: C must be bf16 or fp32";
+  }
+  return last_launch_error();
+}
+
+// Number of row-split CTAs gemm_tn uses for R reduction rows (scratch = parts * Mw * Nw floats).
+int gemm_tn_parts(int64_t R) {
+  const int total_tiles = static_cast<int>((R + KT - 1) / KT);
+  const int want = std::max(1, std::min(num_sms(), total_tiles / 4));
+  const int tpc = (total_tiles + want - 1) / want;
+  return std::max(1, (total_tiles + tpc - 1) / std::max(1, tpc));
+}
+
+const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ldb, float* out,
+                           float* scratch, int64_t scratch_elems, int64_t R, int64_t Mw, int64_t Nw,
+                           int* status, cudaStream_t stream) {
+  if (Mw % 8 || Nw % 8 || lda % 8 || ldb % 8)
+    return "gemm_tn: widths and leading dimensions must be multiples of 8";
+  if (Mw == 0 || Nw == 0) return nullptr;
+  if (R == 0) {
+    cudaMemsetAsync(out, 0, sizeof(float) * Mw * Nw, stream);
+    return last_launch_error();
+  }
+  const int total_tiles = static_cast<int>((R + KT - 1) / KT);
+  const int parts = gemm_tn_parts(R);
+  const int tpc = (total_tiles + parts - 1) / parts;
+  if (scratch_elems < static_cast<int64_t>(parts) * Mw * Nw) return "gemm_tn: scratch too small";
+
+  const int a_atoms = ((static_cast<int>(std::min<int64_t>(256, Mw)) + 63) / 64 + 1) & ~1;
+  const int b_atoms = (static_cast<int>(std::min<int64_t>(256, Nw)) + 63) / 64;
+  const int stage_bytes = (a_atoms + b_atoms) * ATOM_BYTES;
+  const int bar_bytes = sizeof(WgradBarriers) + 1024;
+  const int stages = std::min(8, (SMEM_LIMIT - bar_bytes) / stage_bytes);
+  if (stages < 2) return "gemm_tn: tile does not fit in shared memory";
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + bar_bytes;
+
+  CUtensorMap tmA, tmB;
+  if (const char* e = make_tmap_bf16(&tmA, A, R, Mw, lda, KT)) return e;
+  if (const char* e = make_tmap_bf16(&tmB, B, R, Nw, ldb, KT)) return e;
+  dim3 grid(parts, static_cast<unsigned>((Mw + 255) / 256), static_cast<unsigned>((Nw + 255) / 256));
+  cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(smem));
+  gemm_tn_kernel<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, scratch, static_cast<int>(R),
+                                                       static_cast<int>(Mw), static_cast<int>(Nw), tpc,
+                                                       stages, status);
+  if (const char* e = last_launch_error()) return e;
+  const int n = static_cast<int>(Mw * Nw);
+  reduce_partials_kernel<<<std::min(1024, (n + 255) / 256), 256, 0, stream>>>(scratch, out, parts, n);
+  return last_launch_error();
+}
+
+}  // namespace plx

@@ -106,7 +106,11 @@ def coo_to_csr(
 
 
 def csr_tensor(crow, col, val, shape):
-    return torch.sparse_csr_tensor(crow, col, val, size=tuple(shape), check_invariants=False)
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)
+        return torch.sparse_csr_tensor(crow, col, val, size=tuple(shape), check_invariants=False)
 
 
 def csr_transpose(A: torch.Tensor) -> torch.Tensor:
