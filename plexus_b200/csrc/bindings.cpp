@@ -29,9 +29,17 @@ int* status_ptr(const Tensor& status) {
   return status.data_ptr<int>();
 }
 
+const int* int_ptr(const Tensor& t) {
+  if (!t.defined() || t.numel() == 0) return nullptr;
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous());
+  return t.data_ptr<int>();
+}
+
+// schedule tensors: block_start, piece_beg, piece_end, long_rows, long_piece_start (int32, device)
 void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
-              const c10::optional<Tensor>& mask, int64_t row_begin, int64_t row_end,
-              const Tensor& long_rows) {
+              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
+              const Tensor& piece_beg, const Tensor& piece_end, const Tensor& long_rows,
+              const Tensor& long_piece_start, const Tensor& scratch) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -39,9 +47,8 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
   TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && val.is_contiguous());
   TORCH_CHECK(H.dim() == 2 && out.dim() == 2 && H.stride(1) == 1 && out.stride(1) == 1);
   TORCH_CHECK(out.scalar_type() == H.scalar_type(), "spmm: out dtype must match H");
-  TORCH_CHECK(0 <= row_begin && row_begin <= row_end && row_end < rowptr.numel());
   const int64_t D = H.size(1);
-  TORCH_CHECK(out.size(1) == D && out.size(0) == row_end - row_begin, "spmm: bad output shape");
+  TORCH_CHECK(out.size(1) == D, "spmm: bad output shape");
   const void* mptr = nullptr;
   int64_t ldm = 0;
   if (mask.has_value() && mask->defined()) {
@@ -50,14 +57,33 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
     mptr = mask->data_ptr();
     ldm = mask->stride(0);
   }
-  const int n_long = static_cast<int>(long_rows.numel());
-  if (n_long) TORCH_CHECK(long_rows.is_cuda() && long_rows.scalar_type() == at::kInt);
+  plx::SpmmSchedule s;
+  s.block_start = int_ptr(block_start);
+  s.num_blocks = block_start.numel() > 0 ? static_cast<int>(block_start.numel()) - 1 : 0;
+  s.piece_beg = int_ptr(piece_beg);
+  s.piece_end = int_ptr(piece_end);
+  s.num_pieces = static_cast<int>(piece_beg.numel());
+  TORCH_CHECK(piece_end.numel() == piece_beg.numel());
+  s.long_rows = int_ptr(long_rows);
+  s.long_piece_start = int_ptr(long_piece_start);
+  s.num_long = static_cast<int>(long_rows.numel());
+  TORCH_CHECK(s.num_long == 0 || long_piece_start.numel() == long_rows.numel() + 1);
+  float* scr = nullptr;
+  int64_t scr_n = 0;
+  if (scratch.defined() && scratch.numel() > 0) {
+    TORCH_CHECK(scratch.is_cuda() && scratch.scalar_type() == at::kFloat && scratch.is_contiguous());
+    scr = scratch.data_ptr<float>();
+    scr_n = scratch.numel();
+  }
   c10::cuda::CUDAGuard guard(H.device());
   check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
                              val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
                              out.stride(0), mptr, ldm, static_cast<int>(D), static_cast<int>(row_begin),
-                             static_cast<int>(row_end), n_long ? long_rows.data_ptr<int>() : nullptr,
-                             n_long, stream()));
+                             s, scr, scr_n, stream()));
+}
+
+int64_t spmm_scratch_per_piece(const Tensor& H) {
+  return plx::spmm_scratch_per_piece(dtype_of(H), static_cast<int>(H.size(1)));
 }
 
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
@@ -225,7 +251,8 @@ void wait_flag(const Tensor& flag, int64_t expected, int64_t max_polls, Tensor& 
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("spmm_csr", &spmm_csr, "CSR SpMM, bf16/fp32 features, fp32 accumulate");
-  m.def("spmm_long_row_threshold", &plx::spmm_long_row_threshold);
+  m.def("spmm_piece_size", &plx::spmm_piece_size);
+  m.def("spmm_scratch_per_piece", &spmm_scratch_per_piece);
   m.def("gemm_nt", &gemm_nt, "C = A . B^T on tcgen05 (bf16 in, fp32 accumulate)");
   m.def("gemm_tn_parts", &gemm_tn_parts, "number of row splits gemm_tn uses");
   m.def("gemm_tn", &gemm_tn, "C = A^T . B on tcgen05 with split reduction");

@@ -10,11 +10,27 @@ namespace plx {
 enum DType : int { DT_BF16 = 0, DT_F32 = 1 };
 
 // ---- spmm.cu
+// Per-matrix work schedule (device arrays, built once per shard; see ops/cuda.py):
+//   block_start[num_blocks+1] : consecutive-row blocks of about equal cost
+//   long rows (more than spmm_piece_size() nonzeros) are cut in pieces [piece_beg, piece_end) of
+//   the nonzero range; long_piece_start[num_long+1] indexes the pieces of each long row.
+struct SpmmSchedule {
+  const int* block_start;
+  int num_blocks;
+  const int* piece_beg;
+  const int* piece_end;
+  int num_pieces;
+  const int* long_rows;
+  const int* long_piece_start;
+  int num_long;
+};
+int spmm_piece_size();
+int64_t spmm_scratch_per_piece(int dtype, int D);
+// scratch: fp32, num_pieces * spmm_scratch_per_piece(dtype, D) elements (unused without long rows)
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
-                            int64_t ldm, int D, int row_begin, int row_end, const int* long_rows,
-                            int n_long, cudaStream_t stream);
-int spmm_long_row_threshold();
+                            int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
+                            float* scratch, int64_t scratch_elems, cudaStream_t stream);
 
 // ---- gemm_tcgen05.cu
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.

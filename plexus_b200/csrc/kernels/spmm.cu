@@ -4,10 +4,13 @@
 // the kernel is organised around memory-level parallelism:
 //   * one warp per row; the warp is split in G = 32/LPR groups of LPR lanes, a group reads one
 //     feature row with 16-byte loads (LPR*VPL vectors cover the D columns), different groups
-//     take different nonzeros of the row, several nonzeros are in flight per group (unroll);
+//     take different nonzeros of the row, and each group keeps several nonzeros in flight;
 //   * column indices / values are read coalesced, 32 at a time, and broadcast by shuffles;
-//   * rows longer than LONG_ROW nonzeros are skipped here and processed by a second launch
-//     with one CTA per long row (power-law graphs have a few rows of >10K nonzeros);
+//   * load balance on power-law graphs comes from a per-matrix schedule built once on the
+//     device: consecutive rows are grouped in blocks of about equal cost (nonzeros + a per-row
+//     constant) and warps walk the blocks round-robin; rows longer than PIECE nonzeros are cut
+//     in pieces of PIECE nonzeros, one warp per piece writes an fp32 partial row to scratch
+//     memory and a fix-up launch sums the pieces of each long row in a fixed order;
 //   * the epilogue optionally multiplies by (mask > 0): that is the ReLU derivative of the
 //     layer input, applied where the input gradient is produced.
 //
@@ -23,7 +26,7 @@
 namespace plx {
 
 constexpr int SPMM_WARPS = 8;
-constexpr int LONG_ROW = 4096;
+constexpr int PIECE = 256;  // rows longer than this are cut in pieces of this many nonzeros
 
 template <typename T>
 struct Vec16;  // 16-byte vector of T
@@ -84,6 +87,7 @@ __device__ __forceinline__ uint4 ldg16(const void* p) {
 }
 
 // Accumulate nonzeros [beg, end) of one row.  Group g of the warp takes nonzeros g, g+G, ...
+// and keeps U of them in flight.
 template <typename T, int LPR, int VPL>
 __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
                                                const float* __restrict__ val,
@@ -92,6 +96,7 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
                                                float (&acc)[VPL][Vec16<T>::N]) {
   constexpr int VN = Vec16<T>::N;
   constexpr int G = 32 / LPR;
+  constexpr int U = VPL == 1 ? 4 : 2;
   const int g = lane / LPR, li = lane % LPR;
   bool active[VPL];
 #pragma unroll
@@ -105,25 +110,28 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
       c = __ldg(col + base + lane);
       a = __ldg(val + base + lane);
     }
-    // every group walks the 32 staged nonzeros with stride G, two at a time
-    for (int jj = 0; jj < cnt; jj += 2 * G) {  // trip count is uniform across the warp
-      const int j0 = jj + g, j1 = jj + G + g;
-      const int c0 = __shfl_sync(0xffffffffu, c, j0 & 31);
-      const float a0 = __shfl_sync(0xffffffffu, a, j0 & 31);
-      const int c1 = __shfl_sync(0xffffffffu, c, j1 & 31);
-      const float a1 = __shfl_sync(0xffffffffu, a, j1 & 31);
-      uint4 v0[VPL], v1[VPL];
-      const bool p0 = j0 < cnt, p1 = j1 < cnt;
+    for (int jj = 0; jj < cnt; jj += U * G) {  // trip count is uniform across the warp
+      int cj[U];
+      float aj[U];
+      bool pj[U];
+      uint4 vj[U][VPL];
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) {
-        if (p0 && active[v]) v0[v] = ldg16(H + c0 * ldh + (v * LPR + li) * VN);
-        if (p1 && active[v]) v1[v] = ldg16(H + c1 * ldh + (v * LPR + li) * VN);
+      for (int u = 0; u < U; ++u) {
+        const int j = jj + u * G + g;
+        cj[u] = __shfl_sync(0xffffffffu, c, j & 31);
+        aj[u] = __shfl_sync(0xffffffffu, a, j & 31);
+        pj[u] = j < cnt;
       }
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) {
-        if (p0 && active[v]) Vec16<T>::fma(acc[v], v0[v], a0);
-        if (p1 && active[v]) Vec16<T>::fma(acc[v], v1[v], a1);
-      }
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+          if (pj[u] && active[v]) vj[u][v] = ldg16(H + cj[u] * ldh + (v * LPR + li) * VN);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+          if (pj[u] && active[v]) Vec16<T>::fma(acc[v], vj[u][v], aj[u]);
     }
   }
   // combine the G groups
@@ -151,106 +159,145 @@ __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __re
   }
 }
 
-template <typename T, int LPR, int VPL>
-__global__ void __launch_bounds__(SPMM_WARPS * 32)
-spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
-                 const float* __restrict__ val, const T* __restrict__ H, int64_t ldh,
-                 T* __restrict__ out, int64_t ldo, const T* __restrict__ mask, int64_t ldm, int D,
-                 int row_begin, int row_end, int skip_long) {
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
-  const int warps_total = gridDim.x * SPMM_WARPS;
-  for (int row = row_begin + warp_global; row < row_end; row += warps_total) {
-    const int64_t beg = __ldg(rowptr + row), end = __ldg(rowptr + row + 1);
-    if (skip_long && end - beg > LONG_ROW) continue;
-    float acc[VPL][Vec16<T>::N];
-#pragma unroll
-    for (int v = 0; v < VPL; ++v)
-#pragma unroll
-      for (int i = 0; i < Vec16<T>::N; ++i) acc[v][i] = 0.f;
-    row_accumulate<T, LPR, VPL>(col, val, H, ldh, D, beg, end, lane, acc);
-    const int64_t orow = row - row_begin;
-    row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc);
-  }
-}
-
-// One CTA per long row: the warps split the nonzeros, partial sums meet in shared memory.
-template <typename T, int LPR, int VPL>
-__global__ void __launch_bounds__(SPMM_WARPS * 32)
-spmm_long_rows_kernel(const int* __restrict__ long_rows, const int* __restrict__ rowptr,
-                      const int* __restrict__ col, const float* __restrict__ val,
-                      const T* __restrict__ H, int64_t ldh, T* __restrict__ out, int64_t ldo,
-                      const T* __restrict__ mask, int64_t ldm, int D, int row_begin, int row_end) {
-  constexpr int VN = Vec16<T>::N;
-  __shared__ float red[SPMM_WARPS][VPL * LPR * VN];
-  const int row = long_rows[blockIdx.x];
-  if (row < row_begin || row >= row_end) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t beg = rowptr[row], end = rowptr[row + 1];
-  const int64_t n = end - beg;
-  const int64_t per = ((n + SPMM_WARPS - 1) / SPMM_WARPS + 31) / 32 * 32;
-  int64_t b = beg + warp * per;
-  if (b > end) b = end;
-  int64_t e = b + per;
-  if (e > end) e = end;
-  float acc[VPL][VN];
+template <int VPL, int VN>
+__device__ __forceinline__ void zero_acc(float (&acc)[VPL][VN]) {
 #pragma unroll
   for (int v = 0; v < VPL; ++v)
 #pragma unroll
     for (int i = 0; i < VN; ++i) acc[v][i] = 0.f;
-  row_accumulate<T, LPR, VPL>(col, val, H, ldh, D, b, e, lane, acc);
-  if (lane < LPR) {
-#pragma unroll
-    for (int v = 0; v < VPL; ++v)
-#pragma unroll
-      for (int i = 0; i < VN; ++i) red[warp][(v * LPR + lane) * VN + i] = acc[v][i];
-  }
-  __syncthreads();
-  if (warp == 0) {
-    if (lane < LPR) {
-#pragma unroll
-      for (int v = 0; v < VPL; ++v)
-#pragma unroll
-        for (int i = 0; i < VN; ++i) {
-          float s = 0.f;
-          for (int w = 0; w < SPMM_WARPS; ++w) s += red[w][(v * LPR + lane) * VN + i];
-          acc[v][i] = s;
-        }
+}
+
+// Rows of at most PIECE nonzeros.  block_start[b] .. block_start[b+1] are consecutive rows of
+// about equal total cost; warps take blocks round-robin.
+template <typename T, int LPR, int VPL>
+__global__ void __launch_bounds__(SPMM_WARPS * 32, VPL == 1 ? 4 : 2)
+spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
+                 const float* __restrict__ val, const T* __restrict__ H, int64_t ldh,
+                 T* __restrict__ out, int64_t ldo, const T* __restrict__ mask, int64_t ldm, int D,
+                 int row_begin, const int* __restrict__ block_start, int num_blocks) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * SPMM_WARPS;
+  for (int b = warp_global; b < num_blocks; b += warps_total) {
+    const int rb = __ldg(block_start + b), re = __ldg(block_start + b + 1);
+    for (int row = rb; row < re; ++row) {
+      const int64_t beg = __ldg(rowptr + row), end = __ldg(rowptr + row + 1);
+      if (end - beg > PIECE) continue;  // handled by the piece kernels
+      float acc[VPL][Vec16<T>::N];
+      zero_acc(acc);
+      row_accumulate<T, LPR, VPL>(col, val, H, ldh, D, beg, end, lane, acc);
+      const int64_t orow = row - row_begin;
+      row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc);
     }
-    const int64_t orow = row - row_begin;
+  }
+}
+
+// One warp per piece of a long row: fp32 partial row -> scratch[piece][LPR*VPL*VN].
+template <typename T, int LPR, int VPL>
+__global__ void __launch_bounds__(SPMM_WARPS * 32, VPL == 1 ? 4 : 2)
+spmm_pieces_kernel(const int* __restrict__ piece_beg, const int* __restrict__ piece_end,
+                   int num_pieces, const int* __restrict__ col, const float* __restrict__ val,
+                   const T* __restrict__ H, int64_t ldh, int D, float* __restrict__ scratch) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int W = LPR * VPL * VN;
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * SPMM_WARPS;
+  for (int p = warp_global; p < num_pieces; p += warps_total) {
+    float acc[VPL][VN];
+    zero_acc(acc);
+    row_accumulate<T, LPR, VPL>(col, val, H, ldh, D, __ldg(piece_beg + p), __ldg(piece_end + p), lane,
+                                acc);
+    if (lane < LPR) {
+      float* dst = scratch + static_cast<int64_t>(p) * W;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        float4* d4 = reinterpret_cast<float4*>(dst + (v * LPR + lane) * VN);
+#pragma unroll
+        for (int i = 0; i < VN; i += 4) d4[i / 4] = make_float4(acc[v][i], acc[v][i + 1], acc[v][i + 2], acc[v][i + 3]);
+      }
+    }
+  }
+}
+
+// One warp per long row: sum its pieces in order, apply the mask, store.
+template <typename T, int LPR, int VPL>
+__global__ void __launch_bounds__(SPMM_WARPS * 32)
+spmm_fixup_kernel(const int* __restrict__ long_rows, const int* __restrict__ long_piece_start,
+                  int num_long, const float* __restrict__ scratch, T* __restrict__ out, int64_t ldo,
+                  const T* __restrict__ mask, int64_t ldm, int D, int row_begin) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int W = LPR * VPL * VN;
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * SPMM_WARPS;
+  for (int i = warp_global; i < num_long; i += warps_total) {
+    float acc[VPL][VN];
+    zero_acc(acc);
+    const int p0 = __ldg(long_piece_start + i), p1 = __ldg(long_piece_start + i + 1);
+    if (lane < LPR) {
+      for (int p = p0; p < p1; ++p) {
+        const float* src = scratch + static_cast<int64_t>(p) * W;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          const float4* s4 = reinterpret_cast<const float4*>(src + (v * LPR + lane) * VN);
+#pragma unroll
+          for (int k = 0; k < VN; k += 4) {
+            const float4 f = s4[k / 4];
+            acc[v][k] += f.x;
+            acc[v][k + 1] += f.y;
+            acc[v][k + 2] += f.z;
+            acc[v][k + 3] += f.w;
+          }
+        }
+      }
+    }
+    const int64_t orow = __ldg(long_rows + i) - row_begin;
     row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc);
   }
+}
+
+static int spmm_grid(int work_items) {
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return std::max(1, std::min(sms * 8, (work_items + SPMM_WARPS - 1) / SPMM_WARPS));
 }
 
 template <typename T, int LPR, int VPL>
 static void launch_spmm(const int* rowptr, const int* col, const float* val, const T* H, int64_t ldh,
                         T* out, int64_t ldo, const T* mask, int64_t ldm, int D, int row_begin,
-                        int row_end, const int* long_rows, int n_long, cudaStream_t stream) {
-  const int rows = row_end - row_begin;
-  if (rows <= 0) return;
-  int sms = 148, dev = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int max_blocks = sms * 8;
-  const int blocks = std::max(1, std::min(max_blocks, (rows + SPMM_WARPS - 1) / SPMM_WARPS));
-  spmm_rows_kernel<T, LPR, VPL><<<blocks, SPMM_WARPS * 32, 0, stream>>>(
-      rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, row_end, n_long > 0 ? 1 : 0);
-  if (n_long > 0) {
-    spmm_long_rows_kernel<T, LPR, VPL><<<n_long, SPMM_WARPS * 32, 0, stream>>>(
-        long_rows, rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, row_end);
+                        const SpmmSchedule& s, float* scratch, cudaStream_t stream) {
+  if (s.num_blocks > 0)
+    spmm_rows_kernel<T, LPR, VPL><<<spmm_grid(s.num_blocks), SPMM_WARPS * 32, 0, stream>>>(
+        rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s.block_start, s.num_blocks);
+  if (s.num_long > 0) {
+    spmm_pieces_kernel<T, LPR, VPL><<<spmm_grid(s.num_pieces), SPMM_WARPS * 32, 0, stream>>>(
+        s.piece_beg, s.piece_end, s.num_pieces, col, val, H, ldh, D, scratch);
+    spmm_fixup_kernel<T, LPR, VPL><<<spmm_grid(s.num_long), SPMM_WARPS * 32, 0, stream>>>(
+        s.long_rows, s.long_piece_start, s.num_long, scratch, out, ldo, mask, ldm, D, row_begin);
   }
+}
+
+// fp32 scratch elements per piece for a feature width of D elements of the given dtype.
+int64_t spmm_scratch_per_piece(int dtype, int D) {
+  const int vn = dtype == DT_BF16 ? 8 : 4;
+  const int vecs = (D + vn - 1) / vn;
+  int lpr = 4;
+  while (lpr < 32 && lpr < vecs) lpr <<= 1;
+  const int vpl = (vecs + 31) / 32 > 1 ? (vecs + 31) / 32 : 1;
+  return static_cast<int64_t>(lpr) * vpl * vn;
 }
 
 template <typename T>
 static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const float* val, const T* H,
                                  int64_t ldh, T* out, int64_t ldo, const T* mask, int64_t ldm,
-                                 int row_begin, int row_end, const int* long_rows, int n_long,
+                                 int row_begin, const SpmmSchedule& s, float* scratch,
                                  cudaStream_t stream) {
   constexpr int VN = Vec16<T>::N;
   const int vecs = (D + VN - 1) / VN;  // 16-byte vectors per feature row
-#define PLX_SPMM(LPR, VPL)                                                                        \
-  launch_spmm<T, LPR, VPL>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, row_end, \
-                           long_rows, n_long, stream)
+#define PLX_SPMM(LPR, VPL) \
+  launch_spmm<T, LPR, VPL>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s, scratch, stream)
   if (vecs <= 4) PLX_SPMM(4, 1);
   else if (vecs <= 8) PLX_SPMM(8, 1);
   else if (vecs <= 16) PLX_SPMM(16, 1);
@@ -263,30 +310,32 @@ static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const
   return last_launch_error();
 }
 
-int spmm_long_row_threshold() { return LONG_ROW; }
+int spmm_piece_size() { return PIECE; }
 
-// out[row_begin:row_end] = A[row_begin:row_end] . H  (optionally masked by mask > 0).
-// long_rows: int32 list of rows with more than LONG_ROW nonzeros (may be empty).
+// out[r - row_begin] = A[r, :] . H for the rows covered by the schedule (optionally masked).
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
-                            int64_t ldm, int D, int row_begin, int row_end, const int* long_rows,
-                            int n_long, cudaStream_t stream) {
+                            int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
+                            float* scratch, int64_t scratch_elems, cudaStream_t stream) {
   const int esz = dtype == DT_BF16 ? 2 : 4;
   if ((ldh * esz) % 16 || (ldo * esz) % 16 || (D * esz) % 16 || (mask && (ldm * esz) % 16))
     return "spmm: feature rows must be multiples of 16 bytes";
   if (reinterpret_cast<uintptr_t>(H) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
-      reinterpret_cast<uintptr_t>(mask) % 16)
+      reinterpret_cast<uintptr_t>(mask) % 16 || reinterpret_cast<uintptr_t>(scratch) % 16)
     return "spmm: feature pointers must be 16-byte aligned";
-  if (row_end <= row_begin || D == 0) return nullptr;
+  if (D == 0 || (sched.num_blocks == 0 && sched.num_long == 0)) return nullptr;
+  if (sched.num_pieces > 0 &&
+      scratch_elems < static_cast<int64_t>(sched.num_pieces) * spmm_scratch_per_piece(dtype, D))
+    return "spmm: scratch too small for the long-row pieces";
   if (dtype == DT_BF16)
     return dispatch_spmm<__nv_bfloat16>(D, rowptr, col, val, reinterpret_cast<const __nv_bfloat16*>(H),
                                         ldh, reinterpret_cast<__nv_bfloat16*>(out), ldo,
                                         reinterpret_cast<const __nv_bfloat16*>(mask), ldm, row_begin,
-                                        row_end, long_rows, n_long, stream);
+                                        sched, scratch, stream);
   if (dtype == DT_F32)
     return dispatch_spmm<float>(D, rowptr, col, val, reinterpret_cast<const float*>(H), ldh,
                                 reinterpret_cast<float*>(out), ldo, reinterpret_cast<const float*>(mask),
-                                ldm, row_begin, row_end, long_rows, n_long, stream);
+                                ldm, row_begin, sched, scratch, stream);
   return "spmm: features must be bf16 or fp32";
 }
 

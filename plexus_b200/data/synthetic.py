@@ -137,7 +137,7 @@ def undirected_unique_keys(
         rounds += 1
     if keys.numel() > want:
         h = _lsr(hash_stream(seed, 3000, keys), 1)
-        thr = int((want / keys.numel()) * float(1 << 62))
+        thr = int((want / keys.numel()) * float(1 << 63))
         keys = keys[h < thr]
     return keys
 

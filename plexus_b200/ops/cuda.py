@@ -26,7 +26,6 @@ def _count(n: int) -> None:
 
 _status: Dict[int, torch.Tensor] = {}
 _scratch: Dict[int, torch.Tensor] = {}
-_long_rows: Dict[Tuple[int, int], torch.Tensor] = {}
 
 
 def status_buffer(device=None) -> torch.Tensor:
@@ -62,16 +61,79 @@ def _csr_parts(A):
     return crow, col, val
 
 
-def long_rows_of(crow: torch.Tensor) -> torch.Tensor:
-    """Rows with more nonzeros than the kernel's long-row threshold (cached per matrix)."""
-    key = (crow.data_ptr(), crow.numel())
-    got = _long_rows.get(key)
-    if got is None:
-        thr = _ext.load().spmm_long_row_threshold()
-        deg = crow[1:] - crow[:-1]
-        got = torch.nonzero(deg > thr).flatten().to(torch.int32)
-        _long_rows[key] = got
-    return got
+# per-row constant added to the nonzero count when balancing row blocks, and the cost of a block
+SPMM_ROW_COST = 8
+SPMM_BLOCK_COST = 1024
+
+
+class SpmmSchedule:
+    """Device-side work schedule of one CSR matrix (or row range), built once and cached."""
+
+    __slots__ = ("block_start", "piece_beg", "piece_end", "long_rows", "long_piece_start", "launches")
+
+
+def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSchedule:
+    """Row blocks of about equal cost plus the pieces of rows longer than the kernel's piece size.
+
+    The result is cached on ``owner`` (the sparse tensor object), so it lives exactly as long
+    as the matrix it describes.
+    """
+    cache = None
+    if owner is not None:
+        cache = getattr(owner, "_plx_spmm_schedules", None)
+        if cache is None:
+            cache = {}
+            try:
+                owner._plx_spmm_schedules = cache
+            except Exception:
+                cache = None
+    key = (r0, r1)
+    if cache is not None and key in cache:
+        return cache[key]
+    _schedules = cache if cache is not None else {}
+    piece = _ext.load().spmm_piece_size()
+    dev = crow.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    sch = SpmmSchedule()
+    rows = r1 - r0
+    if rows <= 0:
+        empty = torch.empty(0, **i32)
+        sch.block_start = sch.piece_beg = sch.piece_end = sch.long_rows = sch.long_piece_start = empty
+        sch.launches = 0
+        _schedules[key] = sch
+        return sch
+    beg = crow[r0:r1].to(torch.int64)
+    deg = crow[r0 + 1 : r1 + 1].to(torch.int64) - beg
+    is_long = deg > piece
+    cost = torch.where(is_long, torch.zeros_like(deg), deg) + SPMM_ROW_COST
+    wcum = torch.cumsum(cost, 0)
+    total = int(wcum[-1])
+    nb = max(1, min(rows, total // SPMM_BLOCK_COST))
+    targets = (torch.arange(1, nb, device=dev, dtype=torch.float64) * (total / nb)).to(torch.int64)
+    inner = torch.searchsorted(wcum, targets, right=True)
+    sch.block_start = (torch.cat([
+        torch.zeros(1, dtype=torch.int64, device=dev), inner,
+        torch.full((1,), rows, dtype=torch.int64, device=dev)]) + r0).to(torch.int32)
+    idx = torch.nonzero(is_long).flatten()
+    if idx.numel():
+        ldeg, lbeg = deg[idx], beg[idx]
+        npieces = (ldeg + piece - 1) // piece
+        pstart = torch.zeros(idx.numel() + 1, dtype=torch.int64, device=dev)
+        pstart[1:] = torch.cumsum(npieces, 0)
+        owner = torch.repeat_interleave(torch.arange(idx.numel(), device=dev), npieces)
+        k = torch.arange(int(pstart[-1]), device=dev) - pstart[:-1][owner]
+        pb = lbeg[owner] + k * piece
+        pe = torch.minimum(pb + piece, (lbeg + ldeg)[owner])
+        sch.piece_beg, sch.piece_end = pb.to(torch.int32), pe.to(torch.int32)
+        sch.long_rows = (idx + r0).to(torch.int32)
+        sch.long_piece_start = pstart.to(torch.int32)
+        sch.launches = 3
+    else:
+        empty = torch.empty(0, **i32)
+        sch.piece_beg = sch.piece_end = sch.long_rows = sch.long_piece_start = empty
+        sch.launches = 1
+    _schedules[key] = sch
+    return sch
 
 
 def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None):
@@ -84,12 +146,19 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
         out = torch.empty((r1 - r0, H.shape[1]), dtype=H.dtype, device=H.device)
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
-    lr = long_rows_of(crow)
-    C.spmm_csr(crow, col, val, H, out, relu_mask, r0, r1, lr)
-    _count(2 if lr.numel() else 1)
+    sch = spmm_schedule(crow, r0, r1, owner=A)
+    npieces = sch.piece_beg.numel()
+    scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
+    C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
+               sch.long_rows, sch.long_piece_start, scratch)
+    _count(sch.launches)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
     return out
+
+
+def _EMPTY_F32(device):
+    return torch.empty(0, dtype=torch.float32, device=device)
 
 
 def _bf16(t: torch.Tensor) -> torch.Tensor:

@@ -54,8 +54,8 @@ def test_one_gpu_epoch_matches_cpu_pipeline_and_oracle(fuse):
         got = gpu["gw"][l].view(layer.in_channels, layer.out_channels)
         want = torch.zeros_like(got)
         want[: ref_gw[l].shape[0], : ref_gw[l].shape[1]] = ref_gw[l].float()
-        assert _rel(got, want) < 0.25, l
-    assert _rel(gpu["gx"].view(N, -1)[:, :F], ref_gx.float()) < 0.25
+        assert _rel(got, want) < 0.35, l
+    assert _rel(gpu["gx"].view(N, -1)[:, :F], ref_gx.float()) < 0.35
 
 
 def test_training_reduces_loss_with_fused_adam():
