@@ -227,10 +227,10 @@ def run_ours(args):
     launches0 = opc.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    torch.cuda.nvtx.range_push("timed_epochs")  # lets a profiler select the timed launches
+    nvtx_range = torch.cuda.nvtx.range_start("timed_epochs")  # lets a profiler select these launches
     for _ in range(args.steps):
         loss = step(labels)
-    torch.cuda.nvtx.range_pop()
+    torch.cuda.nvtx.range_end(nvtx_range)
     ev1.record()
     barrier_sync()
     clocks = sampler.stop()
