@@ -29,6 +29,40 @@ int* status_ptr(const Tensor& status) {
   return status.data_ptr<int>();
 }
 
+plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld) {
+  plx::PushTargets p;
+  TORCH_CHECK(ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS), "too many push targets");
+  p.n = static_cast<int>(ptrs.size());
+  for (int i = 0; i < p.n; ++i) p.base[i] = reinterpret_cast<void*>(ptrs[i]);
+  p.ld = ld;
+  return p;
+}
+
+plx::SlotList make_slots(const std::vector<int64_t>& ptrs) {
+  plx::SlotList s;
+  TORCH_CHECK(ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS + 1), "too many slots");
+  s.n = static_cast<int>(ptrs.size());
+  for (int i = 0; i < s.n; ++i) s.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return s;
+}
+
+plx::PeerSync make_sync(const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
+                        int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status) {
+  plx::PeerSync s;
+  TORCH_CHECK(remote_flags.size() == local_flags.size() &&
+              remote_flags.size() <= static_cast<size_t>(plx::MAX_PEERS));
+  s.n = static_cast<int>(remote_flags.size());
+  for (int i = 0; i < s.n; ++i) {
+    s.remote_flag[i] = reinterpret_cast<int*>(remote_flags[i]);
+    s.local_flag[i] = reinterpret_cast<const int*>(local_flags[i]);
+  }
+  s.epoch = static_cast<int>(epoch);
+  s.timeout_ns = static_cast<unsigned long long>(timeout_ms * 1e6);
+  s.kernel_id = static_cast<int>(kernel_id);
+  s.status = status_ptr(status);
+  return s;
+}
+
 const int* int_ptr(const Tensor& t) {
   if (!t.defined() || t.numel() == 0) return nullptr;
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous());
@@ -39,7 +73,8 @@ const int* int_ptr(const Tensor& t) {
 void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
               const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
               const Tensor& piece_beg, const Tensor& piece_end, const Tensor& long_rows,
-              const Tensor& long_piece_start, const Tensor& scratch) {
+              const Tensor& long_piece_start, const Tensor& scratch,
+              const std::vector<int64_t>& push_ptrs, int64_t push_ld) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -75,11 +110,12 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
     scr = scratch.data_ptr<float>();
     scr_n = scratch.numel();
   }
+  plx::PushTargets push = make_push(push_ptrs, push_ld);
   c10::cuda::CUDAGuard guard(H.device());
   check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
                              val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
                              out.stride(0), mptr, ldm, static_cast<int>(D), static_cast<int>(row_begin),
-                             s, scr, scr_n, stream()));
+                             s, scr, scr_n, push.n ? &push : nullptr, stream()));
 }
 
 int64_t spmm_scratch_per_piece(const Tensor& H) {
@@ -87,18 +123,20 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 }
 
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
-             int64_t max_stages, int64_t ctas_limit) {
+             int64_t max_stages, int64_t ctas_limit, const std::vector<int64_t>& push_ptrs,
+             int64_t push_ld) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
+  plx::PushTargets push = make_push(push_ptrs, push_ld);
   c10::cuda::CUDAGuard guard(A.device());
   check(plx::launch_gemm_nt(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(),
                             C.stride(0), dtype_of(C), A.size(0), B.size(0), A.size(1), relu,
                             status_ptr(status), static_cast<int>(max_stages),
-                            static_cast<int>(ctas_limit), stream()));
+                            static_cast<int>(ctas_limit), push.n ? &push : nullptr, stream()));
 }
 
 int64_t gemm_tn_parts(int64_t R) { return plx::gemm_tn_parts(R); }
@@ -247,6 +285,70 @@ void wait_flag(const Tensor& flag, int64_t expected, int64_t max_polls, Tensor& 
                               static_cast<unsigned>(max_polls), status_ptr(status), stream()));
 }
 
+// ---- peer-memory collectives -------------------------------------------------------------
+void reduce_slots(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t slot_ld, bool relu,
+                  const c10::optional<Tensor>& mask, const std::vector<int64_t>& remote_flags,
+                  const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms,
+                  int64_t kernel_id, const Tensor& status) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->scalar_type() == at::kBFloat16 && mask->sizes() == out.sizes() && mask->stride(1) == 1);
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  check(plx::launch_reduce_slots_bf16(out.data_ptr(), out.stride(0), make_slots(slot_ptrs), slot_ld,
+                                      out.size(0), static_cast<int>(out.size(1)), relu, mptr, ldm,
+                                      make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                      stream()));
+}
+
+void reduce_slots_f32(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t op,
+                      const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
+                      int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(out.device());
+  check(plx::launch_reduce_slots_f32(out.data_ptr<float>(), make_slots(slot_ptrs), out.numel(),
+                                     static_cast<int>(op),
+                                     make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                     stream()));
+}
+
+void push_copy(const Tensor& src, const std::vector<int64_t>& dst_ptrs) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous());
+  c10::cuda::CUDAGuard guard(src.device());
+  check(plx::launch_push_copy(src.data_ptr(), make_slots(dst_ptrs), src.numel() * src.element_size(),
+                              stream()));
+}
+
+void gather_slots(const std::vector<int64_t>& src_ptrs, const std::vector<int64_t>& dst_ptrs, int64_t bytes,
+                  const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
+                  int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(plx::launch_gather_slots(make_slots(src_ptrs), make_slots(dst_ptrs), bytes,
+                                 make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                 stream()));
+}
+
+std::tuple<int64_t, py::bytes> symm_alloc(int64_t bytes) {
+  void* p = nullptr;
+  unsigned char h[64];
+  check(plx::symm_alloc(static_cast<size_t>(bytes), &p, h));
+  return {reinterpret_cast<int64_t>(p), py::bytes(reinterpret_cast<const char*>(h), 64)};
+}
+
+int64_t symm_open(const std::string& handle) {
+  TORCH_CHECK(handle.size() == 64, "IPC handle must be 64 bytes");
+  void* p = nullptr;
+  check(plx::symm_open(reinterpret_cast<const unsigned char*>(handle.data()), &p));
+  return reinterpret_cast<int64_t>(p);
+}
+
+void symm_close(int64_t ptr) { check(plx::symm_close(reinterpret_cast<void*>(ptr))); }
+void symm_free(int64_t ptr) { check(plx::symm_free(reinterpret_cast<void*>(ptr))); }
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -263,4 +365,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relu_bwd", &relu_bwd);
   m.def("prep_weight", &prep_weight);
   m.def("wait_flag", &wait_flag);
+  m.def("reduce_slots", &reduce_slots);
+  m.def("reduce_slots_f32", &reduce_slots_f32);
+  m.def("push_copy", &push_copy);
+  m.def("gather_slots", &gather_slots);
+  m.def("symm_alloc", &symm_alloc);
+  m.def("symm_open", &symm_open);
+  m.def("symm_close", &symm_close);
+  m.def("symm_free", &symm_free);
 }

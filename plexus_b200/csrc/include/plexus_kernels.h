@@ -9,6 +9,16 @@ namespace plx {
 
 enum DType : int { DT_BF16 = 0, DT_F32 = 1 };
 
+// Peer-memory destinations of a fused "compute + push" epilogue: besides its own output, a
+// kernel stores every result row at the same (row, column) position of up to MAX_PEERS
+// receive buffers that live in other GPUs' memory (plain stores over NVLink).
+constexpr int MAX_PEERS = 7;
+struct PushTargets {
+  int n;                  // number of peers (0 = no push)
+  void* base[MAX_PEERS];  // receive slot of this rank inside each peer's workspace
+  int64_t ld;             // leading dimension of the receive slots (elements)
+};
+
 // ---- spmm.cu
 // Per-matrix work schedule (device arrays, built once per shard; see ops/cuda.py):
 //   block_start[num_blocks+1] : consecutive-row blocks of about equal cost
@@ -30,13 +40,15 @@ int64_t spmm_scratch_per_piece(int dtype, int D);
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
                             int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
-                            float* scratch, int64_t scratch_elems, cudaStream_t stream);
+                            float* scratch, int64_t scratch_elems, const PushTargets* push,
+                            cudaStream_t stream);
 
 // ---- gemm_tcgen05.cu
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
-                           int* status, int max_stages, int ctas_limit, cudaStream_t stream);
+                           int* status, int max_stages, int ctas_limit, const PushTargets* push,
+                           cudaStream_t stream);
 // out[Mw,Nw] fp32 = A[R,Mw]^T . B[R,Nw]; scratch >= gemm_tn_parts(R)*Mw*Nw floats.
 int gemm_tn_parts(int64_t R);
 const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ldb, float* out,
@@ -83,6 +95,36 @@ const char* launch_prep_weight(int dtype, const void* W, void* Wb, void* WbT, in
                                cudaStream_t stream);
 const char* launch_wait_flag(const int* flag, int expected, unsigned max_polls, int* status,
                              cudaStream_t stream);
+
+// ---- comm_fused.cu
+struct SlotList {
+  int n;
+  void* ptr[MAX_PEERS + 1];
+};
+// Flags of one op: remote_flag[q] is this rank's entry in peer q's flag array (written here),
+// local_flag[q] is peer q's entry in this rank's flag array (polled here).
+struct PeerSync {
+  int n;
+  int* remote_flag[MAX_PEERS];
+  const int* local_flag[MAX_PEERS];
+  int epoch;
+  unsigned long long timeout_ns;
+  int kernel_id;
+  int* status;
+};
+const char* launch_reduce_slots_bf16(void* out, int64_t ldo, const SlotList& slots, int64_t lds,
+                                     int64_t rows, int cols, bool relu, const void* mask, int64_t ldm,
+                                     const PeerSync& sync, cudaStream_t stream);
+const char* launch_reduce_slots_f32(float* out, const SlotList& slots, int64_t n, int op,
+                                    const PeerSync& sync, cudaStream_t stream);
+const char* launch_push_copy(const void* src, const SlotList& dst, int64_t bytes, cudaStream_t stream);
+const char* launch_gather_slots(const SlotList& src, const SlotList& dst, int64_t bytes,
+                                const PeerSync& sync, cudaStream_t stream);
+// symmetric workspace over CUDA IPC (one cudaMalloc per rank, handles exchanged by the caller)
+const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+const char* symm_open(const unsigned char* handle64, void** ptr);
+const char* symm_close(void* ptr);
+const char* symm_free(void* ptr);
 
 inline const char* last_launch_error() {
   cudaError_t e = cudaGetLastError();

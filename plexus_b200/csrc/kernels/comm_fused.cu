@@ -1,0 +1,267 @@
+// Peer-memory collectives over NVLink: the receive side of the fused "compute + push" kernels,
+// small stand-alone collectives, and the CUDA-IPC symmetric workspace they run on.
+//
+// Protocol (one axis of the process grid, p ranks, every rank runs the same sequence of ops):
+//   * every rank owns a workspace [flags | buffer 0 | buffer 1]; buffer b has one receive slot
+//     per source rank.  Op number e (the "epoch", counted per axis) uses buffer e % 2.
+//   * producer: a compute kernel (SpMM / GEMM epilogue, or push_copy) stores its rows into slot
+//     `me` of every peer's buffer with plain 16-byte stores.
+//   * consumer (the next launch on the same stream): block 0 publishes flag[e%2][me] = e on every
+//     peer (release, system scope); every block waits until its own flag[e%2][q] >= e for all
+//     peers q (acquire), then reduces / copies the slots.
+//   * a buffer is rewritten only two ops later; by then every peer has passed the wait of the op
+//     in between, which its owner publishes only after it finished reading: no extra barrier.
+// Every wait is bounded by a wall-clock limit (globaltimer); on expiry the kernel records
+// TIMEOUT(kernel, peer, expected, seen) in the status words and returns without touching data.
+//
+// Reference: the collectives issued through AxoNN/NCCL at plexus/gcn_conv.py:177-278 and
+// plexus/cross_entropy.py:46-98.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../include/plexus_kernels.h"
+#include "../include/ptx_sm100.cuh"
+
+namespace plx {
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Publish this rank's flag on every peer, then wait for every peer's flag.  Returns false on
+// timeout (uniform over the block).
+__device__ __forceinline__ bool signal_and_wait(const PeerSync& s) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  if (blockIdx.x == 0 && threadIdx.x < s.n) {
+    __threadfence_system();
+    st_release_sys(s.remote_flag[threadIdx.x], s.epoch);
+  }
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = global_ns();
+    for (int q = 0; q < s.n; ++q) {
+      int seen = ld_acquire_sys(s.local_flag[q]);
+      while (seen < s.epoch) {
+        if (global_ns() - t0 > s.timeout_ns) {
+          report_status(s.status, ST_TIMEOUT, s.kernel_id, q, s.epoch, seen);
+          ok_flag = 0;
+          break;
+        }
+        __nanosleep(64);
+        seen = ld_acquire_sys(s.local_flag[q]);
+      }
+      if (!ok_flag) break;
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+// out[r, c] = act( out[r, c] + sum_q slot_q[r, c] ) with fp32 accumulation, bf16 storage.
+// act = optional ReLU, then optional multiplication by (mask > 0).
+__global__ void __launch_bounds__(256)
+reduce_slots_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const SlotList slots,
+                         int64_t lds, int64_t rows, int cols, int relu,
+                         const __nv_bfloat16* __restrict__ mask, int64_t ldm, const PeerSync sync) {
+  if (!signal_and_wait(sync)) return;
+  const int vec_per_row = cols / 8;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    float acc[8];
+    {
+      const uint4 v = *reinterpret_cast<const uint4*>(out + r * ldo + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        acc[2 * k] = f.x;
+        acc[2 * k + 1] = f.y;
+      }
+    }
+    for (int q = 0; q < slots.n; ++q) {
+      const uint4 v = *reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    if (relu) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = fmaxf(acc[k], 0.f);
+    }
+    if (mask != nullptr) {
+      const uint4 mv = *reinterpret_cast<const uint4*>(mask + r * ldm + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&mv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        if (!(f.x > 0.f)) acc[2 * k] = 0.f;
+        if (!(f.y > 0.f)) acc[2 * k + 1] = 0.f;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) po[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
+  }
+}
+
+// out[i] = out[i] (op) slot_q[i] for fp32 vectors; op 0 = sum, 1 = max.
+__global__ void __launch_bounds__(256)
+reduce_slots_f32_kernel(float* __restrict__ out, const SlotList slots, int64_t n, int op,
+                        const PeerSync sync) {
+  if (!signal_and_wait(sync)) return;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float a = out[i];
+    for (int q = 0; q < slots.n; ++q) {
+      const float b = static_cast<const float*>(slots.ptr[q])[i];
+      a = op == 0 ? a + b : fmaxf(a, b);
+    }
+    out[i] = a;
+  }
+}
+
+// Copy n words from src to every destination (peers' slots and local copies).
+template <typename W>
+__global__ void __launch_bounds__(256)
+push_copy_kernel(const W* __restrict__ src, const SlotList dst, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const W v = src[i];
+    for (int q = 0; q < dst.n; ++q) static_cast<W*>(dst.ptr[q])[i] = v;
+  }
+}
+
+// After the wait: copy slot q (n words) to dst_q for every peer (all-gather landing).
+template <typename W>
+__global__ void __launch_bounds__(256)
+gather_slots_kernel(const SlotList src, const SlotList dst, int64_t n, const PeerSync sync) {
+  if (!signal_and_wait(sync)) return;
+  for (int q = 0; q < src.n; ++q) {
+    const W* s = static_cast<const W*>(src.ptr[q]);
+    W* d = static_cast<W*>(dst.ptr[q]);
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+      d[i] = s[i];
+  }
+}
+
+static int copy_grid(int64_t items) {
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(sms * 8, (items + 255) / 256)));
+}
+
+const char* launch_reduce_slots_bf16(void* out, int64_t ldo, const SlotList& slots, int64_t lds,
+                                     int64_t rows, int cols, bool relu, const void* mask, int64_t ldm,
+                                     const PeerSync& sync, cudaStream_t stream) {
+  if (cols % 8 || ldo % 8 || lds % 8 || (mask && ldm % 8)) return "reduce_slots: widths must be multiples of 8";
+  if (slots.n < 0 || slots.n > MAX_PEERS || sync.n < 0 || sync.n > MAX_PEERS) return "reduce_slots: too many peers";
+  reduce_slots_bf16_kernel<<<copy_grid(rows * (cols / 8)), 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(out), ldo, slots, lds, rows, cols, relu ? 1 : 0,
+      static_cast<const __nv_bfloat16*>(mask), ldm, sync);
+  return last_launch_error();
+}
+
+const char* launch_reduce_slots_f32(float* out, const SlotList& slots, int64_t n, int op,
+                                    const PeerSync& sync, cudaStream_t stream) {
+  if (slots.n < 0 || slots.n > MAX_PEERS || sync.n < 0 || sync.n > MAX_PEERS) return "reduce_slots: too many peers";
+  reduce_slots_f32_kernel<<<copy_grid(n), 256, 0, stream>>>(out, slots, n, op, sync);
+  return last_launch_error();
+}
+
+static bool all_aligned16(const void* a, const SlotList& l) {
+  if (reinterpret_cast<uintptr_t>(a) % 16) return false;
+  for (int q = 0; q < l.n; ++q)
+    if (reinterpret_cast<uintptr_t>(l.ptr[q]) % 16) return false;
+  return true;
+}
+
+const char* launch_push_copy(const void* src, const SlotList& dst, int64_t bytes, cudaStream_t stream) {
+  if (bytes % 4) return "push_copy: size must be a multiple of 4 bytes";
+  if (bytes == 0 || dst.n == 0) return nullptr;
+  if (bytes % 16 == 0 && all_aligned16(src, dst))
+    push_copy_kernel<uint4><<<copy_grid(bytes / 16), 256, 0, stream>>>(static_cast<const uint4*>(src), dst,
+                                                                       bytes / 16);
+  else
+    push_copy_kernel<uint32_t><<<copy_grid(bytes / 4), 256, 0, stream>>>(static_cast<const uint32_t*>(src),
+                                                                         dst, bytes / 4);
+  return last_launch_error();
+}
+
+const char* launch_gather_slots(const SlotList& src, const SlotList& dst, int64_t bytes,
+                                const PeerSync& sync, cudaStream_t stream) {
+  if (bytes % 4 || src.n != dst.n) return "gather_slots: bad arguments";
+  if (bytes % 16 == 0 && all_aligned16(nullptr, src) && all_aligned16(nullptr, dst))
+    gather_slots_kernel<uint4><<<copy_grid(std::max<int64_t>(1, bytes / 16)), 256, 0, stream>>>(src, dst,
+                                                                                              bytes / 16, sync);
+  else
+    gather_slots_kernel<uint32_t><<<copy_grid(std::max<int64_t>(1, bytes / 4)), 256, 0, stream>>>(src, dst,
+                                                                                                bytes / 4, sync);
+  return last_launch_error();
+}
+
+// ------------------------------------------------------------------ CUDA-IPC workspace
+const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cudaGetErrorString(e);
+  e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) return cudaGetErrorString(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cudaGetErrorString(e);
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return nullptr;
+}
+
+const char* symm_open(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cudaGetErrorString(e);
+  *ptr = p;
+  return nullptr;
+}
+
+const char* symm_close(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+const char* symm_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace plx

@@ -85,7 +85,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
-               int b_resident, int relu, int* status) {
+               int b_resident, int relu, int* status, const PushTargets push) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -229,6 +229,12 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (row < M) {
           if (c0 + 8 <= n_valid) store8<OutT>(crow + c0, r, relu != 0);
           if (c0 + 16 <= n_valid) store8<OutT>(crow + c0 + 8, r + 8, relu != 0);
+          // fused collective: the tile also goes straight into the peers' receive slots
+          for (int q = 0; q < push.n; ++q) {
+            OutT* prow = static_cast<OutT*>(push.base[q]) + static_cast<size_t>(row) * push.ld + n0;
+            if (c0 + 8 <= n_valid) store8<OutT>(prow + c0, r, relu != 0);
+            if (c0 + 16 <= n_valid) store8<OutT>(prow + c0 + 8, r + 8, relu != 0);
+          }
         }
       }
       tc_fence_before();
@@ -459,7 +465,16 @@ static int num_sms() {
 // max_stages / ctas_limit select the launch variant (0 = default).
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
-                           int* status, int max_stages, int ctas_limit, cudaStream_t stream) {
+                           int* status, int max_stages, int ctas_limit, const PushTargets* push_in,
+                           cudaStream_t stream) {
+  PushTargets push;
+  push.n = 0;
+  if (push_in != nullptr) {
+    push = *push_in;
+    if (push.n < 0 || push.n > MAX_PEERS || push.ld % 8) return "gemm_nt: bad push targets";
+    for (int q = 0; q < push.n; ++q)
+      if (reinterpret_cast<uintptr_t>(push.base[q]) % 16) return "gemm_nt: push targets must be 16-byte aligned";
+  }
   if (K % 8 || N % 8 || lda % 8 || ldb % 8 || ldc % 8 || K <= 0)
     return "gemm_nt: K, N and leading dimensions must be positive multiples of 8";
   if (reinterpret_cast<uintptr_t>(C) % 16) return "gemm_nt: C must be 16-byte aligned";
@@ -496,14 +511,14 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
-                                               b_resident, relu ? 1 : 0, status);
+                                               b_resident, relu ? 1 : 0, status, push);
   } else if (c_dtype == DT_F32) {
     auto kern = gemm_nt_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<float*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
-                                               b_resident, relu ? 1 : 0, status);
+                                               b_resident, relu ? 1 : 0, status, push);
   } else {
     return "gemm_nt: C must be bf16 or fp32";
   }

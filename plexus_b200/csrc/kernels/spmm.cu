@@ -146,7 +146,8 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
 
 template <typename T, int LPR, int VPL>
 __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __restrict__ mask_row,
-                                          int D, int lane, float (&acc)[VPL][Vec16<T>::N]) {
+                                          int D, int lane, float (&acc)[VPL][Vec16<T>::N],
+                                          const PushTargets& push, int64_t orow) {
   constexpr int VN = Vec16<T>::N;
   if (lane >= LPR) return;
 #pragma unroll
@@ -154,7 +155,11 @@ __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __re
     const int c = (v * LPR + lane) * VN;
     if (c < D) {
       if (mask_row != nullptr) Vec16<T>::mask(acc[v], ldg16(mask_row + c));
-      *reinterpret_cast<uint4*>(out_row + c) = Vec16<T>::pack(acc[v]);
+      const uint4 packed = Vec16<T>::pack(acc[v]);
+      *reinterpret_cast<uint4*>(out_row + c) = packed;
+      // fused collective: the same row goes straight into the peers' receive slots
+      for (int q = 0; q < push.n; ++q)
+        *reinterpret_cast<uint4*>(static_cast<T*>(push.base[q]) + orow * push.ld + c) = packed;
     }
   }
 }
@@ -174,7 +179,8 @@ __global__ void __launch_bounds__(SPMM_WARPS * 32, VPL == 1 ? 4 : 2)
 spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
                  const float* __restrict__ val, const T* __restrict__ H, int64_t ldh,
                  T* __restrict__ out, int64_t ldo, const T* __restrict__ mask, int64_t ldm, int D,
-                 int row_begin, const int* __restrict__ block_start, int num_blocks) {
+                 int row_begin, const int* __restrict__ block_start, int num_blocks,
+                 const PushTargets push) {
   const int lane = threadIdx.x & 31;
   const int warp_global = blockIdx.x * SPMM_WARPS + (threadIdx.x >> 5);
   const int warps_total = gridDim.x * SPMM_WARPS;
@@ -187,7 +193,8 @@ spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
       zero_acc(acc);
       row_accumulate<T, LPR, VPL>(col, val, H, ldh, D, beg, end, lane, acc);
       const int64_t orow = row - row_begin;
-      row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc);
+      row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc, push,
+                             orow);
     }
   }
 }
@@ -225,7 +232,8 @@ template <typename T, int LPR, int VPL>
 __global__ void __launch_bounds__(SPMM_WARPS * 32)
 spmm_fixup_kernel(const int* __restrict__ long_rows, const int* __restrict__ long_piece_start,
                   int num_long, const float* __restrict__ scratch, T* __restrict__ out, int64_t ldo,
-                  const T* __restrict__ mask, int64_t ldm, int D, int row_begin) {
+                  const T* __restrict__ mask, int64_t ldm, int D, int row_begin,
+                  const PushTargets push) {
   constexpr int VN = Vec16<T>::N;
   constexpr int W = LPR * VPL * VN;
   const int lane = threadIdx.x & 31;
@@ -253,7 +261,8 @@ spmm_fixup_kernel(const int* __restrict__ long_rows, const int* __restrict__ lon
       }
     }
     const int64_t orow = __ldg(long_rows + i) - row_begin;
-    row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc);
+    row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc, push,
+                           orow);
   }
 }
 
@@ -267,15 +276,16 @@ static int spmm_grid(int work_items) {
 template <typename T, int LPR, int VPL>
 static void launch_spmm(const int* rowptr, const int* col, const float* val, const T* H, int64_t ldh,
                         T* out, int64_t ldo, const T* mask, int64_t ldm, int D, int row_begin,
-                        const SpmmSchedule& s, float* scratch, cudaStream_t stream) {
+                        const SpmmSchedule& s, float* scratch, const PushTargets& push,
+                        cudaStream_t stream) {
   if (s.num_blocks > 0)
     spmm_rows_kernel<T, LPR, VPL><<<spmm_grid(s.num_blocks), SPMM_WARPS * 32, 0, stream>>>(
-        rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s.block_start, s.num_blocks);
+        rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s.block_start, s.num_blocks, push);
   if (s.num_long > 0) {
     spmm_pieces_kernel<T, LPR, VPL><<<spmm_grid(s.num_pieces), SPMM_WARPS * 32, 0, stream>>>(
         s.piece_beg, s.piece_end, s.num_pieces, col, val, H, ldh, D, scratch);
     spmm_fixup_kernel<T, LPR, VPL><<<spmm_grid(s.num_long), SPMM_WARPS * 32, 0, stream>>>(
-        s.long_rows, s.long_piece_start, s.num_long, scratch, out, ldo, mask, ldm, D, row_begin);
+        s.long_rows, s.long_piece_start, s.num_long, scratch, out, ldo, mask, ldm, D, row_begin, push);
   }
 }
 
@@ -293,11 +303,12 @@ template <typename T>
 static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const float* val, const T* H,
                                  int64_t ldh, T* out, int64_t ldo, const T* mask, int64_t ldm,
                                  int row_begin, const SpmmSchedule& s, float* scratch,
-                                 cudaStream_t stream) {
+                                 const PushTargets& push, cudaStream_t stream) {
   constexpr int VN = Vec16<T>::N;
   const int vecs = (D + VN - 1) / VN;  // 16-byte vectors per feature row
 #define PLX_SPMM(LPR, VPL) \
-  launch_spmm<T, LPR, VPL>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s, scratch, stream)
+  launch_spmm<T, LPR, VPL>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, s, scratch, push, \
+                           stream)
   if (vecs <= 4) PLX_SPMM(4, 1);
   else if (vecs <= 8) PLX_SPMM(8, 1);
   else if (vecs <= 16) PLX_SPMM(16, 1);
@@ -316,8 +327,17 @@ int spmm_piece_size() { return PIECE; }
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
                             int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
-                            float* scratch, int64_t scratch_elems, cudaStream_t stream) {
+                            float* scratch, int64_t scratch_elems, const PushTargets* push_in,
+                            cudaStream_t stream) {
   const int esz = dtype == DT_BF16 ? 2 : 4;
+  PushTargets push;
+  push.n = 0;
+  if (push_in != nullptr) {
+    push = *push_in;
+    if (push.n < 0 || push.n > MAX_PEERS || (push.ld * esz) % 16) return "spmm: bad push targets";
+    for (int q = 0; q < push.n; ++q)
+      if (reinterpret_cast<uintptr_t>(push.base[q]) % 16) return "spmm: push targets must be 16-byte aligned";
+  }
   if ((ldh * esz) % 16 || (ldo * esz) % 16 || (D * esz) % 16 || (mask && (ldm * esz) % 16))
     return "spmm: feature rows must be multiples of 16 bytes";
   if (reinterpret_cast<uintptr_t>(H) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
@@ -331,11 +351,11 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
     return dispatch_spmm<__nv_bfloat16>(D, rowptr, col, val, reinterpret_cast<const __nv_bfloat16*>(H),
                                         ldh, reinterpret_cast<__nv_bfloat16*>(out), ldo,
                                         reinterpret_cast<const __nv_bfloat16*>(mask), ldm, row_begin,
-                                        sched, scratch, stream);
+                                        sched, scratch, push, stream);
   if (dtype == DT_F32)
     return dispatch_spmm<float>(D, rowptr, col, val, reinterpret_cast<const float*>(H), ldh,
                                 reinterpret_cast<float*>(out), ldo, reinterpret_cast<const float*>(mask),
-                                ldm, row_begin, sched, scratch, stream);
+                                ldm, row_begin, sched, scratch, push, stream);
   return "spmm: features must be bf16 or fp32";
 }
 

@@ -213,11 +213,18 @@ def layer_backward(grad_out, AGG, weight, A_t, spec: LayerSpec, input_relu_mask=
 
     depth_p = group_size(spec.depth_group)
     timers.start("GRAD_H = A.T * GRAD_AGG")
-    if runtime.flags.comm == "fused" and depth_p > 1 and not spec.gather_features:
+    if runtime.flags.comm == "fused" and depth_p > 1:
         from ..parallel import fused
 
         grad_x = fused.spmm_all_reduce(A_t, grad_agg, spec.depth_group, relu_mask=input_relu_mask)
         timers.stop("GRAD_H = A.T * GRAD_AGG")
+        if spec.gather_features:
+            # the features are a flat depth shard: keep this rank's slice of the reduced gradient
+            flat = grad_x.reshape(-1)
+            pad = (-flat.numel()) % depth_p
+            if pad:
+                flat = torch.nn.functional.pad(flat, (0, pad))
+            grad_x = depth_slice(flat, depth_p, group_rank(spec.depth_group)).clone()
     else:
         grad_x = ops.spmm(A_t, grad_agg, relu_mask=input_relu_mask)
         timers.stop("GRAD_H = A.T * GRAD_AGG")

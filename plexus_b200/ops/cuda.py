@@ -136,7 +136,9 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
     return sch
 
 
-def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None):
+def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None,
+         push_ptrs=(), push_ld=0):
+    """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective)."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -150,7 +152,7 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     npieces = sch.piece_beg.numel()
     scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
     C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
-               sch.long_rows, sch.long_piece_start, scratch)
+               sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld))
     _count(sch.launches)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
@@ -170,7 +172,8 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
     )
 
 
-def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0):
+def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0,
+         push_ptrs=(), push_ld=0):
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas = GEMM_VARIANTS[variant]
@@ -204,7 +207,7 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         C.prep_weight(b.contiguous(), None, bt)
         _count(1)
     out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
-    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas)
+    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, list(push_ptrs), int(push_ld))
     _count(1)
     return out
 

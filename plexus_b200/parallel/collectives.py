@@ -15,8 +15,13 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from .. import runtime
 from ..utils.timers import get_timers
 from .grid import group_size
+
+
+def _fused(t: torch.Tensor) -> bool:
+    return runtime.flags.comm == "fused" and t.is_cuda
 
 _bytes_moved = {"gather": 0, "all-reduce": 0, "reduce-scatter": 0}
 
@@ -39,7 +44,11 @@ def all_gather(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.Tenso
     timers.start("gather")
     t = t.contiguous()
     _bytes_moved["gather"] += t.numel() * t.element_size() * (p - 1)
-    if dim == 0:
+    if dim == 0 and _fused(t) and (t.numel() * t.element_size()) % 4 == 0:
+        from . import fused
+
+        out = fused.all_gather(t, process_group)
+    elif dim == 0:
         out = torch.empty((p * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         dist.all_gather_into_tensor(out, t, group=process_group)
     else:
@@ -57,6 +66,16 @@ def all_reduce(t: torch.Tensor, process_group=None, op=None) -> torch.Tensor:
     timers = get_timers()
     timers.start("all-reduce")
     _bytes_moved["all-reduce"] += t.numel() * t.element_size()
+    if _fused(t) and op in (None, dist.ReduceOp.SUM, dist.ReduceOp.MAX):
+        from . import fused
+
+        if fused.supports(t) and (t.dtype == torch.float32 or op in (None, dist.ReduceOp.SUM)):
+            if t.dtype == torch.float32:
+                fused.all_reduce_f32(t, process_group, op)
+            else:
+                fused.all_reduce_bf16(t, process_group)
+            timers.stop("all-reduce")
+            return t
     if not t.is_contiguous():
         tmp = t.contiguous()
         dist.all_reduce(tmp, op=op or dist.ReduceOp.SUM, group=process_group)
@@ -81,6 +100,21 @@ def reduce_scatter(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.T
     t = t.contiguous()
     _bytes_moved["reduce-scatter"] += t.numel() * t.element_size()
     out = torch.empty((t.shape[0] // p,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    if _fused(t):
+        from . import fused
+
+        if fused.supports(t):
+            # peer-memory all-reduce of a copy, then keep this rank's slice
+            tmp = t.clone()
+            if tmp.dtype == torch.float32:
+                fused.all_reduce_f32(tmp, process_group)
+            else:
+                fused.all_reduce_bf16(tmp.view(-1, 8) if tmp.dim() == 1 and tmp.numel() % 8 == 0 else tmp,
+                                      process_group)
+            r = dist.get_rank(process_group)
+            out.copy_(tmp[r * out.shape[0] : (r + 1) * out.shape[0]])
+            timers.stop("reduce-scatter")
+            return out
     if t.device.type == "cpu":
         # gloo has no reduce_scatter_tensor: all-reduce a copy and slice.
         tmp = t.clone()

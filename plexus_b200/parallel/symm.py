@@ -1,0 +1,129 @@
+"""Symmetric peer-memory workspaces, one per grid axis this rank belongs to.
+
+A workspace is one ``cudaMalloc`` per rank whose CUDA-IPC handle is exchanged over the axis'
+process group, so every rank holds a device pointer into every peer's buffer and kernels can
+store into / load from peer memory directly over NVLink.  Layout of each rank's buffer::
+
+    [ flags: int32[2][8] (1 KiB reserved) | buffer 0: p slots | buffer 1: p slots ]
+
+Slot ``s`` of a buffer receives data from group rank ``s``.  The op counter ("epoch") of an axis
+selects buffer ``epoch % 2``; see ``csrc/kernels/comm_fused.cu`` for the flag protocol and why
+double buffering is enough.  Workspaces grow on demand (a collective operation: every rank of
+the axis asks for the same size at the same point of the program).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+
+FLAG_BYTES = 1024
+MAX_GROUP = 8
+DEFAULT_TIMEOUT_MS = 5000.0
+
+
+class AxisComm:
+    def __init__(self, group):
+        self.group = group
+        self.p = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.p > MAX_GROUP:
+            raise ValueError(f"peer-memory collectives support at most {MAX_GROUP} ranks per axis")
+        self.peers = [q for q in range(self.p) if q != self.rank]
+        self.epoch = 0
+        self.slot_bytes = 0
+        self.local_ptr = 0
+        self.ptrs: List[int] = []
+        self.timeout_ms = DEFAULT_TIMEOUT_MS
+
+    # -- allocation ---------------------------------------------------------------------
+    def ensure(self, slot_bytes: int) -> None:
+        slot_bytes = (int(slot_bytes) + 1023) // 1024 * 1024
+        if slot_bytes <= self.slot_bytes:
+            return
+        C = _ext.load()
+        dev = torch.device("cuda", torch.cuda.current_device())
+        # nobody may still be using the old workspace
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.release()
+        total = FLAG_BYTES + 2 * self.p * slot_bytes
+        ptr, handle = C.symm_alloc(total)
+        mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
+        allh = torch.empty((self.p, 64), dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allh, mine, group=self.group)
+        allh = allh.cpu()
+        self.ptrs = []
+        for q in range(self.p):
+            self.ptrs.append(ptr if q == self.rank else C.symm_open(bytes(allh[q].tolist())))
+        self.local_ptr, self.slot_bytes = ptr, slot_bytes
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def release(self) -> None:
+        if not self.ptrs:
+            return
+        C = _ext.load()
+        for q, ptr in enumerate(self.ptrs):
+            if q != self.rank:
+                C.symm_close(ptr)
+        C.symm_free(self.local_ptr)
+        self.ptrs, self.local_ptr, self.slot_bytes = [], 0, 0
+
+    # -- addressing ---------------------------------------------------------------------
+    def slot(self, owner: int, buf: int, src: int) -> int:
+        """Address (in this process) of receive slot ``src`` of buffer ``buf`` on rank ``owner``."""
+        return self.ptrs[owner] + FLAG_BYTES + (buf * self.p + src) * self.slot_bytes
+
+    def flag(self, owner: int, buf: int, src: int) -> int:
+        return self.ptrs[owner] + (buf * MAX_GROUP + src) * 4
+
+    def next_op(self):
+        self.epoch += 1
+        return self.epoch, self.epoch % 2
+
+    def push_targets(self, buf: int) -> List[int]:
+        """This rank's slot in every peer's buffer."""
+        return [self.slot(q, buf, self.rank) for q in self.peers]
+
+    def recv_slots(self, buf: int) -> List[int]:
+        """Every peer's slot in this rank's buffer."""
+        return [self.slot(self.rank, buf, q) for q in self.peers]
+
+    def sync(self, buf: int):
+        remote = [self.flag(q, buf, self.rank) for q in self.peers]
+        local = [self.flag(self.rank, buf, q) for q in self.peers]
+        return remote, local
+
+
+_axes: Dict[int, AxisComm] = {}
+
+
+def axis_for(group) -> AxisComm:
+    key = id(group)
+    if key not in _axes:
+        _axes[key] = AxisComm(group)
+    return _axes[key]
+
+
+def setup(grid) -> None:
+    """Create the (empty) workspace objects of this rank's three line groups."""
+    for axis in ("x", "y", "z"):
+        g = grid.group(axis)
+        if g is not None:
+            axis_for(g)
+
+
+def teardown() -> None:
+    if _axes:
+        torch.cuda.synchronize()
+    for ax in _axes.values():
+        try:
+            ax.release()
+        except Exception:
+            pass
+    _axes.clear()

@@ -1,0 +1,147 @@
+"""Multi-GPU tests: peer-memory (fused) collectives and the 3D-parallel model on 2+ B200s.
+
+Each test spawns one process per GPU (NCCL for bootstrap).  The fused path is compared with the
+NCCL path run in the same processes and, loosely, with the fp64 dense oracle.
+"""
+
+import os
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import oracle, small_processed_graph
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _entry(rank, world, fn, init_file, args, errq):
+    try:
+        torch.cuda.set_device(rank)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+        fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put((rank, traceback.format_exc()))
+        raise
+
+
+def run_gpus(fn, world, *args, timeout=300):
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_entry, args=(r, world, fn, os.path.join(d, "init"), args, errq))
+                 for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout)
+        alive = [p for p in procs if p.is_alive()]
+        for p in alive:
+            p.terminate()
+        errs = []
+        while not errq.empty():
+            errs.append(errq.get())
+        if errs:
+            raise AssertionError("\n".join(f"[rank {r}]\n{tb}" for r, tb in errs))
+        assert not alive, "multi-GPU test timed out"
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def _primitives(rank, world):
+    import plexus_b200 as plx
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.parallel import fused
+
+    grid = plx.init(world, 1, 1, comm="fused")
+    g = grid.group("x")
+    dev = torch.device("cuda", rank)
+    for it, n in enumerate([1000, 37, 250001, 1000, 64, 5]):  # grows and shrinks the workspace use
+        torch.manual_seed(it)
+        full = torch.randn(world, n)
+        mine = full[rank].to(dev)
+        s = fused.all_reduce_f32(mine.clone(), g)
+        assert torch.allclose(s.cpu(), full.sum(0), rtol=1e-5, atol=1e-5), (it, "sum")
+        m = fused.all_reduce_f32(mine.clone(), g, dist.ReduceOp.MAX)
+        assert torch.equal(m.cpu(), full.max(0).values), (it, "max")
+        ga = fused.all_gather(mine, g)
+        assert torch.equal(ga.cpu(), full.reshape(-1)), (it, "gather")
+        fb = torch.randn(world, n, 16).to(torch.bfloat16)
+        r = fused.all_reduce_bf16(fb[rank].to(dev).clone(), g)
+        want = fb.float().sum(0)
+        assert (r.float().cpu() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-3, (it, "bf16")
+    opc.check_status()
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_fused_primitives(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_primitives, world)
+
+
+def _model(rank, world, grid, layers):
+    import plexus_b200 as plx
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.utils.checkpoint import _cut_features, _cut_weight
+    from plexus_b200.utils.dataloader import DataLoader
+
+    data, nc = small_processed_graph(n=5000, e=60000, f=100, c=47, seed=9)
+    results = {}
+    for comm in ("nccl", "fused"):
+        plx.init(*grid, comm=comm)
+        adj, feats, labels, N, F, C = DataLoader(None, layers, data=(data, nc)).load()
+        model = Net(layers, F, 64, C, seed=5)
+        for _ in range(3):  # several steps: exercises buffer reuse across ops
+            feats.grad = None
+            for p_ in model.parameters():
+                p_.grad = None
+            out = model(feats, adj)
+            loss = parallel_cross_entropy(out, labels, layers, N, C)
+            loss.backward()
+        torch.cuda.synchronize()
+        opc.check_status()
+        results[comm] = dict(loss=loss.item(), gx=feats.grad.float().cpu(),
+                             gw=[l.weight.grad.float().cpu() for l in model.layers], model=model, feats=feats)
+        if comm == "nccl":
+            plx.shutdown()
+    a, b = results["nccl"], results["fused"]
+
+    def rel(x, y):
+        return ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item()
+
+    assert abs(a["loss"] - b["loss"]) < 5e-3 * abs(a["loss"]), (a["loss"], b["loss"])
+    for l in range(layers):
+        assert rel(b["gw"][l], a["gw"][l]) < 3e-2, l
+    assert rel(b["gx"], a["gx"]) < 3e-2
+    ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, layers, 64, seed=5)
+    assert abs(b["loss"] - ref_loss.item()) < 2e-2 * abs(ref_loss.item())
+    for l, layer in enumerate(b["model"].layers):
+        want = _cut_weight(layer, ref_gw[l].float())
+        assert rel(b["gw"][l], want) < 0.35, l
+    assert rel(b["gx"], _cut_features(ref_gx.float(), b["feats"])) < 0.35
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 2, 1), (1, 1, 2)])
+def test_fused_model_matches_nccl_and_oracle_2gpu(grid):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("not enough GPUs")
+    run_gpus(_model, 2, grid, 3)
+
+
+@pytest.mark.parametrize("grid", [(2, 2, 2), (4, 2, 1)])
+def test_fused_model_8gpu(grid):
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    run_gpus(_model, 8, grid, 3)
