@@ -95,7 +95,9 @@ reduce_slots_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const Slo
         acc[2 * k + 1] = f.y;
       }
     }
-    for (int q = 0; q < slots.n; ++q) {
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q) {
+      if (q >= slots.n) break;
       const uint4 v = *reinterpret_cast<const uint4*>(
           static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
       const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);

@@ -46,15 +46,23 @@ struct alignas(8) GemmBarriers {
   int abort_flag;
 };
 
+// Epilogue staging: every epilogue warp owns 32 rows; a segment of SEG_BYTES per row goes
+// TMEM -> registers -> shared memory, then leaves with 16-byte stores in which consecutive lanes
+// cover consecutive bytes of one row (256-byte bursts), locally and into the peers' slots.
+constexpr int SEG_BYTES = 256;
+constexpr int STAGE_PITCH = SEG_BYTES + 16;  // padding spreads the rows over the banks
+constexpr int STAGING_BYTES = 4 * 32 * STAGE_PITCH;
+
+// Convert 16 accumulator columns (fp32 bits) and store them at `dst` in shared memory.
 template <typename OutT>
-__device__ __forceinline__ void store8(OutT* dst, const uint32_t* r, bool relu);
+__device__ __forceinline__ void stage16(uint8_t* dst, const uint32_t (&r)[16], bool relu);
 
 template <>
-__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t* r,
-                                                      bool relu) {
-  uint32_t packed[4];
+__device__ __forceinline__ void stage16<__nv_bfloat16>(uint8_t* dst, const uint32_t (&r)[16],
+                                                       bool relu) {
+  uint32_t packed[8];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 8; ++i) {
     float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
     if (relu) {
       a = fmaxf(a, 0.f);
@@ -63,19 +71,22 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const 
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     packed[i] = *reinterpret_cast<uint32_t*>(&v);
   }
-  *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
 }
 
 template <>
-__device__ __forceinline__ void store8<float>(float* dst, const uint32_t* r, bool relu) {
-  float v[8];
+__device__ __forceinline__ void stage16<float>(uint8_t* dst, const uint32_t (&r)[16], bool relu) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  uint32_t v[16];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[i] = __uint_as_float(r[i]);
-    if (relu) v[i] = fmaxf(v[i], 0.f);
-  }
-  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  for (int i = 0; i < 16; ++i)
+    v[i] = relu ? __float_as_uint(fmaxf(__uint_as_float(r[i]), 0.f)) : r[i];
+  d[0] = make_uint4(v[0], v[1], v[2], v[3]);
+  d[1] = make_uint4(v[4], v[5], v[6], v[7]);
+  d[2] = make_uint4(v[8], v[9], v[10], v[11]);
+  d[3] = make_uint4(v[12], v[13], v[14], v[15]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -102,6 +113,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* ring = smem + (b_resident ? KB * b_blk_bytes : 0);   // stages
   const int stage_bytes = A_STAGE_BYTES + (b_resident ? 0 : b_blk_bytes);
   GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(ring + stages * stage_bytes);
+  uint8_t* staging = reinterpret_cast<uint8_t*>(bars) + ((sizeof(GemmBarriers) + 15) & ~15);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -219,27 +231,50 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      const int row = tile * BM + q * 32 + lane;
+      constexpr int ESZ = sizeof(OutT);
+      constexpr int SEG_COLS = SEG_BYTES / ESZ;  // columns per staged segment
+      constexpr int LANES_PER_ROW = SEG_BYTES / 16;
+      constexpr int ROWS_PER_ITER = 32 / LANES_PER_ROW;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256;
-      OutT* crow = C + static_cast<size_t>(row) * ldc + n0;
-      for (int c0 = 0; c0 < bn; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
-        if (row < M) {
-          if (c0 + 8 <= n_valid) store8<OutT>(crow + c0, r, relu != 0);
-          if (c0 + 16 <= n_valid) store8<OutT>(crow + c0 + 8, r + 8, relu != 0);
-          // fused collective: the tile also goes straight into the peers' receive slots
-          for (int q = 0; q < push.n; ++q) {
-            OutT* prow = static_cast<OutT*>(push.base[q]) + static_cast<size_t>(row) * push.ld + n0;
-            if (c0 + 8 <= n_valid) store8<OutT>(prow + c0, r, relu != 0);
-            if (c0 + 16 <= n_valid) store8<OutT>(prow + c0 + 8, r + 8, relu != 0);
+      uint8_t* my_stage = staging + (warp - 2) * 32 * STAGE_PITCH;
+      const int row0 = tile * BM + q * 32;
+      for (int seg0 = 0; seg0 < bn; seg0 += SEG_COLS) {
+        const int seg_cols = min(SEG_COLS, bn - seg0);
+        for (int c0 = 0; c0 < seg_cols; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + seg0 + c0, r);
+          tmem_ld_wait();
+          stage16<OutT>(my_stage + lane * STAGE_PITCH + c0 * ESZ, r, relu != 0);
+        }
+        if (seg0 + SEG_COLS >= bn) {
+          // all TMEM reads of this tile are done: hand the accumulator back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tempty[buf]);
+        } else {
+          __syncwarp();
+        }
+        const int sub = lane / LANES_PER_ROW, l = lane % LANES_PER_ROW;
+        const int col = seg0 + l * (16 / ESZ);  // first column of this lane's 16 bytes
+        if (col + 16 / ESZ <= n_valid) {
+          for (int rr = 0; rr < 32; rr += ROWS_PER_ITER) {
+            const int rl = rr + sub;
+            const int row = row0 + rl;
+            if (row < M) {
+              const uint4 v = *reinterpret_cast<const uint4*>(my_stage + rl * STAGE_PITCH + l * 16);
+              *reinterpret_cast<uint4*>(C + static_cast<size_t>(row) * ldc + n0 + col) = v;
+              // fused collective: the same bytes go straight into the peers' receive slots
+#pragma unroll
+              for (int p = 0; p < MAX_PEERS; ++p)  // static indices keep the pointers in registers
+                if (p < push.n)
+                  *reinterpret_cast<uint4*>(static_cast<OutT*>(push.base[p]) +
+                                            static_cast<size_t>(row) * push.ld + n0 + col) = v;
+            }
           }
         }
+        __syncwarp();
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tempty[buf]);
+
     }
   }
 
@@ -482,7 +517,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   const int KB = static_cast<int>((K + BK - 1) / BK);
   const int bn_box = static_cast<int>(std::min<int64_t>(256, (N + 15) / 16 * 16));
   const int b_blk = bn_box * 128;
-  const int bar_bytes = sizeof(GemmBarriers) + 1024;  // + alignment slack
+  const int bar_bytes = sizeof(GemmBarriers) + 16 + STAGING_BYTES + 1024;  // + staging + alignment slack
   int b_resident = 1, stages = 0;
   {
     int64_t left = SMEM_LIMIT - bar_bytes - static_cast<int64_t>(KB) * b_blk;

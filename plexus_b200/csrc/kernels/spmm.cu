@@ -158,8 +158,10 @@ __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __re
       const uint4 packed = Vec16<T>::pack(acc[v]);
       *reinterpret_cast<uint4*>(out_row + c) = packed;
       // fused collective: the same row goes straight into the peers' receive slots
-      for (int q = 0; q < push.n; ++q)
-        *reinterpret_cast<uint4*>(static_cast<T*>(push.base[q]) + orow * push.ld + c) = packed;
+#pragma unroll
+      for (int q = 0; q < MAX_PEERS; ++q)  // static indices keep the pointers in registers
+        if (q < push.n)
+          *reinterpret_cast<uint4*>(static_cast<T*>(push.base[q]) + orow * push.ld + c) = packed;
     }
   }
 }

@@ -111,6 +111,9 @@ class LayerSpec:
     gather_features: bool
     gather_weights: bool
     relu: bool = False
+    # transform-then-aggregate order: OUT = A . (H . W) with W holding all output columns
+    combine_first: bool = False
+    local_out_channels: int = 0
 
 
 def _aggregate(A, H, spec: LayerSpec):
@@ -137,8 +140,98 @@ def _full_weight(weight, spec: LayerSpec, dtype):
     return W if W.dtype == dtype else W.to(dtype)
 
 
+def _combine_first_forward(H, A, weight, spec: LayerSpec):
+    """``OUT = A . (H . W)``: cheaper when the layer narrows (few output channels).
+
+    ``W`` is sharded by rows over the inner axis only, so ``T = H . W`` (partial over inner)
+    has all output columns; ``A . T`` is partial over the outer axis and is reduce-scattered
+    along the columns, which lands exactly in the standard output layout
+    ``(N/depth) x (out/outer)``.  Returns ``(OUT, H)`` (the input is what backward needs).
+    """
+    timers = get_timers()
+    timers.start("gcn conv fwd")
+    W = _full_weight(weight, spec, H.dtype)
+    timers.start("OUT = AGG * W")
+    T = tuned_matmul(H, W, "H * W " + str(spec.layer_num))
+    timers.stop("OUT = AGG * W")
+    coll.all_reduce(T, spec.inner_group)
+    outer_p = group_size(spec.outer_group)
+    if runtime.flags.comm == "fused" and outer_p > 1:
+        from ..parallel import fused
+
+        timers.start("AGG = A * H and All-Reduce AGG")
+        U = fused.spmm_all_reduce(A, T, spec.outer_group)
+        timers.stop("AGG = A * H and All-Reduce AGG")
+    else:
+        timers.start("AGG = A * H")
+        U = ops.spmm(A, T)
+        timers.stop("AGG = A * H")
+        coll.all_reduce(U, spec.outer_group)
+    lo = spec.local_out_channels
+    r = group_rank(spec.outer_group)
+    OUT = U if outer_p == 1 else U[:, r * lo : (r + 1) * lo].contiguous()
+    if spec.relu:
+        OUT = torch.relu_(OUT)
+    timers.stop("gcn conv fwd")
+    return OUT, H
+
+
+def _combine_first_backward(grad_out, H, weight, A_t, spec: LayerSpec, input_relu_mask=None,
+                            need_input_grad: bool = True):
+    timers = get_timers()
+    timers.start("gcn conv bwd")
+    W = _full_weight(weight, spec, H.dtype)
+    outer_p = group_size(spec.outer_group)
+    depth_p = group_size(spec.depth_group)
+    if outer_p > 1:
+        # column blocks of the output gradient from every outer rank
+        parts = coll.all_gather(grad_out.unsqueeze(0).contiguous(), dim=0, process_group=spec.outer_group)
+        grad_u = parts.permute(1, 0, 2).reshape(grad_out.shape[0], -1).contiguous()
+    else:
+        grad_u = grad_out
+    timers.start("GRAD_H = A.T * GRAD_AGG")
+    if runtime.flags.comm == "fused" and depth_p > 1:
+        from ..parallel import fused
+
+        grad_t = fused.spmm_all_reduce(A_t, grad_u, spec.depth_group)
+        timers.stop("GRAD_H = A.T * GRAD_AGG")
+    else:
+        grad_t = ops.spmm(A_t, grad_u)
+        timers.stop("GRAD_H = A.T * GRAD_AGG")
+        coll.all_reduce(grad_t, spec.depth_group)
+
+    timers.start("GRAD_W = AGG.T * GRAD_OUT")
+    grad_w = tuned_matmul(
+        H, grad_t, "H.T * GRAD_T " + str(spec.layer_num), trans_a=True,
+        out_dtype=torch.promote_types(weight.dtype, torch.float32),
+    )
+    timers.stop("GRAD_W = AGG.T * GRAD_OUT")
+    coll.all_reduce(grad_w, spec.outer_group)  # rows of H are spread over the outer axis
+    grad_w = grad_w.reshape(-1)
+    if spec.gather_weights:
+        # identical on every depth rank already: keep this rank's flat slice
+        grad_w = depth_slice(grad_w, depth_p, group_rank(spec.depth_group)).clone()
+    grad_w = grad_w.to(weight.dtype)
+
+    grad_x = None
+    if need_input_grad:
+        timers.start("GRAD_AGG = GRAD_OUT * W.T")
+        grad_x = tuned_matmul(grad_t, W, "GRAD_T * W.T " + str(spec.layer_num), trans_b=True)
+        timers.stop("GRAD_AGG = GRAD_OUT * W.T")
+        if input_relu_mask is not None:
+            grad_x = ops.relu_backward(grad_x, input_relu_mask)
+    timers.stop("gcn conv bwd")
+    return grad_x, grad_w
+
+
 def layer_forward(x, A, weight, spec: LayerSpec):
-    """Returns ``(OUT, AGG)``; ``OUT`` already has the ReLU applied if ``spec.relu``."""
+    """Returns ``(OUT, saved)``; ``OUT`` already has the ReLU applied if ``spec.relu``.
+
+    ``saved`` is what backward needs besides the weight: ``AGG`` for the aggregate-first order,
+    the layer input for the combine-first order.
+    """
+    if spec.combine_first:
+        return _combine_first_forward(x, A, weight, spec)
     timers = get_timers()
     timers.start("gcn conv fwd")
     if spec.gather_features:
@@ -178,6 +271,8 @@ def layer_backward(grad_out, AGG, weight, A_t, spec: LayerSpec, input_relu_mask=
     is applied to the returned input gradient inside the SpMM epilogue.
     Returns ``(grad_x, grad_weight_flat)``.
     """
+    if spec.combine_first:
+        return _combine_first_backward(grad_out, AGG, weight, A_t, spec, input_relu_mask, need_input_grad)
     timers = get_timers()
     timers.start("gcn conv bwd")
     W = _full_weight(weight, spec, AGG.dtype)
@@ -259,6 +354,8 @@ class GCNConvFunction(torch.autograd.Function):
         gather_weights,
         layer_num,
         relu=False,
+        combine_first=False,
+        local_out_channels=0,
     ):
         spec = LayerSpec(
             layer_num=layer_num,
@@ -270,6 +367,8 @@ class GCNConvFunction(torch.autograd.Function):
             gather_features=bool(gather_features),
             gather_weights=bool(gather_weights),
             relu=bool(relu),
+            combine_first=bool(combine_first),
+            local_out_channels=int(local_out_channels),
         )
         OUT, AGG = layer_forward(x, edge_index, weight, spec)
         ctx.spec = spec
@@ -293,7 +392,7 @@ class GCNConvFunction(torch.autograd.Function):
         grad_x, grad_w = layer_backward(
             grad_output, AGG, weight, ctx.adj_t, spec, need_input_grad=ctx.need_x
         )
-        return (grad_x, None, None, grad_w) + (None,) * 9
+        return (grad_x, None, None, grad_w) + (None,) * 11
 
 
 class GCNStackFunction(torch.autograd.Function):
@@ -368,7 +467,10 @@ class GCNConv(torch.nn.Module):
     """
 
     def __init__(self, in_channels, out_channels, layer_num, activation: Optional[str] = None,
-                 seed: Optional[int] = None, device=None, **kwargs):
+                 seed: Optional[int] = None, device=None, order: str = "aggregate_first", **kwargs):
+        """``order``: ``"aggregate_first"`` computes ``(A.H).W`` as the reference does;
+        ``"combine_first"`` computes ``A.(H.W)`` (not for layer 0); ``"auto"`` picks
+        combine-first when the padded output width is below the local input width."""
         super().__init__()
         self.layer_num = layer_num
         self.activation = activation
@@ -400,13 +502,28 @@ class GCNConv(torch.nn.Module):
         self.out_channels = padded_channels(out_channels, self.outer_group_size, 1, align)
         self.local_in_channels = self.in_channels // self.inner_group_size
         self.local_out_channels = self.out_channels // self.outer_group_size
+        if order == "auto":
+            order = (
+                "combine_first"
+                if layer_num > 0 and self.out_channels < self.local_in_channels
+                else "aggregate_first"
+            )
+        if order not in ("aggregate_first", "combine_first"):
+            raise ValueError("order must be 'aggregate_first', 'combine_first' or 'auto'")
+        if order == "combine_first" and layer_num == 0:
+            raise ValueError("combine_first is not available for layer 0 (depth-sharded input)")
+        self.combine_first = order == "combine_first"
+        # how the weight columns are split: over the outer axis, or not at all (combine-first)
+        self.w_col_parts = 1 if self.combine_first else self.outer_group_size
+        self.w_col_rank = 0 if self.combine_first else self.outer_rank
+        self.local_weight_cols = self.out_channels // self.w_col_parts
 
         full = init_full_weight(in_channels, out_channels, layer_num, seed)
         block = shard_2d(
             torch.nn.functional.pad(
                 full, (0, self.out_channels - out_channels, 0, self.in_channels - in_channels)
             ),
-            self.inner_group_size, self.inner_rank, self.outer_group_size, self.outer_rank,
+            self.inner_group_size, self.inner_rank, self.w_col_parts, self.w_col_rank,
         )
         flat = block.contiguous().reshape(-1)
         if self.gather_weights:
@@ -421,13 +538,15 @@ class GCNConv(torch.nn.Module):
         return LayerSpec(
             layer_num=self.layer_num,
             local_features_shape=(edge_index.shape[1], self.local_in_channels),
-            local_weight_shape=(self.local_in_channels, self.local_out_channels),
+            local_weight_shape=(self.local_in_channels, self.local_weight_cols),
             depth_group=self.depth_group,
             outer_group=self.outer_group,
             inner_group=self.inner_group,
             gather_features=self.gather_features,
             gather_weights=self.gather_weights,
             relu=(self.activation == "relu") if relu is None else relu,
+            combine_first=self.combine_first,
+            local_out_channels=self.local_out_channels,
         )
 
     # the adjacency and the input features are expected to be sharded already
@@ -439,6 +558,7 @@ class GCNConv(torch.nn.Module):
             s.local_features_shape, s.local_weight_shape,
             s.depth_group, s.outer_group, s.inner_group,
             s.gather_features, s.gather_weights, s.layer_num, s.relu,
+            s.combine_first, s.local_out_channels,
         )
 
     def full_weight_block(self) -> torch.Tensor:
@@ -446,4 +566,4 @@ class GCNConv(torch.nn.Module):
         w = self.weight.detach()
         if self.gather_weights:
             w = coll.all_gather(w, dim=0, process_group=self.depth_group)
-        return w.reshape(self.local_in_channels, self.local_out_channels)
+        return w.reshape(self.local_in_channels, self.local_weight_cols)

@@ -18,14 +18,17 @@ from .gcn_conv import GCNConv, GCNStackFunction, init_full_weight
 
 class Net(torch.nn.Module):
     def __init__(self, num_gcn_layers, input_size, hidden_size, output_size, fuse_layers: bool = True,
-                 seed: Optional[int] = None):
+                 seed: Optional[int] = None, order: str = "auto"):
+        """``order``: per-layer multiplication order, see :class:`GCNConv` (``"auto"`` aggregates
+        after the transform wherever that makes the sparse product narrower)."""
         super().__init__()
         self.num_gcn_layers = num_gcn_layers
         self.fuse_layers = fuse_layers
         dims = [input_size] + [hidden_size] * (num_gcn_layers - 1) + [output_size]
         self.dims = dims
         self.layers = torch.nn.ModuleList(
-            GCNConv(dims[i], dims[i + 1], i, seed=seed) for i in range(num_gcn_layers)
+            GCNConv(dims[i], dims[i + 1], i, seed=seed, order=order if i > 0 else "aggregate_first")
+            for i in range(num_gcn_layers)
         )
 
     def forward(self, x, edge_index_shards):

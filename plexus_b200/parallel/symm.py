@@ -65,12 +65,17 @@ class AxisComm:
         dist.barrier(group=self.group)
 
     def release(self) -> None:
+        """Unmap the peers' buffers, then (after everybody did) free the local one."""
         if not self.ptrs:
             return
         C = _ext.load()
         for q, ptr in enumerate(self.ptrs):
             if q != self.rank:
                 C.symm_close(ptr)
+        try:
+            dist.barrier(group=self.group)  # no importer may still map a buffer that gets freed
+        except Exception:
+            pass
         C.symm_free(self.local_ptr)
         self.ptrs, self.local_ptr, self.slot_bytes = [], 0, 0
 

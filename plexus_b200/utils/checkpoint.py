@@ -127,14 +127,14 @@ def _gather_objects(obj):
 
 def _weight_piece(layer, flat: torch.Tensor):
     return {
-        "inner": layer.inner_rank, "outer": layer.outer_rank, "depth": layer.depth_rank,
+        "inner": layer.inner_rank, "outer": layer.w_col_rank, "depth": layer.depth_rank,
         "sharded": layer.gather_weights, "flat": flat.detach().float().cpu(),
     }
 
 
 def _assemble_weight(layer, pieces) -> torch.Tensor:
     """Full unpadded ``[in, out]`` matrix from every rank's flat piece."""
-    li, lo = layer.local_in_channels, layer.local_out_channels
+    li, lo = layer.local_in_channels, layer.local_weight_cols
     full = torch.zeros(layer.in_channels, layer.out_channels)
     d = layer.depth_group_size if layer.gather_weights else 1
     n = li * lo // d
@@ -155,7 +155,7 @@ def _cut_weight(layer, full: torch.Tensor) -> torch.Tensor:
     padded = torch.nn.functional.pad(
         full, (0, layer.out_channels - full.shape[1], 0, layer.in_channels - full.shape[0])
     )
-    blk = shard_2d(padded, layer.inner_group_size, layer.inner_rank, layer.outer_group_size, layer.outer_rank)
+    blk = shard_2d(padded, layer.inner_group_size, layer.inner_rank, layer.w_col_parts, layer.w_col_rank)
     flat = blk.contiguous().reshape(-1)
     if layer.gather_weights:
         flat = depth_slice(flat, layer.depth_group_size, layer.depth_rank)

@@ -23,7 +23,7 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
     data, nc = small_processed_graph(n=n, e=4 * n, f=f, c=c, seed=5, double_perm=double_perm)
     loader = DataLoader(None, num_layers, data=(data, nc), dtype=torch.float64)
     adj, feats, labels, N, F, C = loader.load()
-    model = Net(num_layers, F, hidden, C, fuse_layers=fuse, seed=11).double()
+    model = Net(num_layers, F, hidden, C, fuse_layers=fuse, seed=11, order=flags.get("order", "auto")).double()
     out = model(feats, adj)
     loss = parallel_cross_entropy(out, labels, num_layers, N, C)
     loss.backward()
@@ -56,6 +56,17 @@ def test_eight_ranks(grid):
 @pytest.mark.parametrize("num_layers", [1, 2, 4])
 def test_layer_counts_cover_rotation(num_layers):
     run_distributed(_worker, 4, (2, 1, 2), num_layers, True, 50, 6, 4, 8, True, {})
+
+
+@pytest.mark.parametrize("grid", [(2, 2, 1), (1, 2, 2), (2, 1, 2), (4, 1, 1)])
+@pytest.mark.parametrize("order", ["combine_first", "aggregate_first"])
+def test_layer_order(grid, order):
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, 3, True, 57, 10, 5, 16, True, {"order": order})
+
+
+def test_combine_first_eight_ranks_four_layers():
+    run_distributed(_worker, 8, (2, 2, 2), 4, True, 53, 9, 7, 16, True, {"order": "combine_first"})
 
 
 def test_single_permutation_and_unfused_layers():
