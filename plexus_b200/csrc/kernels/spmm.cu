@@ -28,19 +28,35 @@ namespace plx {
 constexpr int SPMM_WARPS = 8;
 constexpr int PIECE = 256;  // rows longer than this are cut in pieces of this many nonzeros
 
+// Packed fp32x2 arithmetic (sm_100): one instruction updates two accumulators, which halves
+// the issue slots the multiply-adds take.  The SpMM inner loop is issue bound, not DRAM bound.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long pack2u(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long long x, unsigned long long a) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(a));
+}
+
 template <typename T>
 struct Vec16;  // 16-byte vector of T
 template <>
 struct Vec16<__nv_bfloat16> {
   static constexpr int N = 8;
-  __device__ static void fma(float (&acc)[8], const uint4& v, float a) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+  // acc2[i] holds columns (2i, 2i+1); a bf16 pair widens to fp32x2 with one shift and one mask
+  __device__ static void fma2(unsigned long long (&acc2)[4], const uint4& v, unsigned long long a2) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __bfloat1622float2(p[i]);
-      acc[2 * i] = fmaf(a, f.x, acc[2 * i]);
-      acc[2 * i + 1] = fmaf(a, f.y, acc[2 * i + 1]);
-    }
+    for (int i = 0; i < 4; ++i) ffma2(acc2[i], pack2u(w[i] << 16, w[i] & 0xffff0000u), a2);
   }
   __device__ static uint4 pack(const float (&acc)[8]) {
     uint4 o;
@@ -62,10 +78,9 @@ struct Vec16<__nv_bfloat16> {
 template <>
 struct Vec16<float> {
   static constexpr int N = 4;
-  __device__ static void fma(float (&acc)[4], const uint4& v, float a) {
-    const float* p = reinterpret_cast<const float*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = fmaf(a, p[i], acc[i]);
+  __device__ static void fma2(unsigned long long (&acc2)[2], const uint4& v, unsigned long long a2) {
+    ffma2(acc2[0], pack2u(v.x, v.y), a2);
+    ffma2(acc2[1], pack2u(v.z, v.w), a2);
   }
   __device__ static uint4 pack(const float (&acc)[4]) {
     uint4 o;
@@ -99,8 +114,17 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
   constexpr int U = VPL == 1 ? 4 : 2;
   const int g = lane / LPR, li = lane % LPR;
   bool active[VPL];
+  const T* hbase[VPL];  // this lane's column offset folded into the base pointer
 #pragma unroll
-  for (int v = 0; v < VPL; ++v) active[v] = (v * LPR + li) * VN < D;
+  for (int v = 0; v < VPL; ++v) {
+    active[v] = (v * LPR + li) * VN < D;
+    hbase[v] = H + (v * LPR + li) * VN;
+  }
+  unsigned long long acc2[VPL][VN / 2];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+#pragma unroll
+    for (int i = 0; i < VN / 2; ++i) acc2[v][i] = 0ull;
 
   for (int64_t base = beg; base < end; base += 32) {
     const int cnt = (end - base) < 32 ? static_cast<int>(end - base) : 32;
@@ -110,30 +134,40 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
       c = __ldg(col + base + lane);
       a = __ldg(val + base + lane);
     }
+    // lanes beyond cnt repeat the batch's last column with weight 0: their products vanish
+    // (and cannot introduce a NaN the row would not have anyway), so the loop below needs no
+    // per-nonzero predicate
+    {
+      const int c_last = __shfl_sync(0xffffffffu, c, cnt - 1);
+      if (lane >= cnt) c = c_last;
+    }
     for (int jj = 0; jj < cnt; jj += U * G) {  // trip count is uniform across the warp
       int cj[U];
-      float aj[U];
-      bool pj[U];
+      unsigned long long aj[U];
       uint4 vj[U][VPL];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int j = jj + u * G + g;
-        cj[u] = __shfl_sync(0xffffffffu, c, j & 31);
-        aj[u] = __shfl_sync(0xffffffffu, a, j & 31);
-        pj[u] = j < cnt;
+        const int j = (jj + u * G + g) & 31;
+        cj[u] = __shfl_sync(0xffffffffu, c, j);
+        const float av = __shfl_sync(0xffffffffu, a, j);
+        aj[u] = pack2(av, av);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int v = 0; v < VPL; ++v)
-          if (pj[u] && active[v]) vj[u][v] = ldg16(H + cj[u] * ldh + (v * LPR + li) * VN);
+          if (active[v]) vj[u][v] = ldg16(hbase[v] + cj[u] * ldh);
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int v = 0; v < VPL; ++v)
-          if (pj[u] && active[v]) Vec16<T>::fma(acc[v], vj[u][v], aj[u]);
+          if (active[v]) Vec16<T>::fma2(acc2[v], vj[u][v], aj[u]);
     }
   }
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+#pragma unroll
+    for (int i = 0; i < VN / 2; ++i) unpack2(acc2[v][i], acc[v][2 * i], acc[v][2 * i + 1]);
   // combine the G groups
 #pragma unroll
   for (int off = LPR; off < 32; off <<= 1) {
