@@ -94,50 +94,75 @@ def barrier_sync():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs.
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    nvidia-smi takes a few hundred ms to start, so the sampler is started before the warm-up
+    epochs; ``mark_begin`` / ``stop`` bracket the timed region and only samples whose time stamp
+    falls inside it are used (with the closest sample as a fallback for very short regions).
+    """
+
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
-        self.index, self.proc = index, None
+        self.index, self.proc, self.t0 = index, None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+
+        try:
+            return datetime.datetime.strptime(text.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def stop(self):
+        t1 = time.time()
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
+                rows.append((self._stamp(f[0]), float(f[1]), float(f[2]), f[5:9]))
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
+        t0 = self.t0 if self.t0 is not None else 0.0
+        inside = [r for r in rows if r[0] is not None and t0 - 0.02 <= r[0] <= t1 + 0.02]
+        if not inside and rows:
+            mid = 0.5 * (t0 + t1)
+            inside = [min(rows, key=lambda r: abs((r[0] or 0.0) - mid))]
+        reasons = set()
+        for r in inside:
+            for name, v in zip(self.NAMES, r[3]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {
-            "sm_mhz": statistics.median(sm) if sm else None,
-            "sm_max_mhz": max(mx) if mx else None,
-            "samples": len(sm),
+            "sm_mhz": statistics.median(r[1] for r in inside) if inside else None,
+            "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+            "samples": len(inside),
             "reasons": sorted(reasons),
         }
 
@@ -214,6 +239,8 @@ def run_ours(args):
         opt.step()
         return loss
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         loss = step(labels)
     opc.check_status()
@@ -221,9 +248,8 @@ def run_ours(args):
         get_timers().get_times()
 
     # ---- device-timed region
-    sampler = ClockSampler(local)
     barrier_sync()
-    sampler.start()
+    sampler.mark_begin()
     launches0 = opc.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -321,11 +347,12 @@ def run_reference(args):
         # passed every epoch (its loss relabels it in place, which does not change the work done)
         return train(model, optimizer, features, adj, lbl, N, C)
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         loss = step(labels)
-    sampler = ClockSampler(local)
     barrier_sync()
-    sampler.start()
+    sampler.mark_begin()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):

@@ -74,7 +74,7 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
               const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
               const Tensor& piece_beg, const Tensor& piece_end, const Tensor& long_rows,
               const Tensor& long_piece_start, const Tensor& scratch,
-              const std::vector<int64_t>& push_ptrs, int64_t push_ld) {
+              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t variant) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -115,7 +115,7 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
   check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
                              val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
                              out.stride(0), mptr, ldm, static_cast<int>(D), static_cast<int>(row_begin),
-                             s, scr, scr_n, push.n ? &push : nullptr, stream()));
+                             s, scr, scr_n, push.n ? &push : nullptr, static_cast<int>(variant), stream()));
 }
 
 int64_t spmm_scratch_per_piece(const Tensor& H) {

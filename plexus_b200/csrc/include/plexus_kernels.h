@@ -41,7 +41,11 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
                             int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
                             float* scratch, int64_t scratch_elems, const PushTargets* push,
-                            cudaStream_t stream);
+                            int variant, cudaStream_t stream);
+// variant: how a row's nonzeros are accumulated.  FMA: packed fp32x2 multiply-adds on CUDA cores
+// (the fastest measured, used by default from Python).  TENSOR: gathered rows are staged in shared
+// memory and summed by warp-level MMAs (bf16 features up to 256 columns; other cases use FMA).
+enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
 
 // ---- gemm_tcgen05.cu
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.

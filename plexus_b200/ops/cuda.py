@@ -61,6 +61,10 @@ def _csr_parts(A):
     return crow, col, val
 
 
+# default accumulation variant of the SpMM kernels: 1 = packed-FMA (fastest measured), 0 = warp-MMA
+# (staged rows + tensor-core sum; correct but measured ~2x slower, kept selectable for tuning)
+SPMM_VARIANT = int(__import__("os").environ.get("PLEXUS_SPMM_VARIANT", "1"))
+
 # per-row constant added to the nonzero count when balancing row blocks, and the cost of a block
 SPMM_ROW_COST = 8
 SPMM_BLOCK_COST = 1024
@@ -137,8 +141,9 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
 
 
 def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None,
-         push_ptrs=(), push_ld=0):
-    """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective)."""
+         push_ptrs=(), push_ld=0, variant=None):
+    """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
+    ``variant``: 1 = packed-FMA accumulation (default), 0 = warp-MMA accumulation."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -152,7 +157,8 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     npieces = sch.piece_beg.numel()
     scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
     C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
-               sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld))
+               sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld),
+               SPMM_VARIANT if variant is None else int(variant))
     _count(sch.launches)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
