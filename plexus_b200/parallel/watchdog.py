@@ -71,8 +71,13 @@ class Heartbeat:
         parts = raw.split(":")
         return int(parts[0]), float(parts[1])
 
-    def check_peers(self, max_age_s: float, min_step: Optional[int] = None) -> None:
-        """Raise :class:`PeerFailure` if a peer exited, is stale, or lags behind ``min_step``."""
+    def check_peers(self, max_age_s: float, min_step: Optional[int] = None,
+                    missing_is_failure: bool = False) -> None:
+        """Raise :class:`PeerFailure` if a peer exited, is stale, or lags behind ``min_step``.
+
+        A peer that has not published anything yet is only a failure if ``missing_is_failure``
+        (ranks reach their first beat at slightly different times).
+        """
         now = time.time()
         gone, stale = [], []
         for r in range(self.world_size):
@@ -80,7 +85,8 @@ class Heartbeat:
                 continue
             got = self.read(r)
             if got is None:
-                stale.append(r)
+                if missing_is_failure:
+                    stale.append(r)
                 continue
             step, ts = got
             if step < 0:

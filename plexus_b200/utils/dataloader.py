@@ -237,6 +237,8 @@ class DataLoader:
                     self.data, self.num_classes = load_processed(os.path.join(self.data_dir, pt[0]))
                 self.num_nodes, self.num_features = int(self.data.x.shape[0]), int(self.data.x.shape[1])
                 self.symmetric = bool(getattr(self.data, "symmetric", False))
+                # a single processed file says by its contents whether it carries both versions
+                self.double_perm = hasattr(self.data, "edge_index_2")
             self._plan()
 
             n_shards = min(6 if self.double_perm else 3, self.num_gcn_layers)

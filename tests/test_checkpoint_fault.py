@@ -1,0 +1,203 @@
+"""Checkpoint/resume (sharded and grid-independent) and host-side failure detection (CPU, gloo)."""
+
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from helpers import ROOT, run_distributed, small_processed_graph
+
+
+def _setup(grid, layers=3, hidden=12, seed=21):
+    import plexus_b200 as plx
+    from plexus_b200.models.net import Net
+    from plexus_b200.optim import FusedAdamW
+    from plexus_b200.utils.dataloader import DataLoader
+
+    plx.init(*grid, device="cpu", dtype=torch.float32, channel_align=1)
+    data, nc = small_processed_graph(n=64, e=300, f=10, c=5, seed=8)
+    adj, feats, labels, N, F, C = DataLoader(None, layers, data=(data, nc), dtype=torch.float32).load()
+    model = Net(layers, F, hidden, C, seed=seed)
+    opt = FusedAdamW(list(model.parameters()) + [feats], lr=1e-2)
+    return plx, model, opt, adj, feats, labels, N, F, C
+
+
+def _step(model, opt, adj, feats, labels, N, C, layers=3):
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+
+    opt.zero_grad(set_to_none=True)
+    loss = parallel_cross_entropy(model(feats, adj), labels, layers, N, C)
+    loss.backward()
+    opt.step()
+    return loss.item()
+
+
+def _sharded_worker(rank, world, grid, ckdir):
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup(grid)
+    for _ in range(2):
+        _step(model, opt, adj, feats, labels, N, C)
+    ck.save_sharded(ckdir, model, opt, feats, epoch=1)
+    want = [_step(model, opt, adj, feats, labels, N, C) for _ in range(2)]
+    plx.shutdown()
+    # fresh model + optimizer, resume
+    plx, model, opt, adj, feats, labels, N, F, C = _setup(grid, seed=99)
+    assert ck.load_sharded(ckdir, model, opt, feats) == 2
+    got = [_step(model, opt, adj, feats, labels, N, C) for _ in range(2)]
+    assert all(abs(a - b) < 1e-6 for a, b in zip(want, got)), (want, got)
+    assert set(model.state_dict().keys()) == {f"layers.{l}.weight" for l in range(3)}
+
+
+def test_sharded_checkpoint_resume(tmp_path):
+    run_distributed(_sharded_worker, 2, (2, 1, 1), str(tmp_path / "ck"))
+    assert (tmp_path / "ck" / "meta.json").exists() and (tmp_path / "ck" / "rank1.pt").exists()
+    assert not [f for f in os.listdir(tmp_path / "ck") if ".tmp" in f]
+
+
+def _save_consolidated_worker(rank, world, grid, path, out):
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup(grid)
+    for _ in range(2):
+        _step(model, opt, adj, feats, labels, N, C)
+    ck.save_consolidated(path, model, opt, feats, N, F, epoch=1)
+    nxt = [_step(model, opt, adj, feats, labels, N, C) for _ in range(2)]
+    if rank == 0:
+        torch.save(nxt, out)
+
+
+def _load_consolidated_worker(rank, world, grid, path, out):
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup(grid, seed=77)
+    assert ck.load_consolidated(path, model, opt, feats) == 2
+    got = [_step(model, opt, adj, feats, labels, N, C) for _ in range(2)]
+    want = torch.load(out)
+    assert all(abs(a - b) < 2e-5 for a, b in zip(want, got)), (want, got)
+
+
+def test_consolidated_checkpoint_resumes_on_a_different_grid(tmp_path):
+    path, out = str(tmp_path / "full.pt"), str(tmp_path / "next.pt")
+    run_distributed(_save_consolidated_worker, 2, (2, 1, 1), path, out)
+    run_distributed(_load_consolidated_worker, 4, (1, 2, 2), path, out)
+    run_distributed(_load_consolidated_worker, 1, (1, 1, 1), path, out)
+
+
+def test_truncated_or_mismatched_checkpoint_is_rejected(tmp_path):
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup((1, 1, 1))
+    _step(model, opt, adj, feats, labels, N, C)
+    d = str(tmp_path / "ck")
+    ck.save_sharded(d, model, opt, feats, epoch=0)
+    blob = open(os.path.join(d, "rank0.pt"), "rb").read()
+    open(os.path.join(d, "rank0.pt"), "wb").write(blob[: len(blob) // 2])  # crash mid-write of a later save
+    with pytest.raises(ck.CheckpointError, match="cannot read"):
+        ck.load_sharded(d, model, opt, feats)
+    os.remove(os.path.join(d, "meta.json"))
+    with pytest.raises(ck.CheckpointError, match="meta.json missing"):
+        ck.load_sharded(d, model, opt, feats)
+    ck.save_sharded(d, model, opt, feats, epoch=0)
+    import json
+
+    meta = json.load(open(os.path.join(d, "meta.json")))
+    meta["grid"] = [2, 1, 1]
+    json.dump(meta, open(os.path.join(d, "meta.json"), "w"))
+    with pytest.raises(ck.CheckpointError, match="grid"):
+        ck.load_sharded(d, model, opt, feats)
+
+
+# ------------------------------------------------------------------ failure detection
+def _heartbeat_worker(rank, world, mode):
+    from plexus_b200.parallel.watchdog import Heartbeat, PeerFailure
+
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, rank, world, prefix=f"hb-{mode}")
+    hb.beat(0)
+    hb.wait_for_peers(0, timeout_s=20)
+    dist.barrier()  # everybody has seen step 0 before the failure is injected
+    if mode == "exit":
+        if rank == 1:
+            hb.announce_exit("injected")  # a rank that leaves between steps
+        else:
+            t0 = time.time()
+            with pytest.raises(PeerFailure) as e:
+                while time.time() - t0 < 20:
+                    hb.check_peers(max_age_s=30)
+                    time.sleep(0.05)
+            assert e.value.ranks == [1] and "exit" in str(e.value)
+    elif mode == "stall":
+        if rank == 1:
+            time.sleep(1.5)  # never beats again within the limit
+        else:
+            hb.beat(1)
+            with pytest.raises(PeerFailure) as e:
+                hb.wait_for_peers(1, timeout_s=0.6)
+            assert e.value.ranks == [1]
+            time.sleep(0.5)
+            with pytest.raises(PeerFailure):
+                hb.check_peers(max_age_s=0.3)
+    else:
+        for step in range(1, 4):
+            hb.beat(step)
+            hb.wait_for_peers(step, timeout_s=20)
+            hb.check_peers(max_age_s=30)
+
+
+@pytest.mark.parametrize("mode", ["ok", "exit", "stall"])
+def test_heartbeat_detects_lost_and_stalled_peers(mode):
+    run_distributed(_heartbeat_worker, 2, mode)
+
+
+def test_epoch_watchdog_fires_only_past_the_deadline():
+    from plexus_b200.parallel.watchdog import EpochWatchdog
+
+    fired = []
+    with EpochWatchdog(0.2, on_timeout=fired.append, poll_s=0.02) as wd:
+        wd.begin(0)
+        time.sleep(0.05)
+        wd.end()
+        time.sleep(0.3)
+        assert fired == []
+        wd.begin(7)
+        time.sleep(0.5)
+        assert fired == [7] and wd.fired
+
+
+def test_watchdog_default_action_exits_the_process():
+    code = (
+        "import sys, time; sys.path.insert(0, %r)\n"
+        "from plexus_b200.parallel.watchdog import EpochWatchdog\n"
+        "wd = EpochWatchdog(0.2); wd.begin(3); time.sleep(5); print('survived')\n" % ROOT
+    )
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 43 and "survived" not in r.stdout and "step 3" in r.stdout
+
+
+def test_rank_that_never_joins_ends_in_a_timeout_not_a_hang(tmp_path):
+    """A collective with a missing peer must fail within the process-group timeout."""
+    code = (
+        "import sys, datetime, torch, torch.distributed as dist\n"
+        "dist.init_process_group('gloo', init_method='file://%s', rank=0, world_size=2,\n"
+        "                        timeout=datetime.timedelta(seconds=2))\n" % (tmp_path / "init")
+    )
+    t0 = time.time()
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert r.returncode != 0 and time.time() - t0 < 100
+
+
+def test_device_status_decoding():
+    from plexus_b200.parallel.watchdog import PlexusCommTimeout, decode_status, raise_on_device_status
+
+    ok = torch.zeros(8, dtype=torch.int32)
+    raise_on_device_status(ok)
+    st = torch.tensor([1, 1, 3, 42, 41, 0, 0, 0], dtype=torch.int32)
+    assert "spmm_all_reduce" in decode_status(st.tolist()) and "expected 42, seen 41" in decode_status(st.tolist())
+    with pytest.raises(PlexusCommTimeout):
+        raise_on_device_status(st)
+    assert int(st[0]) == 0  # cleared for the next step

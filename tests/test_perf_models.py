@@ -1,0 +1,96 @@
+"""Cost models: golden values (hand-derived from the closed forms) and structure."""
+
+import math
+
+import pytest
+
+from plexus_b200.perf import chooser, comm_model, comp_model, mem_model
+from plexus_b200.perf.common import split_into_three_powers_of_two
+
+
+def test_split_into_three_powers_of_two():
+    assert split_into_three_powers_of_two(1) == [(1, 1, 1)]
+    s = split_into_three_powers_of_two(8)
+    assert len(s) == 10 and all(x * y * z == 8 for x, y, z in s)
+    assert s[0] == (1, 1, 8) and s[-1] == (8, 1, 1)
+    with pytest.raises(ValueError):
+        split_into_three_powers_of_two(6)
+
+
+def test_comm_model_single_layer_by_hand():
+    # one layer, grid (2,1,1): outer = X = 2, inner = Y = 1, depth = Z = 1, bandwidth-agnostic (v1)
+    N, D, Dn = 1000, 64, 32
+    cost = comm_model.compute_config_costs(2, N, [D, Dn], "v1", "perlmutter")[(2, 1, 1)]
+    elem = 4 / 1024**3
+    agg = 2 * (2 - 1) / 2 * (N * D / 1) * elem  # all-reduce of AGG over outer, forward
+    want = (agg + agg) * 1000  # the same all-reduce of gradAGG in backward; every other term has p = 1
+    assert math.isclose(cost, want, rel_tol=1e-12)
+
+
+def test_comm_model_golden_values():
+    c = comm_model.compute_config_costs(8, 2449029, [100, 128, 128, 47], "v3", "perlmutter")
+    first = list(c.items())[:3]
+    assert first[0][0] == (4, 1, 2) and math.isclose(first[0][1], 69.08277956868172, rel_tol=1e-9)
+    assert first[1][0] == (1, 4, 2) and math.isclose(first[1][1], 70.78599689627646, rel_tol=1e-9)
+    assert list(c.values()) == sorted(c.values())
+    f = comm_model.compute_config_costs(8, 2449029, [100, 128, 128, 47], "v3", "frontier")
+    assert len(f) == 10 and all(v > 0 for v in f.values())
+
+
+def test_get_bw_tables():
+    g = comm_model.get_bw
+    assert g(1, 2, 4, "v1", "perlmutter") == 1
+    assert g(1, 4, 4, "v2", "perlmutter") == 200 and g(2, 4, 4, "v2", "perlmutter") == 50
+    assert g(1, 4, 4, "v3", "perlmutter") == 225 and g(1, 8, 4, "v3", "perlmutter") == 66.59
+    assert g(2, 4, 4, "v3", "perlmutter") == 66.59 / 2 and g(4, 2, 4, "v3", "perlmutter") == 66.59 / 4
+    assert g(1, 8, 8, "v3", "frontier") == 135 and g(2, 4, 8, "v3", "frontier") == 72
+    assert g(4, 2, 8, "v3", "frontier") == 36 and g(8, 2, 8, "v3", "frontier") == 5
+    assert g(3, 2, 8, "v3", "b200_nvl8") == comm_model.B200_PORT_GBS  # placement does not matter
+
+
+def test_b200_comm_model_prefers_balanced_grid_and_uses_bf16():
+    c = comm_model.compute_config_costs(8, 2449029, [100, 256, 256, 47], "v3", "b200_nvl8")
+    assert list(c.keys())[0] == (2, 2, 2)
+    one = comm_model.compute_config_costs(1, 1000, [8, 8], "v3", "b200_nvl8")
+    assert one[(1, 1, 1)] == 0.0
+
+
+def test_comp_model_golden_and_symmetry():
+    c = comp_model.comp_model(2449029, 123718280, 8, [100, 128, 128])
+    k0, v0 = next(iter(c.items()))
+    assert k0 == (2, 2, 2) and math.isclose(v0, 9312969914.570568, rel_tol=1e-9)
+    assert math.isclose(c[(2, 1, 4)], c[(4, 1, 2)], rel_tol=1e-12)
+    # single GPU, one layer: cost = sqrt(F) * (1 + 2 N / D)
+    one = comp_model.comp_model(100, 1000, 1, [10])[(1, 1, 1)]
+    assert math.isclose(one, (1000 * 10) ** 0.5 * (1 + 2 * 100 / 10), rel_tol=1e-12)
+
+
+def test_mem_model_golden_and_by_hand():
+    m = mem_model.compute_config_mem(8, 2449029, 123718280, [100, 128, 128, 47])
+    k0, v0 = next(iter(m.items()))
+    assert k0 == "X2Y2Z2" and math.isclose(v0, 5.828322818502784, rel_tol=1e-9)
+    # one GPU, one layer, by hand (32-bit words)
+    N, E, D0, D1 = 10, 40, 4, 2
+    # the adjacency term counts min(3, len(D_list)) = 2 layer types, as the reference does
+    words = 2 * 2 * (3 * E + 2 * N) + 4 * D0 * D1 + 2 * N * D0 + 2 * N * D1 + 4 * N * D0 + (N * D0 + D0 * D1) + 2 * N
+    got = mem_model.compute_config_mem(1, N, E, [D0, D1])["X1Y1Z1"]
+    assert math.isclose(got, words * 4 / 1024**3, rel_tol=1e-12)
+    b = mem_model.compute_config_mem_b200(8, 2449029, 123718280, [100, 128, 128, 47])
+    assert b["X2Y2Z2"] < m["X2Y2Z2"]
+
+
+def test_chooser_returns_valid_grids_and_respects_memory():
+    grids = chooser.choose_grid(8, 2449029, 123718280, [100, 256, 256, 47])
+    assert len(grids) == 10 and all(x * y * z == 8 for x, y, z in grids)
+    assert chooser.choose_grid(1, 1000, 5000, [8, 8]) == [(1, 1, 1)]
+    tiny = chooser.choose_grid(8, 10**9, 5 * 10**10, [128, 128, 128, 64], mem_limit_gb=1.0)
+    assert tiny == [(8, 1, 1)]  # nothing fits: documented fall-back
+
+
+def test_facade_modules_reexport_the_models():
+    import performance.comm_model as pc
+    import performance.comp_model as pp
+    import performance.mem_model as pm
+
+    assert pc.compute_config_costs is comm_model.compute_config_costs
+    assert pp.comp_model is comp_model.comp_model and pm.compute_config_mem is mem_model.compute_config_mem

@@ -1,0 +1,66 @@
+"""The training application end to end on CPU ranks (the 2-layer / 16,384-node plumbing config)."""
+
+import json
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+from helpers import ROOT
+
+
+def _run(args, nproc, tmp_path, port):
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "examples", "train.py"),
+           "--backend", "gloo"] + args
+    if nproc == 1:
+        cmd = [sys.executable, os.path.join(ROOT, "examples", "train.py"), "--backend", "gloo"] + args
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def _losses(out):
+    return [float(m) for m in re.findall(r"Epoch: \d+, Train Loss: ([0-9.]+)", out)]
+
+
+def test_two_rank_grid_matches_serial_run_and_logs_parse(tmp_path):
+    # 2-layer GCN, fp32, R-MAT 16,384 nodes / ~262K undirected edges, 128 features, hidden 128,
+    # 16 classes, Adam lr 0.01, 10 epochs; grid 2x1x1 over gloo versus one process
+    common = ["--synthetic", "16384,262144,128,16", "--num_gcn_layers", "2", "--hidden_size", "128",
+              "--lr", "0.01", "--num_epochs", "10", "--dtype", "fp32", "--seed", "1"]
+    serial = _run(common, 1, tmp_path, 29611)
+    metrics = tmp_path / "m.jsonl"
+    par = _run(common + ["--G_intra_r", "2", "--metrics_file", str(metrics), "--eval"], 2, tmp_path, 29612)
+    ls, lp = _losses(serial), _losses(par)
+    assert len(ls) == len(lp) == 10
+    assert all(abs(a - b) <= 2e-4 for a, b in zip(ls, lp)), (ls, lp)
+    assert lp[-1] < lp[0]
+    # the timer tree of the run parses with the reference-compatible log parser
+    sys.path.insert(0, ROOT)
+    from plexus_b200.utils.parse_results import process_log_file
+
+    log = tmp_path / "par.log"
+    log.write_text(par)
+    epoch_ms, comm_ms = process_log_file(str(log), 2)
+    assert epoch_ms > 0 and 0 < comm_ms < epoch_ms
+    recs = [json.loads(l) for l in metrics.read_text().splitlines()]
+    assert recs[0]["event"] == "start" and recs[0]["grid"] == [2, 1, 1]
+    assert recs[-1]["event"] == "epoch" and 0.0 <= recs[-1]["acc_train"] <= 1.0
+
+
+def test_resume_from_checkpoint_and_auto_grid(tmp_path):
+    base = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
+            "--dtype", "fp32", "--checkpoint_dir", str(tmp_path / "ck")]
+    full = _losses(_run(base + ["--num_epochs", "4"], 1, tmp_path, 29613))
+    os.system(f"rm -rf {tmp_path / 'ck'}")
+    first = _losses(_run(base + ["--num_epochs", "2", "--checkpoint_every", "2"], 1, tmp_path, 29614))
+    rest = _losses(_run(base + ["--num_epochs", "4", "--resume"], 1, tmp_path, 29615))
+    assert len(first) == 2 and len(rest) == 2
+    assert all(abs(a - b) < 1e-4 for a, b in zip(full, first + rest)), (full, first, rest)
+    out = _run(["--synthetic", "600,4000,12,4", "--grid", "auto", "--num_epochs", "1", "--dtype", "fp32"], 2,
+               tmp_path, 29616)
+    assert "cost models chose grid" in out
