@@ -123,8 +123,8 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 }
 
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
-             int64_t max_stages, int64_t ctas_limit, const std::vector<int64_t>& push_ptrs,
-             int64_t push_ld) {
+             int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
+             const std::vector<int64_t>& push_ptrs, int64_t push_ld) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
@@ -136,7 +136,8 @@ void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tenso
   check(plx::launch_gemm_nt(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(),
                             C.stride(0), dtype_of(C), A.size(0), B.size(0), A.size(1), relu,
                             status_ptr(status), static_cast<int>(max_stages),
-                            static_cast<int>(ctas_limit), push.n ? &push : nullptr, stream()));
+                            static_cast<int>(ctas_limit), static_cast<int>(nb_override),
+                            push.n ? &push : nullptr, stream()));
 }
 
 int64_t gemm_tn_parts(int64_t R) { return plx::gemm_tn_parts(R); }
@@ -349,6 +350,66 @@ int64_t symm_open(const std::string& handle) {
 void symm_close(int64_t ptr) { check(plx::symm_close(reinterpret_cast<void*>(ptr))); }
 void symm_free(int64_t ptr) { check(plx::symm_free(reinterpret_cast<void*>(ptr))); }
 
+// ---- start-up kernels ---------------------------------------------------------------------
+std::tuple<Tensor, Tensor> rmat_edges(int64_t num_nodes, int64_t first_edge, int64_t n, int64_t seed,
+                                      double a, double b, double c, const Tensor& like) {
+  TORCH_CHECK(like.is_cuda());
+  c10::cuda::CUDAGuard guard(like.device());
+  auto opts = torch::TensorOptions().dtype(at::kLong).device(like.device());
+  Tensor row = torch::empty({n}, opts), col = torch::empty({n}, opts);
+  check(plx::launch_rmat_edges(num_nodes, first_edge, n, static_cast<uint64_t>(seed), a, b, c,
+                               row.data_ptr<int64_t>(), col.data_ptr<int64_t>(), stream()));
+  return {row, col};
+}
+
+Tensor gcn_norm(const Tensor& edge_index, const c10::optional<Tensor>& weight, int64_t num_nodes) {
+  TORCH_CHECK(edge_index.is_cuda() && edge_index.scalar_type() == at::kLong && edge_index.dim() == 2 &&
+              edge_index.size(0) == 2 && edge_index.is_contiguous());
+  const int64_t nnz = edge_index.size(1);
+  const float* w = nullptr;
+  if (weight.has_value() && weight->defined()) {
+    TORCH_CHECK(weight->scalar_type() == at::kFloat && weight->is_contiguous() && weight->numel() == nnz);
+    w = weight->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(edge_index.device());
+  auto opts = torch::TensorOptions().dtype(at::kFloat).device(edge_index.device());
+  Tensor deg = torch::zeros({num_nodes}, opts), out = torch::empty({nnz}, opts);
+  check(plx::launch_gcn_norm(edge_index.data_ptr<int64_t>(), edge_index.data_ptr<int64_t>() + nnz, w, nnz,
+                             deg.data_ptr<float>(), out.data_ptr<float>(), stream()));
+  return out;
+}
+
+std::tuple<Tensor, Tensor, Tensor> coo_to_csr(const Tensor& row, const Tensor& col, const Tensor& val,
+                                              int64_t nrows, int64_t ncols) {
+  TORCH_CHECK(row.is_cuda() && row.scalar_type() == at::kLong && col.scalar_type() == at::kLong &&
+              val.scalar_type() == at::kFloat && row.is_contiguous() && col.is_contiguous() &&
+              val.is_contiguous() && row.numel() == col.numel() && row.numel() == val.numel());
+  const int64_t nnz = row.numel();
+  c10::cuda::CUDAGuard guard(row.device());
+  auto iopts = torch::TensorOptions().dtype(at::kInt).device(row.device());
+  Tensor crow = torch::zeros({nrows + 1}, iopts), col_out = torch::empty({nnz}, iopts);
+  Tensor val_out = torch::empty({nnz}, val.options());
+  const size_t tb = plx::coo_to_csr_temp_bytes(nnz, nrows);
+  Tensor temp = torch::empty({static_cast<int64_t>(tb)}, torch::TensorOptions().dtype(at::kByte).device(row.device()));
+  check(plx::launch_coo_to_csr(row.data_ptr<int64_t>(), col.data_ptr<int64_t>(), val.data_ptr<float>(), nnz,
+                               nrows, ncols, crow.data_ptr<int>(), col_out.data_ptr<int>(),
+                               val_out.data_ptr<float>(), temp.data_ptr(), tb, stream()));
+  return {crow, col_out, val_out};
+}
+
+Tensor relu_dropout(const Tensor& x, const c10::optional<Tensor>& grad, double p, int64_t seed,
+                    int64_t index_offset) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous());
+  const bool bwd = grad.has_value() && grad->defined();
+  if (bwd) TORCH_CHECK(grad->is_contiguous() && grad->scalar_type() == x.scalar_type() && grad->numel() == x.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  check(plx::launch_relu_dropout(dtype_of(x), bwd, x.data_ptr(), bwd ? grad->data_ptr() : nullptr,
+                                 out.data_ptr(), x.numel(), p, static_cast<uint64_t>(seed), index_offset,
+                                 stream()));
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -365,6 +426,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relu_bwd", &relu_bwd);
   m.def("prep_weight", &prep_weight);
   m.def("wait_flag", &wait_flag);
+  m.def("rmat_edges", &rmat_edges);
+  m.def("gcn_norm", &gcn_norm);
+  m.def("coo_to_csr", &coo_to_csr);
+  m.def("relu_dropout", &relu_dropout);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_slots_f32", &reduce_slots_f32);
   m.def("push_copy", &push_copy);

@@ -51,8 +51,8 @@ enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
-                           int* status, int max_stages, int ctas_limit, const PushTargets* push,
-                           cudaStream_t stream);
+                           int* status, int max_stages, int ctas_limit, int nb_override,
+                           const PushTargets* push, cudaStream_t stream);
 // out[Mw,Nw] fp32 = A[R,Mw]^T . B[R,Nw]; scratch >= gemm_tn_parts(R)*Mw*Nw floats.
 int gemm_tn_parts(int64_t R);
 const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ldb, float* out,
@@ -129,6 +129,18 @@ const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 const char* symm_open(const unsigned char* handle64, void** ptr);
 const char* symm_close(void* ptr);
 const char* symm_free(void* ptr);
+
+// ---- graph_prep.cu (start-up kernels)
+const char* launch_rmat_edges(int64_t num_nodes, int64_t first_edge, int64_t n, uint64_t seed, double a,
+                              double b, double c, int64_t* row, int64_t* col, cudaStream_t stream);
+const char* launch_gcn_norm(const int64_t* row, const int64_t* col, const float* w, int64_t nnz, float* deg,
+                            float* out, cudaStream_t stream);
+size_t coo_to_csr_temp_bytes(int64_t nnz, int64_t nrows);
+const char* launch_coo_to_csr(const int64_t* row, const int64_t* col, const float* val, int64_t nnz,
+                              int64_t nrows, int64_t ncols, int* crow, int* col_out, float* val_out,
+                              void* temp, size_t temp_bytes, cudaStream_t stream);
+const char* launch_relu_dropout(int dtype, bool backward, const void* x, const void* g, void* out, int64_t n,
+                                double p, uint64_t seed, int64_t index_offset, cudaStream_t stream);
 
 inline const char* last_launch_error() {
   cudaError_t e = cudaGetLastError();

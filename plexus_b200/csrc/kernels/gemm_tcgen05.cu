@@ -90,7 +90,7 @@ __device__ __forceinline__ void stage16<float>(uint8_t* dst, const uint32_t (&r)
 }
 
 // ---------------------------------------------------------------------------------------
-// C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = 256-column block)
+// C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = block of bn_box columns)
 // ---------------------------------------------------------------------------------------
 template <typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -103,8 +103,8 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (K + BK - 1) / BK;
-  const int n0 = blockIdx.y * 256;
-  const int n_valid = min(256, N - n0);
+  const int n0 = blockIdx.y * bn_box;
+  const int n_valid = min(bn_box, N - n0);
   const int bn = (n_valid + 15) & ~15;  // UMMA N
   const int b_blk_bytes = bn_box * 128;
   const int num_tiles = (M + BM - 1) / BM;
@@ -497,11 +497,11 @@ static int num_sms() {
   return n;
 }
 
-// max_stages / ctas_limit select the launch variant (0 = default).
+// max_stages / ctas_limit / nb_override (column-block width) select the launch variant (0 = default).
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
-                           int* status, int max_stages, int ctas_limit, const PushTargets* push_in,
-                           cudaStream_t stream) {
+                           int* status, int max_stages, int ctas_limit, int nb_override,
+                           const PushTargets* push_in, cudaStream_t stream) {
   PushTargets push;
   push.n = 0;
   if (push_in != nullptr) {
@@ -515,17 +515,23 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   if (reinterpret_cast<uintptr_t>(C) % 16) return "gemm_nt: C must be 16-byte aligned";
   if (M == 0 || N == 0) return nullptr;
   const int KB = static_cast<int>((K + BK - 1) / BK);
-  const int bn_box = static_cast<int>(std::min<int64_t>(256, (N + 15) / 16 * 16));
-  const int b_blk = bn_box * 128;
   const int bar_bytes = sizeof(GemmBarriers) + 16 + STAGING_BYTES + 1024;  // + staging + alignment slack
-  int b_resident = 1, stages = 0;
-  {
+  // Column block: as wide as possible (A is read once per column block), but narrow enough that
+  // W stays resident AND the TMA ring for A keeps at least 6 stages (~100 KB) in flight per SM,
+  // which is what a bandwidth-bound stream needs.  Two CTAs then share an A tile through L2.
+  int bn_box = static_cast<int>(std::min<int64_t>(256, (N + 15) / 16 * 16));
+  if (nb_override > 0) bn_box = std::min(bn_box, std::max(16, (nb_override + 15) / 16 * 16));
+  int b_resident = 1, stages = 0, b_blk = 0;
+  for (;;) {
+    b_blk = bn_box * 128;
     int64_t left = SMEM_LIMIT - bar_bytes - static_cast<int64_t>(KB) * b_blk;
     stages = left > 0 ? static_cast<int>(left / A_STAGE_BYTES) : 0;
-    if (stages < 3) {
-      b_resident = 0;
-      stages = (SMEM_LIMIT - bar_bytes) / (A_STAGE_BYTES + b_blk);
-    }
+    if (stages >= 6 || bn_box <= 128 || nb_override > 0) break;
+    bn_box = 128;
+  }
+  if (stages < 3) {
+    b_resident = 0;
+    stages = (SMEM_LIMIT - bar_bytes) / (A_STAGE_BYTES + b_blk);
   }
   stages = std::min(stages, 8);
   if (max_stages > 0) stages = std::min(stages, std::max(2, max_stages));
@@ -538,8 +544,9 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   if (const char* e = make_tmap_bf16(&tmA, A, M, K, lda, BM)) return e;
   if (const char* e = make_tmap_bf16(&tmB, B, N, K, ldb, bn_box)) return e;
   const int tiles = static_cast<int>((M + BM - 1) / BM);
-  const int ctas = std::min(tiles, ctas_limit > 0 ? ctas_limit : num_sms());
-  dim3 grid(ctas, static_cast<unsigned>((N + 255) / 256));
+  const int n_blocks = static_cast<int>((N + bn_box - 1) / bn_box);
+  const int ctas = std::min(tiles, ctas_limit > 0 ? ctas_limit : std::max(1, num_sms() / n_blocks));
+  dim3 grid(ctas, static_cast<unsigned>(n_blocks));
   if (c_dtype == DT_BF16) {
     auto kern = gemm_nt_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

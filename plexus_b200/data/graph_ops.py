@@ -49,6 +49,12 @@ def gcn_normalize(edge_index: torch.Tensor, num_nodes: int, edge_weight: Optiona
 
     ``edge_index`` must already contain the self loops.
     """
+    if edge_index.is_cuda and edge_index.dtype == torch.int64 and edge_index.is_contiguous():
+        from ..ops import _ext
+
+        if _ext.available():
+            w = None if edge_weight is None else edge_weight.float().contiguous()
+            return _ext.load().gcn_norm(edge_index, w, num_nodes)
     if edge_weight is None:
         edge_weight = torch.ones(edge_index.shape[1], dtype=torch.float32, device=edge_index.device)
     deg = torch.zeros(num_nodes, dtype=torch.float32, device=edge_index.device)
@@ -92,6 +98,14 @@ def coo_to_csr(
     assume_sorted: bool = False,
 ):
     """``(crow, col, val)`` with columns ascending inside each row."""
+    if (row.is_cuda and index_dtype == torch.int32 and val.dtype == torch.float32
+            and 0 < row.numel() < 2**31 - 1 and not assume_sorted):
+        from ..ops import _ext
+
+        if _ext.available():
+            # one radix sort of (row * ncols + col) keys, histogram and scan in the extension
+            return _ext.load().coo_to_csr(row.to(torch.int64).contiguous(), col.to(torch.int64).contiguous(),
+                                          val.contiguous(), num_rows, num_cols)
     if not assume_sorted and row.numel():
         order = torch.argsort(row.to(torch.int64) * num_cols + col.to(torch.int64))
         row, col, val = row[order], col[order], val[order]

@@ -12,8 +12,9 @@ import torch
 
 from . import _ext
 
-# (max_stages, ctas_limit) launch shapes of the tcgen05 GEMM tried by the tuner; 0 = default
-GEMM_VARIANTS = [(0, 0), (4, 0), (3, 0), (2, 0), (0, 74), (0, 296)]
+# (max_stages, ctas_limit, column-block width) launch shapes of the tcgen05 GEMM tried by the tuner;
+# 0 = default
+GEMM_VARIANTS = [(0, 0, 0), (0, 0, 256), (0, 0, 128), (0, 0, 64), (4, 0, 0), (0, 74, 0)]
 
 # number of kernels of this package launched so far (counted where they are launched)
 launch_count = 0
@@ -182,7 +183,7 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
          push_ptrs=(), push_ld=0):
     C = _ext.load()
     st = status_buffer(a.device)
-    max_stages, ctas = GEMM_VARIANTS[variant]
+    max_stages, ctas, nb = GEMM_VARIANTS[variant]
     if trans_a and not trans_b:
         # out[Mw, Nw] = a[R, Mw]^T . b[R, Nw]   (fp32 result)
         a, b = _bf16(a), _bf16(b)
@@ -213,7 +214,7 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         C.prep_weight(b.contiguous(), None, bt)
         _count(1)
     out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
-    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, list(push_ptrs), int(push_ld))
+    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld))
     _count(1)
     return out
 

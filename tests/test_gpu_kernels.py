@@ -225,3 +225,50 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     flag.fill_(1)
     _ext.load().wait_flag(flag, 1, 2000, status)
     raise_on_device_status(status)
+
+
+def test_startup_kernels_match_the_torch_versions():
+    from plexus_b200.data import graph_ops, synthetic
+
+    dev = _dev()
+    # R-MAT stream: device kernel == torch integer arithmetic on the CPU
+    r_gpu, c_gpu = synthetic.rmat_edges(100000, 12345, 50000, seed=9, device=dev)
+    r_cpu, c_cpu = synthetic.rmat_edges(100000, 12345, 50000, seed=9, device="cpu")
+    assert torch.equal(r_gpu.cpu(), r_cpu) and torch.equal(c_gpu.cpu(), c_cpu)
+    # whole synthetic graph identical on both devices
+    d_gpu, _ = synthetic.synthetic_graph(3000, 20000, 8, 4, seed=2, device=dev)
+    d_cpu, _ = synthetic.synthetic_graph(3000, 20000, 8, 4, seed=2, device="cpu")
+    assert torch.equal(d_gpu.edge_index.cpu(), d_cpu.edge_index)
+    assert torch.allclose(d_gpu.edge_weight.cpu(), d_cpu.edge_weight, rtol=1e-5)
+    assert torch.allclose(d_gpu.x.cpu(), d_cpu.x, atol=1e-5) and torch.equal(d_gpu.y.cpu(), d_cpu.y)
+    # COO -> CSR with shuffled input
+    g = torch.Generator().manual_seed(0)
+    rows, cols = 500, 700
+    key = torch.unique(torch.randint(0, rows * cols, (6000,), generator=g))
+    key = key[torch.randperm(key.numel(), generator=g)]
+    row, col, val = key // cols, key % cols, torch.rand(key.numel(), generator=g)
+    want = graph_ops.coo_to_csr(row, col, val, rows, cols)
+    got = graph_ops.coo_to_csr(row.to(dev), col.to(dev), val.to(dev), rows, cols)
+    for a, b in zip(got, want):
+        assert a.dtype == b.dtype and torch.equal(a.cpu(), b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_relu_dropout_same_mask_on_cpu_and_gpu(dtype):
+    from plexus_b200.ops.dropout import relu_dropout
+
+    torch.manual_seed(0)
+    x = torch.randn(1000, 24).to(dtype)
+    g = torch.randn(1000, 24).to(dtype)
+    outs = []
+    for dev in ("cpu", _dev()):
+        xi = x.to(dev).requires_grad_()
+        y = relu_dropout(xi, p=0.3, seed=5, index_offset=77)
+        y.backward(g.to(dev))
+        outs.append((y.detach().float().cpu(), xi.grad.float().cpu()))
+    assert torch.allclose(outs[0][0], outs[1][0], rtol=1e-2, atol=1e-3)
+    assert torch.allclose(outs[0][1], outs[1][1], rtol=1e-2, atol=1e-3)
+    kept = (outs[1][0] != 0).float().sum() / (x > 0).float().sum()
+    assert 0.6 < kept < 0.8
+    y0 = relu_dropout(x.to(_dev()), p=0.0)
+    assert torch.equal(y0.cpu(), torch.relu(x))
