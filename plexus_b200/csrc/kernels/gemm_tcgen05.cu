@@ -55,11 +55,10 @@ constexpr int STAGING_BYTES = 4 * 32 * STAGE_PITCH;
 
 // Convert 16 accumulator columns (fp32 bits) and store them at `dst` in shared memory.
 template <typename OutT>
-__device__ __forceinline__ void stage16(uint8_t* dst, const uint32_t (&r)[16], bool relu);
+__device__ __forceinline__ void stage16(uint8_t* dst, const uint32_t* r, bool relu);
 
 template <>
-__device__ __forceinline__ void stage16<__nv_bfloat16>(uint8_t* dst, const uint32_t (&r)[16],
-                                                       bool relu) {
+__device__ __forceinline__ void stage16<__nv_bfloat16>(uint8_t* dst, const uint32_t* r, bool relu) {
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -77,7 +76,7 @@ __device__ __forceinline__ void stage16<__nv_bfloat16>(uint8_t* dst, const uint3
 }
 
 template <>
-__device__ __forceinline__ void stage16<float>(uint8_t* dst, const uint32_t (&r)[16], bool relu) {
+__device__ __forceinline__ void stage16<float>(uint8_t* dst, const uint32_t* r, bool relu) {
   uint4* d = reinterpret_cast<uint4*>(dst);
   uint32_t v[16];
 #pragma unroll
@@ -240,11 +239,29 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row0 = tile * BM + q * 32;
       for (int seg0 = 0; seg0 < bn; seg0 += SEG_COLS) {
         const int seg_cols = min(SEG_COLS, bn - seg0);
-        for (int c0 = 0; c0 < seg_cols; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(taddr + seg0 + c0, r);
+        if (seg_cols == 128) {
+          // full bf16 segment: two 64-column loads in flight, one wait
+          uint32_t r[128];
+          tmem_ld64(taddr + seg0, *reinterpret_cast<uint32_t(*)[64]>(&r[0]));
+          tmem_ld64(taddr + seg0 + 64, *reinterpret_cast<uint32_t(*)[64]>(&r[64]));
           tmem_ld_wait();
-          stage16<OutT>(my_stage + lane * STAGE_PITCH + c0 * ESZ, r, relu != 0);
+#pragma unroll
+          for (int c0 = 0; c0 < 128; c0 += 16)
+            stage16<OutT>(my_stage + lane * STAGE_PITCH + c0 * ESZ, &r[c0], relu != 0);
+        } else if (seg_cols == 64) {
+          uint32_t r[64];
+          tmem_ld64(taddr + seg0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c0 = 0; c0 < 64; c0 += 16)
+            stage16<OutT>(my_stage + lane * STAGE_PITCH + c0 * ESZ, &r[c0], relu != 0);
+        } else {
+          for (int c0 = 0; c0 < seg_cols; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(taddr + seg0 + c0, r);
+            tmem_ld_wait();
+            stage16<OutT>(my_stage + lane * STAGE_PITCH + c0 * ESZ, r, relu != 0);
+          }
         }
         if (seg0 + SEG_COLS >= bn) {
           // all TMEM reads of this tile are done: hand the accumulator back to the MMA warp

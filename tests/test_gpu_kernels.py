@@ -262,7 +262,7 @@ def test_relu_dropout_same_mask_on_cpu_and_gpu(dtype):
     g = torch.randn(1000, 24).to(dtype)
     outs = []
     for dev in ("cpu", _dev()):
-        xi = x.to(dev).requires_grad_()
+        xi = x.detach().clone().to(dev).requires_grad_()
         y = relu_dropout(xi, p=0.3, seed=5, index_offset=77)
         y.backward(g.to(dev))
         outs.append((y.detach().float().cpu(), xi.grad.float().cpu()))
