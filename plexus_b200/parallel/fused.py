@@ -21,7 +21,20 @@ from ..ops import _ext
 from ..ops import cuda as opc
 from . import symm
 
+import os
+
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
+
+# The push epilogue is a one-shot all-reduce: every rank sends its whole partial result to every
+# peer, (p-1) x M bytes per rank.  For p = 2 that is the minimum; measured on 4 GPUs it loses to
+# NCCL's bandwidth-optimal ring (2 (p-1)/p x M), so larger groups reduce large messages with NCCL
+# after the compute kernel.  Small messages (latency bound) always use the push path.
+ONE_SHOT_MAX_RANKS = int(os.environ.get("PLEXUS_ONE_SHOT_MAX_RANKS", "2"))
+SMALL_MESSAGE_BYTES = 1 << 20
+
+
+def _push_path(ax, nbytes: int) -> bool:
+    return ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES
 
 
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
@@ -35,6 +48,10 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     """``all_reduce_sum(A @ H)`` over ``group`` with the push fused in the SpMM epilogue."""
     ax = symm.axis_for(group)
     rows, D = A.shape[0], H.shape[1]
+    if not _push_path(ax, rows * D * H.element_size()):
+        out = opc.spmm(A, H)
+        dist.all_reduce(out, group=group)
+        return out if relu_mask is None else opc.relu_backward(out, relu_mask)
     ax.ensure(rows * D * H.element_size())
     epoch, buf = ax.next_op()
     out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
@@ -49,6 +66,10 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
     ax = symm.axis_for(group)
     rows = a.shape[0]
     N = W.shape[0] if trans_b else W.shape[1]
+    if not _push_path(ax, rows * N * a.element_size()):
+        out = opc.gemm(a, W, trans_b=trans_b, relu=False)
+        dist.all_reduce(out, group=group)
+        return torch.relu_(out) if relu else out
     ax.ensure(rows * N * a.element_size())
     epoch, buf = ax.next_op()
     out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
@@ -69,6 +90,9 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
         return t
     ax = symm.axis_for(group)
     C = _ext.load()
+    if not _push_path(ax, t.numel() * 4):
+        dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=group)
+        return t
     ax.ensure(t.numel() * 4)
     epoch, buf = ax.next_op()
     C.push_copy(t, ax.push_targets(buf))
@@ -108,6 +132,9 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
     if t2.numel() == 0:
         return t
     ax = symm.axis_for(group)
+    if not _push_path(ax, t2.numel() * 2):
+        dist.all_reduce(t, group=group)
+        return t
     ax.ensure(t2.numel() * 2)
     epoch, buf = ax.next_op()
     _ext.load().push_copy(t2, ax.push_targets(buf))

@@ -33,7 +33,7 @@ def _entry(rank, world, fn, init_file, args, errq):
         raise
 
 
-def run_gpus(fn, world, *args, timeout=300):
+def run_gpus(fn, world, *args, timeout=150):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     with tempfile.TemporaryDirectory() as d:
@@ -112,13 +112,22 @@ def _model(rank, world, grid, layers):
         torch.cuda.synchronize()
         opc.check_status()
         results[comm] = dict(loss=loss.item(), gx=feats.grad.float().cpu(),
-                             gw=[l.weight.grad.float().cpu() for l in model.layers], model=model, feats=feats)
+                             gw=[l.weight.grad.float().cpu() for l in model.layers], model=model,
+                             feats=feats.detach())
         if comm == "nccl":
             plx.shutdown()
     a, b = results["nccl"], results["fused"]
 
     def rel(x, y):
         return ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item()
+
+    # both paths against the fp64 oracle first: a protocol bug shows up here as a gross error
+    ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, layers, 64, seed=5)
+    for name, r_ in results.items():
+        assert abs(r_["loss"] - ref_loss.item()) < 2e-2 * abs(ref_loss.item()), name
+        for l, layer in enumerate(r_["model"].layers):
+            assert rel(r_["gw"][l], _cut_weight(layer, ref_gw[l].float())) < 0.35, (name, l)
+        assert rel(r_["gx"], _cut_features(ref_gx.float(), r_["feats"])) < 0.35, name
 
     # NCCL's bf16 ring all-reduce rounds after every step, the peer-memory path rounds once:
     # the two differ by a few bf16 ulps more on groups of 4+ ranks
@@ -127,12 +136,6 @@ def _model(rank, world, grid, layers):
     for l in range(layers):
         assert rel(b["gw"][l], a["gw"][l]) < tol, l
     assert rel(b["gx"], a["gx"]) < tol
-    ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, layers, 64, seed=5)
-    assert abs(b["loss"] - ref_loss.item()) < 2e-2 * abs(ref_loss.item())
-    for l, layer in enumerate(b["model"].layers):
-        want = _cut_weight(layer, ref_gw[l].float())
-        assert rel(b["gw"][l], want) < 0.35, l
-    assert rel(b["gx"], _cut_features(ref_gx.float(), b["feats"])) < 0.35
     plx.shutdown()
 
 
