@@ -70,11 +70,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     log = []
     jobs = []
     objs = []
+    extra = os.environ.get("PLEXUS_EXTRA_DEFINES", "").split()  # e.g. -DPLX_GEMM_PROF for timing probes
     for src in cuda_sources():
         obj = os.path.join(BUILD, os.path.basename(src) + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers()):
-            jobs.append([nvcc, *NVCC_FLAGS, "-c", src, "-o", obj])
+            jobs.append([nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj])
     bsrc = os.path.join(CSRC, "bindings.cpp")
     bobj = os.path.join(BUILD, "bindings.o")
     objs.append(bobj)
@@ -86,7 +87,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         jobs.append([
             os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-c", bsrc, "-o", bobj,
             f"-DTORCH_EXTENSION_NAME={NAME}", "-DTORCH_API_INCLUDE_EXTENSION_H",
-            f"-D_GLIBCXX_USE_CXX11_ABI={abi}", *inc,
+            f"-D_GLIBCXX_USE_CXX11_ABI={abi}", *extra, *inc,
         ])
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
         list(pool.map(lambda c: _run(c, log), jobs))

@@ -410,6 +410,17 @@ Tensor relu_dropout(const Tensor& x, const c10::optional<Tensor>& grad, double p
   return out;
 }
 
+#ifdef PLX_GEMM_PROF
+}  // namespace
+namespace plx { void gemm_prof_dump(long long* host); }
+namespace {
+std::vector<int64_t> gemm_prof() {
+  std::vector<long long> h(256);
+  plx::gemm_prof_dump(h.data());
+  return std::vector<int64_t>(h.begin(), h.end());
+}
+#endif
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -426,6 +437,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relu_bwd", &relu_bwd);
   m.def("prep_weight", &prep_weight);
   m.def("wait_flag", &wait_flag);
+#ifdef PLX_GEMM_PROF
+  m.def("gemm_prof", &gemm_prof);
+#endif
   m.def("rmat_edges", &rmat_edges);
   m.def("gcn_norm", &gcn_norm);
   m.def("coo_to_csr", &coo_to_csr);

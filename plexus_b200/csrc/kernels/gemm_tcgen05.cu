@@ -36,6 +36,13 @@ constexpr int SMEM_LIMIT = 232448;        // 227 KB opt-in maximum per CTA
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID_GEMM = 6;
 
+#ifdef PLX_GEMM_PROF
+__device__ long long g_gemm_prof[32][8];
+#define PROF(t, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (t) < 32) g_gemm_prof[(t)][(slot)] = clock64(); } while (0)
+#else
+#define PROF(t, slot) do { } while (0)
+#endif
+
 struct alignas(8) GemmBarriers {
   uint64_t full[8];
   uint64_t empty[8];
@@ -191,6 +198,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           break;
         }
         tc_fence_after();
+        PROF(t, 0);  // accumulator buffer free
         const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % stages;
@@ -214,6 +222,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           umma_commit(&bars->empty[s]);  // stage reusable once these MMAs retire
         }
         if (ok) umma_commit(&bars->tfull[buf]);
+        PROF(t, 1);  // all MMAs of the tile issued
       }
     }
   } else {
@@ -230,6 +239,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
+      if (warp == 2 && lane == 0) PROF(t, 2);  // accumulator ready
       constexpr int ESZ = sizeof(OutT);
       constexpr int SEG_COLS = SEG_BYTES / ESZ;  // columns per staged segment
       constexpr int LANES_PER_ROW = SEG_BYTES / 16;
@@ -268,29 +278,42 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->tempty[buf]);
+          if (warp == 2 && lane == 0) PROF(t, 3);  // TMEM read + staged
         } else {
           __syncwarp();
         }
         const int sub = lane / LANES_PER_ROW, l = lane % LANES_PER_ROW;
         const int col = seg0 + l * (16 / ESZ);  // first column of this lane's 16 bytes
         if (col + 16 / ESZ <= n_valid) {
-          for (int rr = 0; rr < 32; rr += ROWS_PER_ITER) {
-            const int rl = rr + sub;
-            const int row = row0 + rl;
-            if (row < M) {
-              const uint4 v = *reinterpret_cast<const uint4*>(my_stage + rl * STAGE_PITCH + l * 16);
-              *reinterpret_cast<uint4*>(C + static_cast<size_t>(row) * ldc + n0 + col) = v;
-              // fused collective: the same bytes go straight into the peers' receive slots
+          // read the whole staged segment into registers first, then stream the stores back to back
+          constexpr int NIT = 32 / ROWS_PER_ITER;
+          uint4 v[NIT];
 #pragma unroll
-              for (int p = 0; p < MAX_PEERS; ++p)  // static indices keep the pointers in registers
-                if (p < push.n)
-                  *reinterpret_cast<uint4*>(static_cast<OutT*>(push.base[p]) +
-                                            static_cast<size_t>(row) * push.ld + n0 + col) = v;
+          for (int i = 0; i < NIT; ++i)
+            v[i] = *reinterpret_cast<const uint4*>(my_stage + (i * ROWS_PER_ITER + sub) * STAGE_PITCH + l * 16);
+          OutT* cbase = C + static_cast<size_t>(row0 + sub) * ldc + n0 + col;
+#pragma unroll
+          for (int i = 0; i < NIT; ++i) {
+            const int row = row0 + i * ROWS_PER_ITER + sub;
+            if (row < M) *reinterpret_cast<uint4*>(cbase + static_cast<size_t>(i * ROWS_PER_ITER) * ldc) = v[i];
+          }
+          // fused collective: the same bytes go straight into the peers' receive slots
+#pragma unroll
+          for (int p = 0; p < MAX_PEERS; ++p) {  // static indices keep the pointers in registers
+            if (p < push.n) {
+              OutT* pbase = static_cast<OutT*>(push.base[p]) + static_cast<size_t>(row0 + sub) * push.ld + n0 + col;
+#pragma unroll
+              for (int i = 0; i < NIT; ++i) {
+                const int row = row0 + i * ROWS_PER_ITER + sub;
+                if (row < M)
+                  *reinterpret_cast<uint4*>(pbase + static_cast<size_t>(i * ROWS_PER_ITER) * push.ld) = v[i];
+              }
             }
           }
         }
         __syncwarp();
       }
+      if (warp == 2 && lane == 0) PROF(t, 4);  // rows written
 
     }
   }
@@ -533,18 +556,16 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   if (M == 0 || N == 0) return nullptr;
   const int KB = static_cast<int>((K + BK - 1) / BK);
   const int bar_bytes = sizeof(GemmBarriers) + 16 + STAGING_BYTES + 1024;  // + staging + alignment slack
-  // Column block: as wide as possible (A is read once per column block), but narrow enough that
-  // W stays resident AND the TMA ring for A keeps at least 6 stages (~100 KB) in flight per SM,
-  // which is what a bandwidth-bound stream needs.  Two CTAs then share an A tile through L2.
+  // Column block: as wide as possible, so that A is streamed exactly once (measured: a 256-wide
+  // block with a 3-stage ring reaches 0.87 of copy bandwidth, two 128-wide blocks sharing the A
+  // tiles through L2 only 0.52).  nb_override narrows it for tuning.
   int bn_box = static_cast<int>(std::min<int64_t>(256, (N + 15) / 16 * 16));
   if (nb_override > 0) bn_box = std::min(bn_box, std::max(16, (nb_override + 15) / 16 * 16));
-  int b_resident = 1, stages = 0, b_blk = 0;
-  for (;;) {
-    b_blk = bn_box * 128;
+  int b_resident = 1, stages = 0;
+  const int b_blk = bn_box * 128;
+  {
     int64_t left = SMEM_LIMIT - bar_bytes - static_cast<int64_t>(KB) * b_blk;
     stages = left > 0 ? static_cast<int>(left / A_STAGE_BYTES) : 0;
-    if (stages >= 6 || bn_box <= 128 || nb_override > 0) break;
-    bn_box = 128;
   }
   if (stages < 3) {
     b_resident = 0;
@@ -583,6 +604,10 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   }
   return last_launch_error();
 }
+
+#ifdef PLX_GEMM_PROF
+void gemm_prof_dump(long long* host) { cudaMemcpyFromSymbol(host, g_gemm_prof, sizeof(long long) * 32 * 8); }
+#endif
 
 // Number of row-split CTAs gemm_tn uses for R reduction rows (scratch = parts * Mw * Nw floats).
 int gemm_tn_parts(int64_t R) {
