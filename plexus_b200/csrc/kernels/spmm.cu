@@ -584,7 +584,7 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
                             int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
                             float* scratch, int64_t scratch_elems, const PushTargets* push_in,
                             int variant, cudaStream_t stream) {
-  const bool use_mma = variant != SPMM_VARIANT_FMA;
+  const bool use_mma = variant == SPMM_VARIANT_TENSOR;
   const int esz = dtype == DT_BF16 ? 2 : 4;
   PushTargets push;
   push.n = 0;

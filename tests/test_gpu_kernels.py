@@ -28,7 +28,7 @@ def _random_csr(rows, cols, mean_deg, long_row=None, empty_every=7, seed=0):
     return torch.sparse_csr_tensor(crow.int(), col.int(), val, size=(rows, cols), check_invariants=False)
 
 
-@pytest.mark.parametrize("variant", [0, 1])  # 0: tensor-core accumulation, 1: FMA accumulation
+@pytest.mark.parametrize("variant", [0, 1])  # 0: warp-MMA accumulation, 1: packed-FMA accumulation
 @pytest.mark.parametrize("D", [8, 24, 48, 104, 128, 256, 304, 608])
 def test_spmm_bf16_matches_fp32_reference(D, variant):
     from plexus_b200.ops import cuda as opc
