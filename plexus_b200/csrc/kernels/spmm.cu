@@ -112,7 +112,10 @@ __device__ __forceinline__ void row_accumulate(const int* __restrict__ col,
                                                float (&acc)[VPL][Vec16<T>::N]) {
   constexpr int VN = Vec16<T>::N;
   constexpr int G = 32 / LPR;
-  constexpr int U = VPL == 1 ? 4 : 2;
+#ifndef PLX_SPMM_U
+#define PLX_SPMM_U 4
+#endif
+  constexpr int U = VPL == 1 ? PLX_SPMM_U : 2;  // nonzeros in flight per group
   const int g = lane / LPR, li = lane % LPR;
   const uint32_t ldh32 = static_cast<uint32_t>(ldh);  // 32 x 32 -> 64-bit multiply-add per row address
   bool active[VPL];
@@ -404,7 +407,10 @@ __device__ __forceinline__ uint8_t* warp_stage(int lane) {
 }
 
 template <typename T, int LPR, int VPL, bool MMA>
-__global__ void __launch_bounds__(MMA ? MMA_WARPS * 32 : SPMM_WARPS * 32, MMA ? 3 : (VPL == 1 ? 4 : 2))
+#ifndef PLX_SPMM_MINB
+#define PLX_SPMM_MINB 4
+#endif
+__global__ void __launch_bounds__(MMA ? MMA_WARPS * 32 : SPMM_WARPS * 32, MMA ? 3 : (VPL == 1 ? PLX_SPMM_MINB : 2))
 spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
                  const float* __restrict__ val, const T* __restrict__ H, int64_t ldh,
                  T* __restrict__ out, int64_t ldo, const T* __restrict__ mask, int64_t ldm, int D,
@@ -432,7 +438,7 @@ spmm_rows_kernel(const int* __restrict__ rowptr, const int* __restrict__ col,
 
 // One warp per piece of a long row: fp32 partial row -> scratch[piece][LPR*VPL*VN].
 template <typename T, int LPR, int VPL, bool MMA>
-__global__ void __launch_bounds__(MMA ? MMA_WARPS * 32 : SPMM_WARPS * 32, MMA ? 3 : (VPL == 1 ? 4 : 2))
+__global__ void __launch_bounds__(MMA ? MMA_WARPS * 32 : SPMM_WARPS * 32, MMA ? 3 : (VPL == 1 ? PLX_SPMM_MINB : 2))
 spmm_pieces_kernel(const int* __restrict__ piece_beg, const int* __restrict__ piece_end,
                    int num_pieces, const int* __restrict__ col, const float* __restrict__ val,
                    const T* __restrict__ H, int64_t ldh, int D, float* __restrict__ scratch) {
