@@ -124,7 +124,7 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
              int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
-             const std::vector<int64_t>& push_ptrs, int64_t push_ld) {
+             const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
@@ -132,12 +132,20 @@ void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tenso
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
   plx::PushTargets push = make_push(push_ptrs, push_ld);
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == C.scalar_type() && mask->sizes() == C.sizes() &&
+                mask->stride(1) == 1, "gemm_nt: bad mask");
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
   c10::cuda::CUDAGuard guard(A.device());
   check(plx::launch_gemm_nt(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(),
                             C.stride(0), dtype_of(C), A.size(0), B.size(0), A.size(1), relu,
                             status_ptr(status), static_cast<int>(max_stages),
                             static_cast<int>(ctas_limit), static_cast<int>(nb_override),
-                            push.n ? &push : nullptr, stream()));
+                            push.n ? &push : nullptr, mptr, ldm, stream()));
 }
 
 int64_t gemm_tn_parts(int64_t R) { return plx::gemm_tn_parts(R); }

@@ -52,7 +52,8 @@ enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
                            int* status, int max_stages, int ctas_limit, int nb_override,
-                           const PushTargets* push, cudaStream_t stream);
+                           const PushTargets* push, const void* mask, int64_t ldm, cudaStream_t stream);
+// mask (same dtype and shape as C, may be null): C = result where mask > 0, else 0.
 // out[Mw,Nw] fp32 = A[R,Mw]^T . B[R,Nw]; scratch >= gemm_tn_parts(R)*Mw*Nw floats.
 int gemm_tn_parts(int64_t R);
 const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ldb, float* out,

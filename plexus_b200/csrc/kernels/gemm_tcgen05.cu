@@ -95,6 +95,31 @@ __device__ __forceinline__ void stage16<float>(uint8_t* dst, const uint32_t* r, 
   d[3] = make_uint4(v[12], v[13], v[14], v[15]);
 }
 
+// v = v where mask > 0 else 0, on a 16-byte vector of OutT
+template <typename OutT>
+__device__ __forceinline__ void apply_relu_mask(uint4& v, const uint4& m);
+template <>
+__device__ __forceinline__ void apply_relu_mask<__nv_bfloat16>(uint4& v, const uint4& m) {
+  uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+  const uint32_t* mw = reinterpret_cast<const uint32_t*>(&m);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = mw[i] & 0xffffu, hi = mw[i] >> 16;
+    // positive bf16: sign bit clear and not zero
+    const uint32_t keep_lo = ((lo & 0x8000u) == 0 && (lo & 0x7fffu) != 0) ? 0x0000ffffu : 0u;
+    const uint32_t keep_hi = ((hi & 0x8000u) == 0 && (hi & 0x7fffu) != 0) ? 0xffff0000u : 0u;
+    vw[i] &= keep_lo | keep_hi;
+  }
+}
+template <>
+__device__ __forceinline__ void apply_relu_mask<float>(uint4& v, const uint4& m) {
+  uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+  const float* mf = reinterpret_cast<const float*>(&m);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (!(mf[i] > 0.f)) vw[i] = 0u;
+}
+
 // ---------------------------------------------------------------------------------------
 // C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = block of bn_box columns)
 // ---------------------------------------------------------------------------------------
@@ -102,7 +127,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
-               int b_resident, int relu, int* status, const PushTargets push) {
+               int b_resident, int relu, int* status, const PushTargets push,
+               const OutT* __restrict__ mask, int ldm) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -291,6 +317,19 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < NIT; ++i)
             v[i] = *reinterpret_cast<const uint4*>(my_stage + (i * ROWS_PER_ITER + sub) * STAGE_PITCH + l * 16);
+          if (mask != nullptr) {
+            // ReLU derivative of the layer input: zero the gradient where the saved activation is <= 0
+            uint4 mk[NIT];
+            const OutT* mbase = mask + static_cast<size_t>(row0 + sub) * ldm + n0 + col;
+#pragma unroll
+            for (int i = 0; i < NIT; ++i) {
+              mk[i] = make_uint4(0, 0, 0, 0);
+              if (row0 + i * ROWS_PER_ITER + sub < M)
+                mk[i] = __ldg(reinterpret_cast<const uint4*>(mbase + static_cast<size_t>(i * ROWS_PER_ITER) * ldm));
+            }
+#pragma unroll
+            for (int i = 0; i < NIT; ++i) apply_relu_mask<OutT>(v[i], mk[i]);
+          }
           OutT* cbase = C + static_cast<size_t>(row0 + sub) * ldc + n0 + col;
 #pragma unroll
           for (int i = 0; i < NIT; ++i) {
@@ -541,7 +580,9 @@ static int num_sms() {
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
                            int* status, int max_stages, int ctas_limit, int nb_override,
-                           const PushTargets* push_in, cudaStream_t stream) {
+                           const PushTargets* push_in, const void* mask, int64_t ldm, cudaStream_t stream) {
+  if (mask != nullptr && (ldm % 8 || reinterpret_cast<uintptr_t>(mask) % 16))
+    return "gemm_nt: mask must be 16-byte aligned with a leading dimension multiple of 8";
   PushTargets push;
   push.n = 0;
   if (push_in != nullptr) {
@@ -591,14 +632,17 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
-                                               b_resident, relu ? 1 : 0, status, push);
+                                               b_resident, relu ? 1 : 0, status, push,
+                                               reinterpret_cast<const __nv_bfloat16*>(mask),
+                                               static_cast<int>(ldm));
   } else if (c_dtype == DT_F32) {
     auto kern = gemm_nt_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<float*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
-                                               b_resident, relu ? 1 : 0, status, push);
+                                               b_resident, relu ? 1 : 0, status, push,
+                                               reinterpret_cast<const float*>(mask), static_cast<int>(ldm));
   } else {
     return "gemm_nt: C must be bf16 or fp32";
   }

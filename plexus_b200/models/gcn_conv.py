@@ -216,10 +216,10 @@ def _combine_first_backward(grad_out, H, weight, A_t, spec: LayerSpec, input_rel
     grad_x = None
     if need_input_grad:
         timers.start("GRAD_AGG = GRAD_OUT * W.T")
-        grad_x = tuned_matmul(grad_t, W, "GRAD_T * W.T " + str(spec.layer_num), trans_b=True)
+        # the ReLU derivative of the layer input is applied in the GEMM epilogue
+        grad_x = tuned_matmul(grad_t, W, "GRAD_T * W.T " + str(spec.layer_num), trans_b=True,
+                              relu_mask=input_relu_mask)
         timers.stop("GRAD_AGG = GRAD_OUT * W.T")
-        if input_relu_mask is not None:
-            grad_x = ops.relu_backward(grad_x, input_relu_mask)
     timers.stop("gcn conv bwd")
     return grad_x, grad_w
 

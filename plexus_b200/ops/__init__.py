@@ -34,11 +34,16 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     return res
 
 
-def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None):
-    """``op(a) @ op(b)`` (fp32 accumulate) with optional fused ReLU."""
+def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, relu_mask=None):
+    """``op(a) @ op(b)`` (fp32 accumulate) with optional fused ReLU or ``* (relu_mask > 0)``."""
+    if a.is_cuda and not trans_a:
+        return _cuda().gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype,
+                            relu_mask=relu_mask)
     if a.is_cuda:
-        return _cuda().gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype)
-    return reference.gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype)
+        out = _cuda().gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype)
+    else:
+        out = reference.gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype)
+    return out if relu_mask is None else relu_backward(out, relu_mask)
 
 
 def relu_backward(grad, out):

@@ -180,7 +180,8 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
 
 
 def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0,
-         push_ptrs=(), push_ld=0):
+         push_ptrs=(), push_ld=0, relu_mask=None):
+    """``relu_mask`` (shape of the result): zero the result where the mask is not positive."""
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas, nb = GEMM_VARIANTS[variant]
@@ -214,7 +215,9 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         C.prep_weight(b.contiguous(), None, bt)
         _count(1)
     out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
-    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld))
+    if relu_mask is not None and relu_mask.dtype != out.dtype:
+        relu_mask = relu_mask.to(out.dtype)
+    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask)
     _count(1)
     return out
 

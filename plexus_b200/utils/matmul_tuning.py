@@ -74,19 +74,22 @@ def _cpu_variant(A, B, idx, trans_a, trans_b, relu, out_dtype):
     return out.to(out_dtype or A.dtype)
 
 
-def tuned_matmul(A, B, matmul_name, trans_a=False, trans_b=False, relu=False, out_dtype=None):
+def tuned_matmul(A, B, matmul_name, trans_a=False, trans_b=False, relu=False, out_dtype=None, relu_mask=None):
     """``op(A) @ op(B)``; tunes and caches the variant per ``matmul_name`` if enabled."""
     if not runtime.flags.tune_gemm:
-        return ops.gemm(A, B, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype)
+        return ops.gemm(A, B, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype,
+                        relu_mask=relu_mask)
 
     if A.is_cuda:
         from ..ops import cuda as opc
 
         run = lambda i: opc.gemm(A, B, trans_a=trans_a, trans_b=trans_b, relu=relu,
-                                 out_dtype=out_dtype, variant=i)
+                                 out_dtype=out_dtype, variant=i, relu_mask=relu_mask)
         n_variants = len(opc.GEMM_VARIANTS)
     else:
-        run = lambda i: _cpu_variant(A, B, i, trans_a, trans_b, relu, out_dtype)
+        def run(i):
+            out = _cpu_variant(A, B, i, trans_a, trans_b, relu, out_dtype)
+            return out if relu_mask is None else ops.relu_backward(out, relu_mask)
         n_variants = len(transpose_orders)
 
     if matmul_name not in matmul_to_index:

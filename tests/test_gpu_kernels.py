@@ -272,3 +272,20 @@ def test_relu_dropout_same_mask_on_cpu_and_gpu(dtype):
     assert 0.6 < kept < 0.8
     y0 = relu_dropout(x.to(_dev()), p=0.0)
     assert torch.equal(y0.cpu(), torch.relu(x))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_nt_relu_derivative_mask_in_epilogue(out_dtype):
+    from plexus_b200.ops import cuda as opc
+
+    torch.manual_seed(3)
+    a = torch.randn(1111, 48).to(torch.bfloat16)
+    w = (torch.randn(256, 48) / 7).to(torch.bfloat16)  # [N, K]: used transposed
+    mask = torch.randn(1111, 256).to(out_dtype)
+    mask[::5] = 0
+    ref = (a.float() @ w.float().t()) * (mask.float() > 0)
+    out = opc.gemm(a.to(_dev()), w.to(_dev()), trans_b=True, out_dtype=out_dtype, relu_mask=mask.to(_dev()))
+    opc.check_status()
+    assert out.dtype == out_dtype
+    assert (out.float().cpu() - ref).abs().max() < 1e-2 * ref.abs().max()
+    assert torch.equal(out.float().cpu() == 0, ref == 0)
