@@ -8,7 +8,10 @@ P ranks compute ``all_reduce_sum(A_r . H_r)`` and ``all_reduce_sum(X_r . W_r)``,
 of a 3D-parallel GCN layer (AGG over the outer axis, OUT over the inner axis).  Three paths:
 
 * ``fused``     : this package's kernels; the SpMM / tcgen05-GEMM epilogue stores each row into
-                  the peers' receive slots over NVLink, a flagged kernel sums the slots;
+                  the peers' receive slots over NVLink, a flagged kernel sums the slots.  Timed in
+                  the default form for the group size and in both forms explicitly: ``one_shot``
+                  (every row to every peer) and ``two_shot`` (each row to its owner, which reduces
+                  and broadcasts its segment);
 * ``nccl``      : the same compute kernels followed by ``dist.all_reduce`` (NCCL);
 * ``reference`` : what the reference executes: ``torch.sparse.mm`` / ``torch.mm`` in fp32
                   (cuSPARSE / cuBLAS) followed by an fp32 NCCL all-reduce.
@@ -109,6 +112,11 @@ def main():
     b = spmm_nccl().float()
     res["spmm_max_rel_diff_fused_vs_nccl"] = ((a - b).abs().max() / b.abs().max()).item()
     res["spmm_fused_ms"] = timed(spmm_fused, args.warmup, args.iters)
+    default_ranks = fused.ONE_SHOT_MAX_RANKS
+    for name, ranks in (("one_shot", p), ("two_shot", 1)):
+        fused.ONE_SHOT_MAX_RANKS = ranks
+        res[f"spmm_{name}_ms"] = timed(spmm_fused, args.warmup, args.iters)
+    fused.ONE_SHOT_MAX_RANKS = default_ranks
     res["spmm_nccl_ms"] = timed(spmm_nccl, args.warmup, args.iters)
     res["spmm_only_ms"] = timed(lambda: ops.spmm(A, H), args.warmup, args.iters)
     msg = rows * D * 2
@@ -133,6 +141,10 @@ def main():
     b = gemm_nccl().float()
     res["gemm_max_rel_diff_fused_vs_nccl"] = ((a - b).abs().max() / b.abs().max()).item()
     res["gemm_fused_ms"] = timed(gemm_fused, args.warmup, args.iters)
+    for name, ranks in (("one_shot", p), ("two_shot", 1)):
+        fused.ONE_SHOT_MAX_RANKS = ranks
+        res[f"gemm_{name}_ms"] = timed(gemm_fused, args.warmup, args.iters)
+    fused.ONE_SHOT_MAX_RANKS = default_ranks
     res["gemm_nccl_ms"] = timed(gemm_nccl, args.warmup, args.iters)
     res["gemm_only_ms"] = timed(lambda: ops.gemm(X, W), args.warmup, args.iters)
     msg = rows * N * 2

@@ -29,12 +29,18 @@ int* status_ptr(const Tensor& status) {
   return status.data_ptr<int>();
 }
 
-plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld) {
-  plx::PushTargets p;
+// seg_rows > 0 selects the reduce-scatter push (row r goes only to group rank r / seg_rows).
+plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t seg_rows = 0,
+                           int64_t me = 0) {
+  plx::PushTargets p = {};
   TORCH_CHECK(ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS), "too many push targets");
+  TORCH_CHECK(seg_rows >= 0 && seg_rows < (1ll << 31) && me >= 0 && me <= static_cast<int64_t>(ptrs.size()),
+              "bad reduce-scatter push description");
   p.n = static_cast<int>(ptrs.size());
   for (int i = 0; i < p.n; ++i) p.base[i] = reinterpret_cast<void*>(ptrs[i]);
   p.ld = ld;
+  p.seg_rows = static_cast<int>(seg_rows);
+  p.me = static_cast<int>(me);
   return p;
 }
 
@@ -74,7 +80,8 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
               const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
               const Tensor& piece_beg, const Tensor& piece_end, const Tensor& long_rows,
               const Tensor& long_piece_start, const Tensor& scratch,
-              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t variant) {
+              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t variant,
+              int64_t push_seg_rows, int64_t push_me) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -110,7 +117,9 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
     scr = scratch.data_ptr<float>();
     scr_n = scratch.numel();
   }
-  plx::PushTargets push = make_push(push_ptrs, push_ld);
+  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
+  TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
+              "spmm: row segments do not cover the output");
   c10::cuda::CUDAGuard guard(H.device());
   check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
                              val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
@@ -124,14 +133,15 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
              int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
-             const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask) {
+             const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask,
+             int64_t push_seg_rows, int64_t push_me) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
-  plx::PushTargets push = make_push(push_ptrs, push_ld);
+  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
   const void* mptr = nullptr;
   int64_t ldm = 0;
   if (mask.has_value() && mask->defined()) {
@@ -314,6 +324,43 @@ void reduce_slots(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t sl
                                       stream()));
 }
 
+// Middle step of the two-shot all-reduce: reduce rows [row0, row0 + rows) of `out` with the
+// peers' partials and store the result into `bcast_ptrs` (receive slots of the next op).
+void reduce_segment(Tensor& out, int64_t row0, int64_t rows, const std::vector<int64_t>& slot_ptrs,
+                    int64_t slot_ld, bool relu, const c10::optional<Tensor>& mask,
+                    const std::vector<int64_t>& bcast_ptrs, const std::vector<int64_t>& remote_flags,
+                    const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms,
+                    int64_t kernel_id, const Tensor& status) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(row0 >= 0 && rows >= 0 && row0 + rows <= out.size(0), "reduce_segment: bad row range");
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->scalar_type() == at::kBFloat16 && mask->sizes() == out.sizes() && mask->stride(1) == 1);
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  check(plx::launch_reduce_segment_bf16(out.data_ptr(), out.stride(0), row0, make_slots(slot_ptrs), slot_ld,
+                                        rows, static_cast<int>(out.size(1)), relu, mptr, ldm,
+                                        make_slots(bcast_ptrs),
+                                        make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                        stream()));
+}
+
+void gather_segments(const std::vector<int64_t>& src_ptrs, const std::vector<int64_t>& dst_ptrs,
+                     const std::vector<int64_t>& bytes, const std::vector<int64_t>& remote_flags,
+                     const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms,
+                     int64_t kernel_id, const Tensor& status) {
+  TORCH_CHECK(bytes.size() == src_ptrs.size() && bytes.size() <= static_cast<size_t>(plx::MAX_PEERS));
+  plx::SlotBytes b = {};
+  for (size_t q = 0; q < bytes.size(); ++q) b.n[q] = bytes[q];
+  c10::cuda::CUDAGuard guard(status.device());
+  check(plx::launch_gather_segments(make_slots(src_ptrs), make_slots(dst_ptrs), b,
+                                    make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                    stream()));
+}
+
 void reduce_slots_f32(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t op,
                       const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
                       int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status) {
@@ -454,6 +501,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relu_dropout", &relu_dropout);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_slots_f32", &reduce_slots_f32);
+  m.def("reduce_segment", &reduce_segment);
+  m.def("gather_segments", &gather_segments);
   m.def("push_copy", &push_copy);
   m.def("gather_slots", &gather_slots);
   m.def("symm_alloc", &symm_alloc);

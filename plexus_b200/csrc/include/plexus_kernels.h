@@ -9,14 +9,21 @@ namespace plx {
 
 enum DType : int { DT_BF16 = 0, DT_F32 = 1 };
 
-// Peer-memory destinations of a fused "compute + push" epilogue: besides its own output, a
-// kernel stores every result row at the same (row, column) position of up to MAX_PEERS
-// receive buffers that live in other GPUs' memory (plain stores over NVLink).
+// Peer-memory destinations of a fused "compute + push" epilogue (plain stores over NVLink into
+// receive buffers that live in other GPUs' memory).  Two modes:
+//   seg_rows == 0 (one-shot all-reduce): besides its own output, the kernel stores every result
+//     row at the same (row, column) position of every peer's receive slot.
+//   seg_rows  > 0 (first half of a two-shot all-reduce, i.e. a reduce-scatter): output row r
+//     belongs to group rank r / seg_rows.  Rows of this rank (`me`) go to the local output only;
+//     a row of another rank goes ONLY to that rank's receive slot, at row r - owner * seg_rows.
+//     base[] lists the peers in group-rank order with `me` left out.
 constexpr int MAX_PEERS = 7;
 struct PushTargets {
   int n;                  // number of peers (0 = no push)
   void* base[MAX_PEERS];  // receive slot of this rank inside each peer's workspace
   int64_t ld;             // leading dimension of the receive slots (elements)
+  int seg_rows;           // rows per owner (0 = broadcast every row)
+  int me;                 // this rank's position in the group (seg_rows > 0 only)
 };
 
 // ---- spmm.cu
@@ -125,6 +132,20 @@ const char* launch_reduce_slots_f32(float* out, const SlotList& slots, int64_t n
 const char* launch_push_copy(const void* src, const SlotList& dst, int64_t bytes, cudaStream_t stream);
 const char* launch_gather_slots(const SlotList& src, const SlotList& dst, int64_t bytes,
                                 const PeerSync& sync, cudaStream_t stream);
+// Second half of a two-shot all-reduce.  `out` holds this rank's partial sums of its own row
+// segment [row0, row0 + rows); slots hold the peers' partials of the same rows.  The kernel waits
+// for the peers (op `sync.epoch`), sums in fp32, applies ReLU / the mask, writes the segment back
+// to `out` and stores it into `bcast` (this rank's receive slot of the NEXT op on every peer).
+const char* launch_reduce_segment_bf16(void* out, int64_t ldo, int64_t row0, const SlotList& slots,
+                                       int64_t lds, int64_t rows, int cols, bool relu, const void* mask,
+                                       int64_t ldm, const SlotList& bcast, const PeerSync& sync,
+                                       cudaStream_t stream);
+// After the wait: copy bytes[q] bytes of slot q to dst.ptr[q] (segments of unequal length).
+struct SlotBytes {
+  int64_t n[MAX_PEERS + 1];
+};
+const char* launch_gather_segments(const SlotList& src, const SlotList& dst, const SlotBytes& bytes,
+                                   const PeerSync& sync, cudaStream_t stream);
 // symmetric workspace over CUDA IPC (one cudaMalloc per rank, handles exchanged by the caller)
 const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 const char* symm_open(const unsigned char* handle64, void** ptr);

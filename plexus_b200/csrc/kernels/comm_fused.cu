@@ -130,6 +130,88 @@ reduce_slots_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const Slo
   }
 }
 
+// Two-shot all-reduce, middle step: reduce this rank's row segment and broadcast the result.
+//   out rows [row0, row0 + rows) += sum_q slot_q[0 .. rows)  (fp32), then ReLU / mask, then the
+//   reduced rows are written to `out` and to slot row (r - row0) of every destination in `bcast`.
+__global__ void __launch_bounds__(256)
+reduce_segment_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, int64_t row0, const SlotList slots,
+                           int64_t lds, int64_t rows, int cols, int relu,
+                           const __nv_bfloat16* __restrict__ mask, int64_t ldm, const SlotList bcast,
+                           const PeerSync sync) {
+  if (!signal_and_wait(sync)) return;
+  const int vec_per_row = cols / 8;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    float acc[8];
+    {
+      const uint4 v = *reinterpret_cast<const uint4*>(out + (row0 + r) * ldo + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        acc[2 * k] = f.x;
+        acc[2 * k + 1] = f.y;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q) {
+      if (q >= slots.n) break;
+      const uint4 v = *reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    if (relu) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = fmaxf(acc[k], 0.f);
+    }
+    if (mask != nullptr) {
+      const uint4 mv = *reinterpret_cast<const uint4*>(mask + (row0 + r) * ldm + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&mv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        if (!(f.x > 0.f)) acc[2 * k] = 0.f;
+        if (!(f.y > 0.f)) acc[2 * k + 1] = 0.f;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) po[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + (row0 + r) * ldo + c) = o;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q) {
+      if (q >= bcast.n) break;
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bcast.ptr[q]) + r * lds + c) = o;
+    }
+  }
+}
+
+// After the wait: copy n.n[q] 16-byte words of slot q to dst_q (row segments of unequal length).
+__global__ void __launch_bounds__(256)
+gather_segments_kernel(const SlotList src, const SlotList dst, const SlotBytes n, const PeerSync sync) {
+  if (!signal_and_wait(sync)) return;
+#pragma unroll
+  for (int q = 0; q < MAX_PEERS; ++q) {
+    if (q >= src.n) break;
+    const uint4* s = static_cast<const uint4*>(src.ptr[q]);
+    uint4* d = static_cast<uint4*>(dst.ptr[q]);
+    const int64_t words = n.n[q];
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < words;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+      d[i] = s[i];
+  }
+}
+
 // out[i] = out[i] (op) slot_q[i] for fp32 vectors; op 0 = sum, 1 = max.
 __global__ void __launch_bounds__(256)
 reduce_slots_f32_kernel(float* __restrict__ out, const SlotList slots, int64_t n, int op,
@@ -186,6 +268,38 @@ const char* launch_reduce_slots_bf16(void* out, int64_t ldo, const SlotList& slo
   reduce_slots_bf16_kernel<<<copy_grid(rows * (cols / 8)), 256, 0, stream>>>(
       static_cast<__nv_bfloat16*>(out), ldo, slots, lds, rows, cols, relu ? 1 : 0,
       static_cast<const __nv_bfloat16*>(mask), ldm, sync);
+  return last_launch_error();
+}
+
+const char* launch_reduce_segment_bf16(void* out, int64_t ldo, int64_t row0, const SlotList& slots,
+                                       int64_t lds, int64_t rows, int cols, bool relu, const void* mask,
+                                       int64_t ldm, const SlotList& bcast, const PeerSync& sync,
+                                       cudaStream_t stream) {
+  if (cols % 8 || ldo % 8 || lds % 8 || (mask && ldm % 8)) return "reduce_segment: widths must be multiples of 8";
+  if (slots.n < 0 || slots.n > MAX_PEERS || bcast.n < 0 || bcast.n > MAX_PEERS || sync.n < 0 ||
+      sync.n > MAX_PEERS)
+    return "reduce_segment: too many peers";
+  if (rows < 0 || row0 < 0) return "reduce_segment: bad row range";
+  // an empty segment still takes part in the flag exchange
+  reduce_segment_bf16_kernel<<<copy_grid(std::max<int64_t>(1, rows * (cols / 8))), 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(out), ldo, row0, slots, lds, rows, cols, relu ? 1 : 0,
+      static_cast<const __nv_bfloat16*>(mask), ldm, bcast, sync);
+  return last_launch_error();
+}
+
+const char* launch_gather_segments(const SlotList& src, const SlotList& dst, const SlotBytes& bytes,
+                                   const PeerSync& sync, cudaStream_t stream) {
+  if (src.n != dst.n || src.n < 0 || src.n > MAX_PEERS) return "gather_segments: bad arguments";
+  SlotBytes words = {};
+  int64_t most = 1;
+  for (int q = 0; q < src.n; ++q) {
+    if (bytes.n[q] < 0 || bytes.n[q] % 16) return "gather_segments: sizes must be multiples of 16 bytes";
+    if (reinterpret_cast<uintptr_t>(src.ptr[q]) % 16 || reinterpret_cast<uintptr_t>(dst.ptr[q]) % 16)
+      return "gather_segments: pointers must be 16-byte aligned";
+    words.n[q] = bytes.n[q] / 16;
+    most = std::max(most, words.n[q]);
+  }
+  gather_segments_kernel<<<copy_grid(most), 256, 0, stream>>>(src, dst, words, sync);
   return last_launch_error();
 }
 

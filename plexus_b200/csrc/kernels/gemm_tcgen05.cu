@@ -331,21 +331,43 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int i = 0; i < NIT; ++i) apply_relu_mask<OutT>(v[i], mk[i]);
           }
           OutT* cbase = C + static_cast<size_t>(row0 + sub) * ldc + n0 + col;
+          if (push.seg_rows > 0) {
+            // reduce-scatter push: a row owned by a peer goes only into that peer's receive slot,
+            // at its position inside the owner's row segment
 #pragma unroll
-          for (int i = 0; i < NIT; ++i) {
-            const int row = row0 + i * ROWS_PER_ITER + sub;
-            if (row < M) *reinterpret_cast<uint4*>(cbase + static_cast<size_t>(i * ROWS_PER_ITER) * ldc) = v[i];
-          }
-          // fused collective: the same bytes go straight into the peers' receive slots
+            for (int i = 0; i < NIT; ++i) {
+              const int row = row0 + i * ROWS_PER_ITER + sub;
+              if (row < M) {
+                const int owner = row / push.seg_rows;
+                OutT* dst = cbase + static_cast<size_t>(i * ROWS_PER_ITER) * ldc;
+                if (owner != push.me) {
+                  const int idx = owner - (owner > push.me ? 1 : 0);
+                  void* sel = push.base[0];
 #pragma unroll
-          for (int p = 0; p < MAX_PEERS; ++p) {  // static indices keep the pointers in registers
-            if (p < push.n) {
-              OutT* pbase = static_cast<OutT*>(push.base[p]) + static_cast<size_t>(row0 + sub) * push.ld + n0 + col;
+                  for (int p = 1; p < MAX_PEERS; ++p)  // static indices keep the pointers in registers
+                    if (idx == p) sel = push.base[p];
+                  dst = static_cast<OutT*>(sel) + static_cast<size_t>(row - owner * push.seg_rows) * push.ld + n0 + col;
+                }
+                *reinterpret_cast<uint4*>(dst) = v[i];
+              }
+            }
+          } else {
 #pragma unroll
-              for (int i = 0; i < NIT; ++i) {
-                const int row = row0 + i * ROWS_PER_ITER + sub;
-                if (row < M)
-                  *reinterpret_cast<uint4*>(pbase + static_cast<size_t>(i * ROWS_PER_ITER) * push.ld) = v[i];
+            for (int i = 0; i < NIT; ++i) {
+              const int row = row0 + i * ROWS_PER_ITER + sub;
+              if (row < M) *reinterpret_cast<uint4*>(cbase + static_cast<size_t>(i * ROWS_PER_ITER) * ldc) = v[i];
+            }
+            // one-shot push: the same bytes go straight into every peer's receive slot
+#pragma unroll
+            for (int p = 0; p < MAX_PEERS; ++p) {  // static indices keep the pointers in registers
+              if (p < push.n) {
+                OutT* pbase = static_cast<OutT*>(push.base[p]) + static_cast<size_t>(row0 + sub) * push.ld + n0 + col;
+#pragma unroll
+                for (int i = 0; i < NIT; ++i) {
+                  const int row = row0 + i * ROWS_PER_ITER + sub;
+                  if (row < M)
+                    *reinterpret_cast<uint4*>(pbase + static_cast<size_t>(i * ROWS_PER_ITER) * push.ld) = v[i];
+                }
               }
             }
           }
@@ -583,11 +605,13 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
                            const PushTargets* push_in, const void* mask, int64_t ldm, cudaStream_t stream) {
   if (mask != nullptr && (ldm % 8 || reinterpret_cast<uintptr_t>(mask) % 16))
     return "gemm_nt: mask must be 16-byte aligned with a leading dimension multiple of 8";
-  PushTargets push;
-  push.n = 0;
+  PushTargets push = {};
   if (push_in != nullptr) {
     push = *push_in;
     if (push.n < 0 || push.n > MAX_PEERS || push.ld % 8) return "gemm_nt: bad push targets";
+    if (push.seg_rows < 0 || (push.seg_rows > 0 && (push.me < 0 || push.me > push.n ||
+                                                    static_cast<int64_t>(push.seg_rows) * (push.n + 1) < M)))
+      return "gemm_nt: bad reduce-scatter push description";
     for (int q = 0; q < push.n; ++q)
       if (reinterpret_cast<uintptr_t>(push.base[q]) % 16) return "gemm_nt: push targets must be 16-byte aligned";
   }

@@ -346,12 +346,42 @@ __device__ __forceinline__ void row_accumulate_mma(const int* __restrict__ col,
   __syncwarp();
 }
 
+// Peer slot that owns output row `orow` in the reduce-scatter mode (nullptr: this rank owns it).
+// Static indices keep the pointer table in registers.
+template <typename T>
+__device__ __forceinline__ T* scatter_target(const PushTargets& push, int64_t orow, int64_t& slot_row) {
+  const int owner = static_cast<int>(orow / push.seg_rows);
+  if (owner == push.me) return nullptr;
+  const int idx = owner - (owner > push.me ? 1 : 0);
+  void* sel = push.base[0];
+#pragma unroll
+  for (int q = 1; q < MAX_PEERS; ++q)
+    if (idx == q) sel = push.base[q];
+  slot_row = orow - static_cast<int64_t>(owner) * push.seg_rows;
+  return static_cast<T*>(sel);
+}
+
 template <typename T, int LPR, int VPL>
 __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __restrict__ mask_row,
                                           int D, int lane, float (&acc)[VPL][Vec16<T>::N],
                                           const PushTargets& push, int64_t orow) {
   constexpr int VN = Vec16<T>::N;
   if (lane >= LPR) return;
+  if (push.seg_rows > 0) {
+    // reduce-scatter: a row owned by a peer goes only into that peer's receive slot
+    int64_t slot_row = 0;
+    T* peer = scatter_target<T>(push, orow, slot_row);
+    if (peer != nullptr) out_row = peer + slot_row * push.ld;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int c = (v * LPR + lane) * VN;
+      if (c < D) {
+        if (mask_row != nullptr) Vec16<T>::mask(acc[v], ldg16(mask_row + c));
+        *reinterpret_cast<uint4*>(out_row + c) = Vec16<T>::pack(acc[v]);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int v = 0; v < VPL; ++v) {
     const int c = (v * LPR + lane) * VN;
@@ -592,11 +622,12 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
                             int variant, cudaStream_t stream) {
   const bool use_mma = variant == SPMM_VARIANT_TENSOR;
   const int esz = dtype == DT_BF16 ? 2 : 4;
-  PushTargets push;
-  push.n = 0;
+  PushTargets push = {};
   if (push_in != nullptr) {
     push = *push_in;
     if (push.n < 0 || push.n > MAX_PEERS || (push.ld * esz) % 16) return "spmm: bad push targets";
+    if (push.seg_rows < 0 || (push.seg_rows > 0 && (push.me < 0 || push.me > push.n)))
+      return "spmm: bad reduce-scatter push description";
     for (int q = 0; q < push.n; ++q)
       if (reinterpret_cast<uintptr_t>(push.base[q]) % 16) return "spmm: push targets must be 16-byte aligned";
   }

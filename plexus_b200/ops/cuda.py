@@ -142,8 +142,10 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
 
 
 def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None,
-         push_ptrs=(), push_ld=0, variant=None):
+         push_ptrs=(), push_ld=0, variant=None, push_seg=(0, 0)):
     """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
+    ``push_seg = (rows per owner, this rank's position)``: reduce-scatter push (each row goes only
+    to the rank that owns it) instead of the broadcast push.
     ``variant``: 1 = packed-FMA accumulation (default), 0 = warp-MMA accumulation."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
@@ -159,7 +161,7 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
     C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
                sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld),
-               SPMM_VARIANT if variant is None else int(variant))
+               SPMM_VARIANT if variant is None else int(variant), int(push_seg[0]), int(push_seg[1]))
     _count(sch.launches)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
@@ -180,8 +182,9 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
 
 
 def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0,
-         push_ptrs=(), push_ld=0, relu_mask=None):
-    """``relu_mask`` (shape of the result): zero the result where the mask is not positive."""
+         push_ptrs=(), push_ld=0, relu_mask=None, push_seg=(0, 0)):
+    """``relu_mask`` (shape of the result): zero the result where the mask is not positive.
+    ``push_ptrs`` / ``push_seg``: fused-collective epilogue, see :func:`spmm`."""
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas, nb = GEMM_VARIANTS[variant]
@@ -217,7 +220,8 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
     out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
     if relu_mask is not None and relu_mask.dtype != out.dtype:
         relu_mask = relu_mask.to(out.dtype)
-    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask)
+    C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask,
+              int(push_seg[0]), int(push_seg[1]))
     _count(1)
     return out
 

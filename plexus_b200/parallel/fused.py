@@ -1,10 +1,17 @@
 """Collectives carried out by kernels that store into / load from peer memory over NVLink.
 
-* ``spmm_all_reduce`` / ``gemm_all_reduce``: the compute kernel's epilogue writes every result
-  row to the local output *and* into this rank's receive slot on each peer of the axis (plain
-  16-byte stores, overlapped with the rest of the kernel's work); a second launch publishes a
-  flag, waits for the peers' flags and sums the received partials into the output in fp32
-  (ReLU / ReLU-derivative mask applied after the sum).
+* ``spmm_all_reduce`` / ``gemm_all_reduce``, one-shot form (2-rank axes, small messages): the
+  compute kernel's epilogue writes every result row to the local output *and* into this rank's
+  receive slot on each peer of the axis (plain 16-byte stores, overlapped with the rest of the
+  kernel's work); a second launch publishes a flag, waits for the peers' flags and sums the
+  received partials into the output in fp32 (ReLU / ReLU-derivative mask applied after the sum).
+* two-shot form (axes of more than 2 ranks, large messages): the output rows are split in one
+  segment per rank.  The compute kernel's epilogue stores each row only where it is reduced:
+  own rows locally, other rows into the owner's receive slot (a reduce-scatter overlapped with
+  the compute, (p-1)/p of the message per rank over NVLink).  The second launch waits, reduces
+  the own segment in fp32, applies ReLU / the mask and stores the result into every peer's
+  receive slot of the next op; a third launch waits and copies the peers' segments into the
+  output (the all-gather half).  Link traffic equals a ring all-reduce, 2 (p-1)/p x message.
 * ``all_reduce_f32`` (SUM / MAX) and ``all_gather``: push-copy kernel + flagged consumer, used
   for the cross-entropy row statistics, weight shards and weight gradients.
 
@@ -25,16 +32,58 @@ import os
 
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
 
-# The push epilogue is a one-shot all-reduce: every rank sends its whole partial result to every
-# peer, (p-1) x M bytes per rank.  For p = 2 that is the minimum; measured on 4 GPUs it loses to
-# NCCL's bandwidth-optimal ring (2 (p-1)/p x M), so larger groups reduce large messages with NCCL
-# after the compute kernel.  Small messages (latency bound) always use the push path.
+# The one-shot push sends the whole partial result to every peer, (p-1) x M bytes per rank.  For
+# p = 2 that is the minimum; measured on 4 GPUs it loses to a bandwidth-optimal all-reduce
+# (2 (p-1)/p x M), so larger groups use the two-shot form for large bf16 matrices (or, with
+# PLEXUS_TWO_SHOT=0, NCCL after the compute kernel).  Small messages are latency bound and
+# always use the one-shot push.
 ONE_SHOT_MAX_RANKS = int(os.environ.get("PLEXUS_ONE_SHOT_MAX_RANKS", "2"))
 SMALL_MESSAGE_BYTES = 1 << 20
+TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "1") != "0"
 
 
 def _push_path(ax, nbytes: int) -> bool:
     return ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES
+
+
+def _two_shot_path(ax, rows: int, cols: int, dtype) -> bool:
+    return TWO_SHOT and dtype == torch.bfloat16 and cols % 8 == 0 and rows >= ax.p
+
+
+def _segment(ax, rows: int):
+    """Rows per owner and the row range ``[r0, r0 + n)`` of every group rank."""
+    seg = (rows + ax.p - 1) // ax.p
+    ranges = [(min(q * seg, rows), max(0, min(seg, rows - q * seg))) for q in range(ax.p)]
+    return seg, ranges
+
+
+def _two_shot_begin(ax, rows: int, cols: int, esz: int):
+    """Reserve the op of the reduce-scatter half; returns what the compute kernel needs."""
+    seg, ranges = _segment(ax, rows)
+    ax.ensure(seg * cols * esz)
+    epoch, buf = ax.next_op()
+    return seg, ranges, epoch, buf
+
+
+def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
+    """Reduce this rank's segment and broadcast it (op ``epoch``), then land the peers' (next op)."""
+    C = _ext.load()
+    st = opc.status_buffer(out.device)
+    cols, esz = out.shape[1], out.element_size()
+    assert out.stride(0) == cols and out.stride(1) == 1
+    if mask is not None and mask.dtype != out.dtype:
+        mask = mask.to(out.dtype)
+    epoch2, buf2 = ax.next_op()
+    remote, local = ax.sync(buf)
+    r0, n = ranges[ax.rank]
+    C.reduce_segment(out, r0, n, ax.recv_slots(buf), cols, bool(relu), mask, ax.push_targets(buf2),
+                     remote, local, epoch, ax.timeout_ms, kid, st)
+    remote2, local2 = ax.sync(buf2)
+    base = out.data_ptr()
+    C.gather_segments(ax.recv_slots(buf2), [base + ranges[q][0] * cols * esz for q in ax.peers],
+                      [ranges[q][1] * cols * esz for q in ax.peers], remote2, local2, epoch2,
+                      ax.timeout_ms, KID_GATHER, st)
+    opc._count(2)
 
 
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
@@ -49,6 +98,11 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     ax = symm.axis_for(group)
     rows, D = A.shape[0], H.shape[1]
     if not _push_path(ax, rows * D * H.element_size()):
+        if _two_shot_path(ax, rows, D, H.dtype):
+            seg, ranges, epoch, buf = _two_shot_begin(ax, rows, D, H.element_size())
+            out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D, push_seg=(seg, ax.rank))
+            _two_shot_finish(ax, out, seg, ranges, epoch, buf, False, relu_mask, KID_SPMM)
+            return out
         out = opc.spmm(A, H)
         dist.all_reduce(out, group=group)
         return out if relu_mask is None else opc.relu_backward(out, relu_mask)
@@ -67,6 +121,12 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
     rows = a.shape[0]
     N = W.shape[0] if trans_b else W.shape[1]
     if not _push_path(ax, rows * N * a.element_size()):
+        if _two_shot_path(ax, rows, N, a.dtype):
+            seg, ranges, epoch, buf = _two_shot_begin(ax, rows, N, a.element_size())
+            out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
+                           push_seg=(seg, ax.rank))
+            _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, None, KID_GEMM)
+            return out
         out = opc.gemm(a, W, trans_b=trans_b, relu=False)
         dist.all_reduce(out, group=group)
         return torch.relu_(out) if relu else out
@@ -133,6 +193,17 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
         return t
     ax = symm.axis_for(group)
     if not _push_path(ax, t2.numel() * 2):
+        if _two_shot_path(ax, t2.shape[0], t2.shape[1], t2.dtype):
+            # stand-alone two-shot: scatter the rows to their owners with a copy kernel per peer
+            seg, ranges, epoch, buf = _two_shot_begin(ax, t2.shape[0], t2.shape[1], 2)
+            C = _ext.load()
+            for q in ax.peers:
+                r0, n = ranges[q]
+                if n:
+                    C.push_copy(t2[r0 : r0 + n], [ax.slot(q, buf, ax.rank)])
+                    opc._count(1)
+            _two_shot_finish(ax, t2, seg, ranges, epoch, buf, False, None, KID_BARRIER)
+            return t
         dist.all_reduce(t, group=group)
         return t
     ax.ensure(t2.numel() * 2)

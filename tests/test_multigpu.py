@@ -88,7 +88,71 @@ def test_fused_primitives(world):
     run_gpus(_primitives, world)
 
 
-def _model(rank, world, grid, layers):
+def _two_shot_ops(rank, world):
+    """Two-shot (reduce-scatter push + reduce/broadcast + landing) all-reduce against fp32 sums."""
+    import plexus_b200 as plx
+    from plexus_b200.data import graph_ops
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.parallel import fused
+
+    fused.SMALL_MESSAGE_BYTES = 0  # every message takes the large-message path
+    fused.ONE_SHOT_MAX_RANKS = 1   # ... and that path is the two-shot form even on 2 ranks
+    grid = plx.init(world, 1, 1, comm="fused")
+    g = grid.group("x")
+    dev = torch.device("cuda", rank)
+
+    def close(got, want, tag):
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-3, (tag, err)
+
+    # rows not divisible by the group size, an empty last segment (rows=5), interleaved with
+    # one-shot ops of the same axis (both kinds share the op counter and the two buffers)
+    for it, (rows, cols, D) in enumerate([(1003, 777, 64), (5, 40, 8), (4096, 4096, 256), (1003, 777, 104)]):
+        gen = torch.Generator().manual_seed(100 + it)
+        dense = [(torch.rand(rows, cols, generator=gen) < 0.02).float() * torch.randn(rows, cols, generator=gen)
+                 for _ in range(world)]
+        Hs = [torch.randn(cols, D, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        mask = torch.randn(rows, D, generator=gen).to(torch.bfloat16)
+        want = sum(dense[r] @ Hs[r].float() for r in range(world))
+        sp = dense[rank].to_sparse_coo().coalesce()
+        crow, col, val = graph_ops.coo_to_csr(sp.indices()[0].to(dev), sp.indices()[1].to(dev),
+                                              sp.values().to(dev), rows, cols)
+        A = graph_ops.csr_tensor(crow, col, val, (rows, cols))
+        H = Hs[rank].to(dev)
+        close(fused.spmm_all_reduce(A, H, g), want, ("spmm", it))
+        close(fused.spmm_all_reduce(A, H, g, relu_mask=mask.to(dev)), want * (mask.float() > 0), ("spmm mask", it))
+        # one-shot ops in between
+        fused.ONE_SHOT_MAX_RANKS = world
+        s = fused.all_reduce_f32(torch.full((33,), float(rank + 1), device=dev), g)
+        fused.ONE_SHOT_MAX_RANKS = 1
+        assert torch.equal(s.cpu(), torch.full((33,), float(sum(range(1, world + 1))))), it
+        ga = fused.all_gather(torch.full((7,), float(rank), device=dev), g)
+        assert torch.equal(ga.cpu(), torch.arange(world).float().repeat_interleave(7)), it
+        # GEMM: X_r [rows, K] . W_r [K, N]
+        K, N = 64, D
+        Xs = [torch.randn(rows, K, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        Ws = [(torch.randn(K, N, generator=gen) / 8).to(torch.bfloat16) for _ in range(world)]
+        wantg = sum(Xs[r].float() @ Ws[r].float() for r in range(world))
+        close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].to(dev), g), wantg, ("gemm", it))
+        close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].to(dev), g, relu=True), torch.relu(wantg),
+              ("gemm relu", it))
+        close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].t().contiguous().to(dev), g, trans_b=True),
+              wantg, ("gemm nt", it))
+        tb = torch.stack([x.float() for x in Xs]).sum(0)
+        close(fused.all_reduce_bf16(Xs[rank].to(dev).clone(), g), tb, ("bf16", it))
+    torch.cuda.synchronize()
+    opc.check_status()
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_two_shot_all_reduce(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_two_shot_ops, world)
+
+
+def _model(rank, world, grid, layers, force_two_shot=False):
     import plexus_b200 as plx
     from plexus_b200.models.cross_entropy import parallel_cross_entropy
     from plexus_b200.models.net import Net
@@ -96,6 +160,11 @@ def _model(rank, world, grid, layers):
     from plexus_b200.utils.checkpoint import _cut_features, _cut_weight
     from plexus_b200.utils.dataloader import DataLoader
 
+    if force_two_shot:
+        from plexus_b200.parallel import fused
+
+        fused.SMALL_MESSAGE_BYTES = 0
+        fused.ONE_SHOT_MAX_RANKS = 1
     data, nc = small_processed_graph(n=5000, e=60000, f=100, c=47, seed=9)
     results = {}
     for comm in ("nccl", "fused"):
@@ -144,6 +213,18 @@ def test_fused_model_matches_nccl_and_oracle_2gpu(grid):
     if torch.cuda.device_count() < 2:
         pytest.skip("not enough GPUs")
     run_gpus(_model, 2, grid, 3)
+
+
+def test_fused_model_two_shot_2gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("not enough GPUs")
+    run_gpus(_model, 2, (2, 1, 1), 3, True)
+
+
+def test_fused_model_two_shot_4gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    run_gpus(_model, 4, (4, 1, 1), 3, True)
 
 
 @pytest.mark.parametrize("grid", [(4, 1, 1), (2, 1, 2)])
