@@ -283,14 +283,11 @@ def layer_backward(grad_out, AGG, weight, A_t, spec: LayerSpec, input_relu_mask=
         out_dtype=torch.promote_types(weight.dtype, torch.float32),
     )
     timers.stop("GRAD_W = AGG.T * GRAD_OUT")
-    if spec.gather_weights:
-        grad_w = coll.reduce_scatter(grad_w.reshape(-1), dim=0, process_group=spec.depth_group)
-    else:
-        coll.all_reduce(grad_w, spec.depth_group)
-        grad_w = grad_w.reshape(-1)
-    grad_w = grad_w.to(weight.dtype)
+    # the reduction over the depth axis overlaps the rest of this layer's backward
+    pending_w = coll.reduce_grad_async(grad_w.reshape(-1), spec.depth_group, scatter=spec.gather_weights)
 
     if not need_input_grad:
+        grad_w = pending_w.wait().reshape(-1).to(weight.dtype)
         timers.stop("gcn conv bwd")
         return None, grad_w
 
@@ -331,6 +328,7 @@ def layer_backward(grad_out, AGG, weight, A_t, spec: LayerSpec, input_relu_mask=
             grad_x = coll.reduce_scatter(flat, dim=0, process_group=spec.depth_group)
         else:
             coll.all_reduce(grad_x, spec.depth_group)
+    grad_w = pending_w.wait().reshape(-1).to(weight.dtype)
     timers.stop("gcn conv bwd")
     return grad_x, grad_w
 

@@ -127,6 +127,51 @@ def reduce_scatter(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.T
     return out
 
 
+class PendingReduce:
+    """Result of a reduction that may still be in flight; ``wait()`` returns the tensor."""
+
+    def __init__(self, result: torch.Tensor, work=None, finish=None):
+        self._result, self._work, self._finish = result, work, finish
+
+    def wait(self) -> torch.Tensor:
+        if self._work is not None:
+            self._work.wait()  # the current stream waits for the collective's stream
+            self._work = None
+        if self._finish is not None:
+            self._result = self._finish(self._result)
+            self._finish = None
+        return self._result
+
+
+def reduce_grad_async(t: torch.Tensor, process_group=None, scatter: bool = False) -> PendingReduce:
+    """Start ``all_reduce`` (or, with ``scatter``, ``reduce_scatter`` along dim 0) of a gradient.
+
+    On the library path the collective is issued asynchronously on the communicator's own stream,
+    so the kernels launched before ``wait()`` (the rest of a layer's backward) overlap it; the
+    weight gradient is not needed before the optimizer step.  The peer-memory path and
+    single-rank groups complete immediately.
+    """
+    p = group_size(process_group)
+    if p == 1:
+        return PendingReduce(t)
+    if _fused(t) or t.device.type == "cpu" or get_timers().enabled:
+        # in-line: peer-memory kernels are stream-ordered already; timed runs keep the
+        # collective inside its own timer region
+        return PendingReduce(reduce_scatter(t, 0, process_group) if scatter else all_reduce(t, process_group))
+    t = t.contiguous()
+    if scatter:
+        if t.shape[0] % p != 0:
+            raise ValueError(f"reduce_scatter: leading size {t.shape[0]} not divisible by {p}")
+        _bytes_moved["reduce-scatter"] += t.numel() * t.element_size()
+        out = torch.empty((t.shape[0] // p,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        work = dist.reduce_scatter_tensor(out, t, group=process_group, async_op=True)
+        # keep the input alive until the collective has consumed it
+        return PendingReduce(out, work, finish=lambda r, _keep=t: r)
+    _bytes_moved["all-reduce"] += t.numel() * t.element_size()
+    work = dist.all_reduce(t, group=process_group, async_op=True)
+    return PendingReduce(t, work)
+
+
 # Names used by code written against AxoNN's intra-layer communication module.
 _gather = all_gather
 _all_reduce = all_reduce
