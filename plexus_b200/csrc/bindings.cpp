@@ -465,6 +465,26 @@ Tensor relu_dropout(const Tensor& x, const c10::optional<Tensor>& grad, double p
   return out;
 }
 
+void weight_init_shard(Tensor& out, int64_t flat_offset, int64_t local_cols, int64_t row0, int64_t col0,
+                       int64_t in_ch, int64_t out_ch, int64_t seed, int64_t stream_id, double bound) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(out.device());
+  check(plx::launch_weight_init_shard(out.data_ptr<float>(), out.numel(), flat_offset,
+                                      static_cast<int>(local_cols), static_cast<int>(row0),
+                                      static_cast<int>(col0), static_cast<int>(in_ch), static_cast<int>(out_ch),
+                                      static_cast<uint64_t>(seed), static_cast<uint64_t>(stream_id),
+                                      static_cast<float>(bound), stream()));
+}
+
+void csr_validate(const Tensor& rowptr, const Tensor& col, int64_t nrows, int64_t ncols, const Tensor& status) {
+  TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && rowptr.is_contiguous() && col.is_contiguous());
+  TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt, "csr_validate: int32 indices");
+  TORCH_CHECK(rowptr.numel() == nrows + 1, "csr_validate: rowptr must have nrows + 1 entries");
+  c10::cuda::CUDAGuard guard(col.device());
+  check(plx::launch_csr_validate(rowptr.data_ptr<int>(), col.data_ptr<int>(), nrows, ncols, col.numel(),
+                                 status_ptr(status), stream()));
+}
+
 #ifdef PLX_GEMM_PROF
 }  // namespace
 namespace plx { void gemm_prof_dump(long long* host); }
@@ -499,6 +519,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gcn_norm", &gcn_norm);
   m.def("coo_to_csr", &coo_to_csr);
   m.def("relu_dropout", &relu_dropout);
+  m.def("weight_init_shard", &weight_init_shard);
+  m.def("csr_validate", &csr_validate);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_slots_f32", &reduce_slots_f32);
   m.def("reduce_segment", &reduce_segment);

@@ -164,6 +164,15 @@ const char* launch_coo_to_csr(const int64_t* row, const int64_t* col, const floa
 const char* launch_relu_dropout(int dtype, bool backward, const void* x, const void* g, void* out, int64_t n,
                                 double p, uint64_t seed, int64_t index_offset, cudaStream_t stream);
 
+// out[i] (fp32, i < n) = entry flat_offset + i of the row-major local block [.., local_cols] at
+// (row0, col0) of the zero-padded Kaiming-uniform weight; a pure function of (seed, stream_id, r, c).
+const char* launch_weight_init_shard(float* out, int64_t n, int64_t flat_offset, int local_cols, int row0,
+                                     int col0, int in_ch, int out_ch, uint64_t seed, uint64_t stream_id,
+                                     float bound, cudaStream_t stream);
+// Checks rowptr[0..nrows] / col[0..nnz) of an int32 CSR matrix; violations go to the status words.
+const char* launch_csr_validate(const int* rowptr, const int* col, int64_t nrows, int64_t ncols, int64_t nnz,
+                                int* status, cudaStream_t stream);
+
 inline const char* last_launch_error() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

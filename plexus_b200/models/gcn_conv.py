@@ -442,19 +442,55 @@ class GCNStackFunction(torch.autograd.Function):
         return (None, None, grad_x, *grad_ws)
 
 
+WEIGHT_STREAM = 500  # hash stream of layer l is WEIGHT_STREAM + l
+
+
+def _weight_seed(seed: Optional[int]) -> int:
+    return (torch.initial_seed() if seed is None else seed) % (1 << 62)
+
+
 def init_full_weight(in_channels: int, out_channels: int, layer_num: int, seed: Optional[int] = None):
     """Kaiming-uniform (a=sqrt(5)) ``[in, out]`` matrix, identical on every rank and grid.
 
-    ``fan_in`` is the number of input channels, so the bound is
-    ``1/sqrt(in_channels)``.  The matrix is drawn on the host from a generator
-    keyed by (seed, layer), which makes the values independent of the grid
-    shape and lets each rank keep only its shard.
+    ``fan_in`` is the number of input channels, so the bound is ``1/sqrt(in_channels)``.  Entry
+    ``(r, c)`` is a counter-based hash of ``(seed, layer, r * out + c)``: the values do not depend
+    on the grid shape, and a rank can produce just its shard (:func:`init_weight_shard`).
     """
-    gen = torch.Generator(device="cpu")
-    base = torch.initial_seed() if seed is None else seed
-    gen.manual_seed((base * 1000003 + layer_num * 7919 + 12345) % (2**63 - 1))
+    from ..data.synthetic import uniform01
+
     bound = 1.0 / math.sqrt(in_channels) if in_channels > 0 else 0.0
-    return (torch.rand(in_channels, out_channels, generator=gen) * 2.0 - 1.0) * bound
+    idx = torch.arange(in_channels * out_channels, dtype=torch.int64)
+    u = uniform01(_weight_seed(seed), WEIGHT_STREAM + layer_num, idx)
+    return ((u * 2.0 - 1.0) * bound).reshape(in_channels, out_channels)
+
+
+def init_weight_shard(in_channels: int, out_channels: int, layer_num: int, seed: Optional[int],
+                      row0: int, col0: int, local_cols: int, flat_start: int, flat_count: int,
+                      device) -> torch.Tensor:
+    """``flat_count`` entries, starting at ``flat_start``, of the row-major local block
+    ``[.., local_cols]`` whose corner is ``(row0, col0)`` of the zero-padded weight matrix.
+
+    Only the shard is ever materialised (on the device by one kernel); the reference draws the
+    full matrix on every rank and slices it (plexus/gcn_conv.py:332-390).
+    """
+    device = torch.device(device)
+    bound = 1.0 / math.sqrt(in_channels) if in_channels > 0 else 0.0
+    if device.type == "cuda":
+        from ..ops import _ext
+        from ..ops import cuda as opc
+
+        out = torch.empty(flat_count, dtype=torch.float32, device=device)
+        _ext.load().weight_init_shard(out, flat_start, local_cols, row0, col0, in_channels, out_channels,
+                                      _weight_seed(seed), WEIGHT_STREAM + layer_num, bound)
+        opc._count(1)
+        return out
+    from ..data.synthetic import uniform01
+
+    f = torch.arange(flat_start, flat_start + flat_count, dtype=torch.int64)
+    r, c = row0 + f // local_cols, col0 + f % local_cols
+    valid = (r < in_channels) & (c < out_channels)
+    u = uniform01(_weight_seed(seed), WEIGHT_STREAM + layer_num, torch.where(valid, r * out_channels + c, 0))
+    return torch.where(valid, (u * 2.0 - 1.0) * bound, torch.zeros(()))
 
 
 class GCNConv(torch.nn.Module):
@@ -516,21 +552,26 @@ class GCNConv(torch.nn.Module):
         self.w_col_rank = 0 if self.combine_first else self.outer_rank
         self.local_weight_cols = self.out_channels // self.w_col_parts
 
-        full = init_full_weight(in_channels, out_channels, layer_num, seed)
-        block = shard_2d(
-            torch.nn.functional.pad(
-                full, (0, self.out_channels - out_channels, 0, self.in_channels - in_channels)
-            ),
-            self.inner_group_size, self.inner_rank, self.w_col_parts, self.w_col_rank,
-        )
-        flat = block.contiguous().reshape(-1)
-        if self.gather_weights:
-            flat = depth_slice(flat, self.depth_group_size, self.depth_rank)
         if device is None:
             from ..parallel.grid import default_device
 
             device = default_device()
-        self.weight = Parameter(flat.clone().to(device), requires_grad=True)
+        # this rank's flat shard is generated directly: rows by inner rank, columns by outer rank
+        # (or all of them), row-major, and of that the depth rank's contiguous slice
+        block_elems = self.local_in_channels * self.local_weight_cols
+        if self.gather_weights:
+            if block_elems % self.depth_group_size:
+                raise ValueError(f"cannot split {block_elems} weight elements in {self.depth_group_size} depth slices")
+            per = block_elems // self.depth_group_size
+            flat_start, flat_count = self.depth_rank * per, per
+        else:
+            flat_start, flat_count = 0, block_elems
+        flat = init_weight_shard(
+            in_channels, out_channels, layer_num, seed,
+            row0=self.inner_rank * self.local_in_channels, col0=self.w_col_rank * self.local_weight_cols,
+            local_cols=self.local_weight_cols, flat_start=flat_start, flat_count=flat_count, device=device,
+        )
+        self.weight = Parameter(flat, requires_grad=True)
 
     def spec(self, edge_index, relu: Optional[bool] = None) -> LayerSpec:
         return LayerSpec(

@@ -8,6 +8,8 @@ from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
 
+import os
+
 import torch
 
 from . import _ext
@@ -141,6 +143,20 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
     return sch
 
 
+DEBUG = os.environ.get("PLEXUS_DEBUG", "0") not in ("", "0")
+
+
+def validate_csr(A) -> None:
+    """Check the structure of a sparse CSR shard on the device (row pointers start at 0, are
+    monotone and end at nnz; every column index is inside the matrix).  Raises ``RuntimeError``
+    naming the first violation.  Runs automatically once per matrix when ``PLEXUS_DEBUG=1``."""
+    crow, col, _ = _csr_parts(A)
+    st = status_buffer(col.device)
+    _ext.load().csr_validate(crow, col, A.shape[0], A.shape[1], st)
+    _count(1)
+    check_status(col.device)
+
+
 def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None,
          push_ptrs=(), push_ld=0, variant=None, push_seg=(0, 0)):
     """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
@@ -150,6 +166,16 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
+    if H.shape[0] < A.shape[1]:
+        raise ValueError(f"spmm: dense operand has {H.shape[0]} rows, the sparse one {A.shape[1]} columns")
+    if not 0 <= r0 <= r1 <= A.shape[0]:
+        raise ValueError(f"spmm: row range {(r0, r1)} outside the matrix")
+    if DEBUG and not getattr(A, "_plx_validated", False):
+        validate_csr(A)
+        try:
+            A._plx_validated = True
+        except AttributeError:
+            pass
     if H.stride(-1) != 1:
         H = H.contiguous()
     if out is None:

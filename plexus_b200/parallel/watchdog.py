@@ -173,7 +173,7 @@ class EpochWatchdog:
 
 _KERNEL_NAMES = {
     1: "spmm_all_reduce", 2: "gemm_all_reduce", 3: "all_gather", 4: "barrier", 5: "xent_exchange",
-    6: "gemm (mbarrier)", 7: "wait_flag_probe",
+    6: "gemm (mbarrier)", 7: "wait_flag_probe", 8: "csr_validate",
 }
 
 

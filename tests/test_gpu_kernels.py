@@ -289,3 +289,41 @@ def test_gemm_nt_relu_derivative_mask_in_epilogue(out_dtype):
     assert out.dtype == out_dtype
     assert (out.float().cpu() - ref).abs().max() < 1e-2 * ref.abs().max()
     assert torch.equal(out.float().cpu() == 0, ref == 0)
+
+
+def test_csr_validate_reports_bad_structure_without_touching_memory_through_it():
+    """The validator reads only the index arrays themselves; a bad index ends in a status word."""
+    from plexus_b200.ops import cuda as opc
+
+    A = _random_csr(500, 300, 6.0, seed=4).to(_dev())
+    opc.validate_csr(A)  # a well-formed matrix passes
+    crow, col, val = A.crow_indices().clone(), A.col_indices().clone(), A.values()
+    bad_col = col.clone()
+    bad_col[17] = 300  # one past the last column
+    B = torch.sparse_csr_tensor(crow, bad_col, val, size=(500, 300), check_invariants=False)
+    with pytest.raises(RuntimeError, match="csr_validate"):
+        opc.validate_csr(B)
+    bad_crow = crow.clone()
+    bad_crow[200] = bad_crow[201] + 1  # not monotone
+    Cm = torch.sparse_csr_tensor(bad_crow, col, val, size=(500, 300), check_invariants=False)
+    with pytest.raises(RuntimeError, match="csr_validate"):
+        opc.validate_csr(Cm)
+    opc.validate_csr(A)  # the status was cleared, the context is fine
+    # host-side shape checks of the SpMM wrapper
+    with pytest.raises(ValueError):
+        opc.spmm(A, torch.zeros(299, 8, dtype=torch.bfloat16, device=_dev()))
+
+
+def test_weight_shard_kernel_equals_the_host_hash():
+    from plexus_b200.models.gcn_conv import init_full_weight, init_weight_shard
+
+    in_ch, out_ch, layer, seed = 100, 47, 1, 3
+    full = torch.nn.functional.pad(init_full_weight(in_ch, out_ch, layer, seed), (0, 1, 0, 4))  # 104 x 48
+    lr, lc = 52, 24
+    for i in range(2):
+        for o in range(2):
+            block = full[i * lr:(i + 1) * lr, o * lc:(o + 1) * lc].reshape(-1)
+            for d in range(2):
+                per = block.numel() // 2
+                got = init_weight_shard(in_ch, out_ch, layer, seed, i * lr, o * lc, lc, d * per, per, _dev())
+                assert torch.equal(got.cpu(), block[d * per:(d + 1) * per]), (i, o, d)

@@ -109,3 +109,29 @@ def test_extract_local_params_single_rank():
     w = torch.randn(6, 4)
     flat = extract_local_params_from_full_params(w, None, None, None)
     assert torch.equal(flat, w.reshape(-1))
+
+
+def test_weight_shard_init_equals_slices_of_the_full_matrix():
+    """Every (row block, column block, depth slice) generated on its own equals the slice of the
+    zero-padded full matrix; values do not depend on how the matrix is cut."""
+    import torch
+    from plexus_b200.models.gcn_conv import init_full_weight, init_weight_shard
+
+    in_ch, out_ch, layer, seed = 100, 47, 2, 11
+    full = init_full_weight(in_ch, out_ch, layer, seed)
+    assert full.shape == (in_ch, out_ch)
+    bound = 1.0 / in_ch ** 0.5
+    assert full.abs().max() <= bound and full.std() > 0.4 * bound
+    assert not torch.equal(full, init_full_weight(in_ch, out_ch, layer + 1, seed))
+    for inner, outer, depth in [(1, 1, 1), (2, 2, 2), (4, 1, 2), (1, 8, 1)]:
+        pin = -(-in_ch // (inner * depth * 8)) * inner * depth * 8
+        pout = -(-out_ch // (outer * 8)) * outer * 8
+        padded = torch.nn.functional.pad(full, (0, pout - out_ch, 0, pin - in_ch))
+        lr, lc = pin // inner, pout // outer
+        for i in range(inner):
+            for o in range(outer):
+                block = padded[i * lr:(i + 1) * lr, o * lc:(o + 1) * lc].reshape(-1)
+                per = block.numel() // depth
+                for d in range(depth):
+                    got = init_weight_shard(in_ch, out_ch, layer, seed, i * lr, o * lc, lc, d * per, per, "cpu")
+                    assert torch.equal(got, block[d * per:(d + 1) * per]), (inner, outer, depth, i, o, d)
