@@ -5,7 +5,8 @@
   receive slot on each peer of the axis (plain 16-byte stores, overlapped with the rest of the
   kernel's work); a second launch publishes a flag, waits for the peers' flags and sums the
   received partials into the output in fp32 (ReLU / ReLU-derivative mask applied after the sum).
-* two-shot form (axes of more than 2 ranks, large messages): the output rows are split in one
+* two-shot form (opt-in for axes of more than 2 ranks and large messages; by default those are
+  reduced by NCCL after the compute kernel, which measured faster): the output rows are split in one
   segment per rank.  The compute kernel's epilogue stores each row only where it is reduced:
   own rows locally, other rows into the owner's receive slot (a reduce-scatter overlapped with
   the compute, (p-1)/p of the message per rank over NVLink).  The second launch waits, reduces
@@ -33,13 +34,17 @@ import os
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
 
 # The one-shot push sends the whole partial result to every peer, (p-1) x M bytes per rank.  For
-# p = 2 that is the minimum; measured on 4 GPUs it loses to a bandwidth-optimal all-reduce
-# (2 (p-1)/p x M), so larger groups use the two-shot form for large bf16 matrices (or, with
-# PLEXUS_TWO_SHOT=0, NCCL after the compute kernel).  Small messages are latency bound and
-# always use the one-shot push.
+# p = 2 that is the minimum.  On larger groups a bandwidth-optimal all-reduce moves 2 (p-1)/p x M;
+# measured on 1M x 256 bf16 (512 MB) messages:
+#     ranks   one-shot   two-shot   NCCL after the compute kernel      (SpMM+AR / GEMM+AR, ms)
+#       4     3.56/2.68  2.63/1.84  2.64/1.59
+#       8     7.32/6.01  3.16/2.72  2.79/1.81
+# so groups of more than two ranks reduce large messages with NCCL after the compute kernel by
+# default, and the two-shot form is opt-in (PLEXUS_TWO_SHOT=1).  Small messages are latency
+# bound and always use the one-shot push.
 ONE_SHOT_MAX_RANKS = int(os.environ.get("PLEXUS_ONE_SHOT_MAX_RANKS", "2"))
 SMALL_MESSAGE_BYTES = 1 << 20
-TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "1") != "0"
+TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 
 
 def _push_path(ax, nbytes: int) -> bool:

