@@ -204,7 +204,7 @@ def _model(rank, world, grid, layers, force_two_shot=False):
     # the peer-memory path sums in fp32 and rounds once; NCCL's bf16 ring rounds at every step.
     # The fused result must be about as close to the oracle as NCCL's ...
     for ef, en in zip(err["fused"], err["nccl"]):
-        assert ef < max(2.0 * en, 5e-2), (err["fused"], err["nccl"])
+        assert ef < max(3.0 * en, 0.1), (err["fused"], err["nccl"])
     assert abs(a["loss"] - b["loss"]) < 5e-3 * abs(a["loss"]), (a["loss"], b["loss"])
     # ... and on 2-rank groups (same number of roundings) the two paths agree closely
     if max(grid) <= 2:
