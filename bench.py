@@ -51,6 +51,9 @@ def parse_args():
     p.add_argument("--classes", type=int, default=CONFIG["classes"])
     p.add_argument("--layers", type=int, default=CONFIG["layers"])
     p.add_argument("--no_e2e", action="store_true")
+    p.add_argument("--sharded_data", action="store_true",
+                   help="every rank generates only its own shards; --edges then counts raw generator edges "
+                        "before de-duplication (for graphs whose global edge list does not fit one GPU)")
     p.add_argument("--timers", action="store_true", help="print the per-region timer tree once")
     return p.parse_args()
 
@@ -223,10 +226,19 @@ def run_ours(args):
     plx.init(*grid, gpus_per_node=torch.cuda.device_count(), enable_internal_timers=args.timers, comm=comm)
     device = torch.device("cuda", local)
 
-    data = make_graph(args, device)
-    nnz = int(data.edge_index.shape[1])
-    adj, features, labels, N, F, C = DataLoader(None, args.layers, data=(data, args.classes)).load()
-    del data
+    if args.sharded_data:
+        from plexus_b200.data.sharded_synthetic import ShardedSyntheticGraph
+
+        src = ShardedSyntheticGraph(args.nodes, args.edges, args.features, args.classes, seed=args.seed,
+                                    kind="rmat", device=device)
+        adj, features, labels, N, F, C = DataLoader(None, args.layers, source=src).load()
+        nnz = int(src.nnz_total)
+        del src
+    else:
+        data = make_graph(args, device)
+        nnz = int(data.edge_index.shape[1])
+        adj, features, labels, N, F, C = DataLoader(None, args.layers, data=(data, args.classes)).load()
+        del data
     torch.cuda.empty_cache()
     model = Net(args.layers, F, args.hidden, C, seed=args.seed)
     opt = FusedAdamW(list(model.parameters()) + [features], lr=3e-3, weight_decay=0.0)

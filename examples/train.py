@@ -62,6 +62,10 @@ def create_parser():
     parser.add_argument("--dtype", type=str, default=None, choices=["bf16", "fp32"])
     parser.add_argument("--synthetic", type=str, default=None,
                         help="nodes,undirected_edges,features,classes[,kind] instead of --data_dir")
+    parser.add_argument("--sharded_synthetic", action="store_true", default=False,
+                        help="with --synthetic: every rank generates only its own shards (the edge count "
+                             "is then the number of raw generator edges before de-duplication); for graphs "
+                             "whose global edge list does not fit one device")
     parser.add_argument("--single_perm", action="store_true", default=False)
     parser.add_argument("--checkpoint_dir", type=str, default=None)
     parser.add_argument("--checkpoint_every", type=int, default=0)
@@ -140,7 +144,14 @@ def main(argv=None):
         device=None if use_cuda else "cpu",
     )
 
-    if synthetic is not None:
+    if synthetic is not None and args.sharded_synthetic:
+        from plexus_b200.data.sharded_synthetic import ShardedSyntheticGraph
+
+        n, e, f, c, kind = synthetic
+        dev = torch.device("cuda", torch.cuda.current_device()) if use_cuda else "cpu"
+        loader = DataLoader(None, args.num_gcn_layers,
+                            source=ShardedSyntheticGraph(n, e, f, c, seed=args.seed, kind=kind, device=dev))
+    elif synthetic is not None:
         from plexus_b200.data.synthetic import synthetic_graph
         from plexus_b200.utils.dataset import preprocess_data
 

@@ -43,6 +43,7 @@ class DataLoader:
         num_gcn_layers: int,
         *,
         data: Optional[Tuple[object, int]] = None,
+        source=None,
         device: Optional[torch.device] = None,
         dtype: Optional[torch.dtype] = None,
         keep_masks: bool = True,
@@ -52,10 +53,13 @@ class DataLoader:
             data_dir: directory with one processed ``.pt`` file or a partition tree
             num_gcn_layers: number of GCN layers in the model
             data: optional in-memory ``(data, num_classes)`` instead of files
+            source: optional generator object (``data.sharded_synthetic.ShardedSyntheticGraph``)
+                that produces this rank's blocks directly; no global edge list exists then
         """
         self.data_dir = data_dir
         self.num_gcn_layers = num_gcn_layers
         self._in_memory = data
+        self.source = source
         self.device = device if device is not None else default_device()
         self.dtype = dtype if dtype is not None else runtime.flags.dtype
         self.keep_masks = keep_masks
@@ -63,7 +67,9 @@ class DataLoader:
         self.symmetric = False
         self.partitioned = False
         self.double_perm = False
-        if data is None:
+        if source is not None:
+            self.double_perm = bool(source.double_perm)
+        elif data is None:
             self.partitioned = os.path.exists(os.path.join(data_dir, "metadata.pt"))
             self.double_perm = os.path.exists(os.path.join(data_dir, "edge_index", "1"))
             self.labels_dir = os.path.join(data_dir, "output_labels")
@@ -219,7 +225,12 @@ class DataLoader:
         self._edge_cache: Dict[int, tuple] = {}
         self._csr_cache: Dict[tuple, torch.Tensor] = {}
         with torch.no_grad():
-            if self.partitioned:
+            if self.source is not None:
+                src = self.source
+                self.num_nodes, self.num_features, self.num_classes = src.num_nodes, src.num_features, src.num_classes
+                self.symmetric, self.double_perm = bool(src.symmetric), bool(src.double_perm)
+                self.data = None
+            elif self.partitioned:
                 self.num_nodes, self.num_features, self.num_classes = torch.load(
                     os.path.join(self.data_dir, "metadata.pt"), weights_only=False
                 )
@@ -246,7 +257,16 @@ class DataLoader:
             # edge list is resident on the device at a time
             order = sorted(range(n_shards), key=lambda i: (i % 2 if self.double_perm else 0, i))
             pairs = {}
-            if self.symmetric and self.double_perm:
+            if self.source is not None:
+                # every block this rank needs, generated in one pass over the raw edge stream
+                need = []
+                for i in range(n_shards):
+                    v = i % 2 if self.double_perm else 0
+                    r0, r1, c0, c1 = self.adj_ranges[i % 3]
+                    need.append((v, r0, r1, c0, c1))
+                    need.append(((1 - v) if self.double_perm else v, c0, c1, r0, r1))  # its transpose
+                self._csr_cache.update(self.source.build_blocks(need))
+            elif self.symmetric and self.double_perm:
                 # both members of a pair come from different versions; warm the
                 # cache version by version
                 for v in (0, 1):
@@ -262,7 +282,19 @@ class DataLoader:
             self._edge_cache = {}
 
             use_second = self.double_perm and self.num_gcn_layers % 2 == 0
-            if self.partitioned:
+            if self.source is not None:
+                src = self.source
+                x = src.feature_block(self.nodes_start, self.nodes_stop, self.features_start, self.features_stop)
+                features = self._feature_shard(x, (self.nodes_start, self.features_start))
+                del x
+                ver = 1 if use_second else 0
+                labels = self._label_shard(src.labels(ver, self.labels_start, self.labels_stop), self.labels_start)
+                if self.keep_masks:
+                    n = self.labels_stop - self.labels_start
+                    for m in ("train_mask", "val_mask", "test_mask"):
+                        loc = src.mask(m, ver, self.labels_start, self.labels_stop)
+                        self.masks[m] = F.pad(loc, (0, n - loc.shape[0]), value=False).to(self.device)
+            elif self.partitioned:
                 x, origin = self._load_feature_blocks()
                 features = self._feature_shard(x, origin)
                 y, yo = self._load_label_blocks(1 if use_second else 0)

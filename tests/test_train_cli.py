@@ -64,3 +64,13 @@ def test_resume_from_checkpoint_and_auto_grid(tmp_path):
     out = _run(["--synthetic", "600,4000,12,4", "--grid", "auto", "--num_epochs", "1", "--dtype", "fp32"], 2,
                tmp_path, 29616)
     assert "cost models chose grid" in out
+
+
+def test_rank_local_synthetic_shards_train_like_one_process(tmp_path):
+    """--sharded_synthetic: no rank builds the global graph, yet 4 ranks follow the 1-rank losses."""
+    base = ["--synthetic", "900,6000,12,5", "--sharded_synthetic", "--num_gcn_layers", "3", "--hidden_size", "16",
+            "--seed", "3", "--dtype", "fp32", "--num_epochs", "3", "--lr", "0.01"]
+    one = _losses(_run(base, 1, tmp_path, 29617))
+    four = _losses(_run(base + ["--G_intra_r", "2", "--G_intra_d", "2"], 4, tmp_path, 29618))
+    assert len(one) == len(four) == 3
+    assert all(abs(a - b) <= 2e-4 for a, b in zip(one, four)), (one, four)
