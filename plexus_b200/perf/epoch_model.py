@@ -1,0 +1,144 @@
+"""Epoch-time model of this framework on one NVSwitch box of B200s, per region.
+
+The reference's three models (communication volume, SpMM shape penalty, memory; reference:
+performance/comm_model.py, comp_model.py, mem_model.py) rank grids without predicting a time.
+This model walks the same per-layer schedule the layers execute (``models/gcn_conv.py``) and prices
+every kernel and collective with constants measured on B200 (CUDA events, bf16):
+
+* SpMM: ``nnz * (16.2 ps + 0.0709 ps per byte of a gathered row)`` - a fit through the measured
+  2.84 / 4.20 / 6.48 ms of the 123.7M-nonzero product at 48 / 104 / 256 columns (issue-bound floor
+  per nonzero plus an L2-assisted 14 TB/s gather);
+* tcgen05 GEMMs: operand + result bytes at 0.85 of the measured HBM copy bandwidth;
+* fused all-reduce on a 2-rank axis: the push overlaps the compute kernel
+  (``max(compute, bytes / 680 GB/s)``), the slot-reduce kernel moves 3 x message bytes through HBM;
+* larger axes: NCCL after the compute kernel at a measured bus bandwidth of 585 GB/s (NVLS off);
+  messages up to 1 MiB use the one-shot push (latency only);
+* all-gather: ``(p-1)/p`` of the gathered bytes at the push rate plus the landing copy;
+* cross-entropy and Adam: measured cost per element;
+* every collective pays a launch + flag latency.
+
+``predict_epoch_ms`` returns the regions and their sum; ``tests/test_perf_models.py`` pins it to the
+measured epochs (33.2 ms on 1 GPU, 24.95 on 2, 17.5 on 4, 11.04 / 12.85 on 8) within 20 %.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Sequence, Tuple
+
+from .comm_model import load_measured_peaks
+from .common import DEPTH, INNER, OUTER, split_into_three_powers_of_two
+
+SPMM_PS_PER_NNZ = 16.2
+SPMM_PS_PER_BYTE = 0.0709
+GEMM_HBM_FRACTION = 0.85
+PUSH_GBS = 680.0            # achieved rate of epilogue stores into a peer's memory
+NCCL_BUS_GBS = 585.0        # all-reduce bus bandwidth on 4- and 8-rank axes, 512 MB messages
+SMALL_MESSAGE_BYTES = 1 << 20
+COLLECTIVE_LATENCY_MS = 0.02
+XENT_PS_PER_ELEM = 6.8      # 0.8 ms for 2.45M rows x 48 classes
+ADAM_PS_PER_ELEM = 4.4      # 1.12 ms for 255M bf16 elements with fp32 master and moments
+ELEM = 2                    # bf16
+
+
+def _pad(v: int, m: int) -> int:
+    return -(-v // m) * m
+
+
+def _spmm_ms(nnz: float, row_elems: float) -> float:
+    return nnz * (SPMM_PS_PER_NNZ + SPMM_PS_PER_BYTE * row_elems * ELEM) * 1e-9
+
+
+def _gemm_ms(m: float, k: float, n: float, hbm_gbs: float, out_bytes: int = ELEM) -> float:
+    return (m * k * ELEM + k * n * ELEM + m * n * out_bytes) / (GEMM_HBM_FRACTION * hbm_gbs * 1e9) * 1e3
+
+
+def _all_reduce_ms(p: int, elems: float, compute_ms: float, hbm_gbs: float) -> Tuple[float, float]:
+    """``(time of compute + all-reduce, exposed communication)`` for a fused op on a ``p``-rank axis."""
+    if p == 1:
+        return compute_ms, 0.0
+    nbytes = elems * ELEM
+    if p == 2 or nbytes <= SMALL_MESSAGE_BYTES:
+        link = (p - 1) * nbytes / (PUSH_GBS * 1e9) * 1e3
+        reduce_ms = (p + 1) * nbytes / (hbm_gbs * 1e9) * 1e3
+        total = max(compute_ms, link) + reduce_ms + COLLECTIVE_LATENCY_MS
+    else:
+        total = compute_ms + 2 * (p - 1) / p * nbytes / (NCCL_BUS_GBS * 1e9) * 1e3 + COLLECTIVE_LATENCY_MS
+    return total, total - compute_ms
+
+
+def _gather_ms(p: int, elems_total: float, hbm_gbs: float) -> float:
+    if p == 1:
+        return 0.0
+    nbytes = elems_total * ELEM
+    return ((p - 1) / p * nbytes / (PUSH_GBS * 1e9) + 2 * (p - 1) / p * nbytes / (hbm_gbs * 1e9)) * 1e3 \
+        + COLLECTIVE_LATENCY_MS
+
+
+def predict_epoch_ms(grid: Sequence[int], N: int, NNZ: int, D_list: List[int], align: int = 8,
+                     hbm_gbs: float = None) -> Dict[str, float]:
+    """Predicted milliseconds per region of one training epoch (forward, backward, loss, Adam)."""
+    X, Y, Z = grid
+    sizes = {"X": X, "Y": Y, "Z": Z}
+    G = X * Y * Z
+    hbm = hbm_gbs or load_measured_peaks().get("hbm_gbs", 6555.0)
+    L = len(D_list) - 1
+    r: Dict[str, float] = {"spmm": 0.0, "gemm": 0.0, "wgrad": 0.0, "exposed_comm": 0.0, "gather": 0.0,
+                           "xent": 0.0, "adam": 0.0}
+    for i in range(L):
+        po, pn, pd = sizes[OUTER[i % 3]], sizes[INNER[i % 3]], sizes[DEPTH[i % 3]]
+        d_in = _pad(D_list[i], pn * (pd if i == 0 else 1) * align) / pn      # local input width
+        d_out_full = _pad(D_list[i + 1], po * align)
+        d_out = d_out_full / po                                              # local output width
+        nnz = NNZ / (pd * po)
+        rows_d, rows_o = N / pd, N / po
+        combine_first = i > 0 and d_out_full < d_in
+        if i == 0:
+            r["gather"] += _gather_ms(pd, rows_o * d_in, hbm)
+        r["gather"] += 2 * (COLLECTIVE_LATENCY_MS if pd > 1 else 0.0)      # weight shards, fwd + bwd
+        if not combine_first:
+            for rows, p in ((rows_d, po), (rows_o, pd)):                      # A.H and A^T.gradAGG
+                t = _spmm_ms(nnz, d_in)
+                total, exposed = _all_reduce_ms(p, rows * d_in, t, hbm)
+                r["spmm"] += t
+                r["exposed_comm"] += exposed
+            t = _gemm_ms(rows_d, d_in, d_out, hbm)                            # OUT = AGG.W
+            total, exposed = _all_reduce_ms(pn, rows_d * d_out, t, hbm)
+            r["gemm"] += t
+            r["exposed_comm"] += exposed
+            t = _gemm_ms(rows_d, d_out, d_in, hbm)                            # gradAGG = gradOUT.W^T
+            total, exposed = _all_reduce_ms(po, rows_d * d_in, t, hbm)
+            r["gemm"] += t
+            r["exposed_comm"] += exposed
+            r["wgrad"] += _gemm_ms(rows_d, d_in, 0, hbm) + _gemm_ms(rows_d, d_out, 0, hbm)
+        else:
+            t = _gemm_ms(rows_o, d_in, d_out_full, hbm)                       # T = H.W
+            total, exposed = _all_reduce_ms(pn, rows_o * d_out_full, t, hbm)
+            r["gemm"] += t
+            r["exposed_comm"] += exposed
+            for rows, p in ((rows_d, po), (rows_o, pd)):                      # A.T and A^T.gradU
+                t = _spmm_ms(nnz, d_out_full)
+                total, exposed = _all_reduce_ms(p, rows * d_out_full, t, hbm)
+                r["spmm"] += t
+                r["exposed_comm"] += exposed
+            r["gather"] += _gather_ms(po, rows_d * d_out_full, hbm)           # gradOUT column blocks
+            r["gemm"] += _gemm_ms(rows_o, d_out_full, d_in, hbm)              # gradH = gradT.W^T
+            r["wgrad"] += _gemm_ms(rows_o, d_in, 0, hbm) + _gemm_ms(rows_o, d_out_full, 0, hbm)
+        if pd > 1 or (combine_first and po > 1):
+            r["exposed_comm"] += COLLECTIVE_LATENCY_MS                        # weight-gradient reduction
+    # loss on the last layer's output layout
+    po, pd = sizes[OUTER[(L - 1) % 3]], sizes[DEPTH[(L - 1) % 3]]
+    c_local = _pad(D_list[-1], po * align) / po
+    r["xent"] = (N / pd) * c_local * XENT_PS_PER_ELEM * 1e-9 + (3 * COLLECTIVE_LATENCY_MS if po > 1 else 0.0) \
+        + (COLLECTIVE_LATENCY_MS if pd > 1 else 0.0)
+    # Adam over the flat feature shard and the weight shards
+    feat = N * _pad(D_list[0], Y * Z * align) / G
+    weights = sum(D_list[i] * D_list[i + 1] for i in range(L)) / G
+    r["adam"] = (feat + weights) * ADAM_PS_PER_ELEM * 1e-9 + 0.01
+    r["total"] = sum(r.values())
+    return r
+
+
+def rank_grids(G: int, N: int, NNZ: int, D_list: List[int]) -> List[Tuple[float, Tuple[int, int, int]]]:
+    """``[(predicted epoch ms, grid)]`` for every power-of-two grid of ``G`` ranks, best first."""
+    scored = [(predict_epoch_ms(g, N, NNZ, D_list)["total"], g) for g in split_into_three_powers_of_two(G)]
+    return sorted(scored)

@@ -7,6 +7,10 @@ are bracketed by CUDA events on the current stream and only resolved in
 ``get_times()``, so timing does not synchronize the training stream.  On CPU
 ``time.perf_counter`` is used.
 
+With ``PLEXUS_NVTX=1`` (or ``Timers(nvtx=True)``) every region is also an NVTX range, whether or
+not the timers are enabled, so a profiler capture can be filtered or grouped by the same region
+names (the reference has no profiler hooks).
+
 The region names used across the package are the ones the reference's log
 parser matches (reference: examples/parse_results.py:46-69, plexus/gcn_conv.py
 timer calls), so ``process_log_file`` works on logs of either framework.
@@ -14,6 +18,7 @@ timer calls), so ``process_log_file`` works on logs of either framework.
 
 from __future__ import annotations
 
+import os
 import time
 from collections import defaultdict
 from typing import Dict, List, Tuple
@@ -22,9 +27,12 @@ import torch
 
 
 class Timers:
-    def __init__(self, enabled: bool = False, use_cuda: bool | None = None):
+    def __init__(self, enabled: bool = False, use_cuda: bool | None = None, nvtx: bool | None = None):
         self.enabled = enabled
         self._use_cuda = use_cuda
+        if nvtx is None:
+            nvtx = os.environ.get("PLEXUS_NVTX", "0") not in ("", "0")
+        self.nvtx = bool(nvtx) and torch.cuda.is_available()
         self._stack: List[str] = []
         self._open: Dict[Tuple[str, ...], object] = {}
         self._pending: List[Tuple[Tuple[str, ...], object, object]] = []
@@ -44,6 +52,8 @@ class Timers:
         return self._use_cuda
 
     def start(self, name: str) -> None:
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(name)
         if not self.enabled:
             return
         self._stack.append(name)
@@ -56,6 +66,8 @@ class Timers:
             self._open[key] = time.perf_counter()
 
     def stop(self, name: str) -> None:
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         if not self.enabled:
             return
         if not self._stack or self._stack[-1] != name:

@@ -94,3 +94,21 @@ def test_facade_modules_reexport_the_models():
 
     assert pc.compute_config_costs is comm_model.compute_config_costs
     assert pp.comp_model is comp_model.comp_model and pm.compute_config_mem is mem_model.compute_config_mem
+
+
+def test_epoch_model_tracks_the_measured_epochs():
+    """Predicted epoch times of the headline config against the device-timed B200 measurements."""
+    from plexus_b200.perf.epoch_model import predict_epoch_ms, rank_grids
+
+    N, NNZ, D = 2449029, 123717823, [100, 256, 256, 47]
+    measured = {(1, 1, 1): 33.2, (1, 1, 2): 24.95, (2, 1, 2): 17.5, (2, 2, 2): 11.04, (4, 2, 1): 12.85}
+    for grid, ms in measured.items():
+        r = predict_epoch_ms(grid, N, NNZ, D, hbm_gbs=6555.0)
+        assert abs(r["total"] - ms) < 0.2 * ms, (grid, r)
+        assert abs(sum(v for k, v in r.items() if k != "total") - r["total"]) < 1e-9
+    one = predict_epoch_ms((1, 1, 1), N, NNZ, D, hbm_gbs=6555.0)
+    assert one["exposed_comm"] == 0.0 and one["gather"] == 0.0 and one["spmm"] > 0.7 * one["total"]
+    # the 3D grid beats the flat ones on 8 ranks, as measured (11.04 vs 12.85 ms for 4x2x1)
+    ranked = rank_grids(8, N, NNZ, D)
+    assert ranked[0][1] == (2, 2, 2)
+    assert dict((g, t) for t, g in ranked)[(8, 1, 1)] > 1.5 * ranked[0][0]
