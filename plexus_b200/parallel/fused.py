@@ -48,11 +48,12 @@ TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 
 
 def _push_path(ax, nbytes: int) -> bool:
-    return ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES
+    # an axis that spans hosts has no peer-memory workspace: everything goes through NCCL
+    return ax.same_host and (ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES)
 
 
 def _two_shot_path(ax, rows: int, cols: int, dtype) -> bool:
-    return TWO_SHOT and dtype == torch.bfloat16 and cols % 8 == 0 and rows >= ax.p
+    return ax.same_host and TWO_SHOT and dtype == torch.bfloat16 and cols % 8 == 0 and rows >= ax.p
 
 
 def _segment(ax, rows: int):
@@ -178,6 +179,9 @@ def all_gather(t: torch.Tensor, group) -> torch.Tensor:
         raise NotImplementedError("fused all-gather needs a multiple of 4 bytes per rank")
     out = torch.empty((ax.p * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     if nbytes == 0:
+        return out
+    if not ax.same_host:
+        dist.all_gather_into_tensor(out, t, group=group)
         return out
     ax.ensure(nbytes)
     epoch, buf = ax.next_op()

@@ -14,6 +14,8 @@ the axis asks for the same size at the same point of the program).
 
 from __future__ import annotations
 
+import os
+import socket
 from typing import Dict, List, Optional
 
 import torch
@@ -34,6 +36,10 @@ class AxisComm:
         if self.p > MAX_GROUP:
             raise ValueError(f"peer-memory collectives support at most {MAX_GROUP} ranks per axis")
         self.peers = [q for q in range(self.p) if q != self.rank]
+        # CUDA-IPC handles only open inside one host: an axis that spans hosts keeps the library path
+        hosts: List[Optional[str]] = [None] * self.p
+        dist.all_gather_object(hosts, os.environ.get("PLEXUS_HOST_ID") or socket.gethostname(), group=group)
+        self.same_host = len(set(hosts)) == 1
         self.epoch = 0
         self.slot_bytes = 0
         self.local_ptr = 0
@@ -42,6 +48,8 @@ class AxisComm:
 
     # -- allocation ---------------------------------------------------------------------
     def ensure(self, slot_bytes: int) -> None:
+        if not self.same_host:
+            raise RuntimeError("peer-memory workspace requested for an axis that spans hosts")
         slot_bytes = (int(slot_bytes) + 1023) // 1024 * 1024
         if slot_bytes <= self.slot_bytes:
             return

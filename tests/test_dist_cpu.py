@@ -103,3 +103,28 @@ def test_single_process_matches_oracle():
     assert torch.allclose(feats.grad.view(N, F), ref_gx, rtol=1e-8, atol=1e-12)
     for l, layer in enumerate(model.layers):
         assert torch.allclose(layer.weight.grad.view_as(ref_gw[l]), ref_gw[l], rtol=1e-8, atol=1e-12)
+
+
+def _axis_host_check(rank, world, split):
+    import os
+
+    import torch.distributed as dist
+    from plexus_b200.parallel import symm
+
+    os.environ["PLEXUS_HOST_ID"] = f"node{rank // 2}" if split else "node0"
+    ax = symm.AxisComm(dist.group.WORLD)
+    assert ax.p == world and ax.rank == rank and ax.peers == [q for q in range(world) if q != rank]
+    assert ax.same_host == (not split)
+    if split:
+        # no peer-memory workspace may be requested for an axis that spans hosts
+        try:
+            ax.ensure(1024)
+        except RuntimeError as e:
+            assert "spans hosts" in str(e)
+        else:
+            raise AssertionError("ensure() must refuse")
+
+
+@pytest.mark.parametrize("split", [False, True])
+def test_peer_memory_axes_are_limited_to_one_host(split):
+    run_distributed(_axis_host_check, 4, split)
