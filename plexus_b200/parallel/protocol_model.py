@@ -1,0 +1,179 @@
+"""Executable model of the peer-memory flag protocol, for exhaustive interleaving checks on the host.
+
+The kernels in ``csrc/kernels/comm_fused.cu`` synchronise ranks with nothing but per-buffer epoch
+flags: op number ``e`` of an axis uses receive buffer ``e % 2``; a producer stores into its slot of
+every peer's buffer without waiting; the consumer launch publishes ``flag[e % 2][me] = e`` on every
+peer, waits until all peers' flags in its own array reach ``e``, then reads the slots.  The claim is
+that double buffering alone prevents a slot from being rewritten before its reader is done.  No race
+detector can be run on the device here, so the claim is checked on a model instead:
+
+* every rank runs the same program of ops (``"one"`` = one-shot all-reduce / all-gather,
+  ``"two"`` = two-shot all-reduce, which is a reduce-scatter op followed by a gather op whose pushes
+  are issued by the first op's consumer kernel);
+* each op is expanded into the events a stream executes in order: slot writes (begin / end, so a
+  reader can observe a write in progress), flag publications, the wait, slot reads (begin / end);
+* a scheduler interleaves the ranks' events in every possible order (depth-first with memoisation)
+  or at random; a read that overlaps a write of the same slot, or that sees another op's data, is
+  reported.
+
+``buffers=1`` models the protocol without double buffering and must fail (negative control).
+"""
+
+from __future__ import annotations
+
+import random
+from typing import Dict, List, Optional, Sequence, Tuple
+
+Event = Tuple  # (kind, ...)
+
+
+def expand_program(program: Sequence[str], p: int, me: int, buffers: int = 2) -> List[Event]:
+    """Stream-ordered events of rank ``me``; ops are numbered from 1 as on the device."""
+    peers = [q for q in range(p) if q != me]
+    ev: List[Event] = []
+    e = 0
+
+    def push(epoch):
+        b = epoch % buffers
+        for q in peers:
+            ev.append(("wbeg", q, b, me, epoch))
+            ev.append(("wend", q, b, me, epoch))
+
+    def consume(epoch, then_push: Optional[int] = None):
+        b = epoch % buffers
+        for q in peers:
+            ev.append(("flag", q, b, me, epoch))
+        ev.append(("wait", b, epoch))
+        for q in peers:
+            ev.append(("rbeg", b, q, epoch))
+            ev.append(("rend", b, q, epoch))
+        if then_push is not None:
+            push(then_push)  # same kernel: stores of the next op's data follow the reads
+
+    for kind in program:
+        if kind == "one":
+            e += 1
+            push(e)
+            consume(e)
+        elif kind == "two":
+            e += 1
+            push(e)
+            consume(e, then_push=e + 1)
+            e += 1
+            consume(e)
+        else:
+            raise ValueError(kind)
+    return ev
+
+
+class ProtocolViolation(AssertionError):
+    pass
+
+
+class _State:
+    __slots__ = ("pc", "slot", "writing", "reading", "flag")
+
+    def __init__(self, p: int, buffers: int):
+        self.pc = [0] * p
+        # slot[owner][buffer][src] = epoch of the data it holds; writing/reading = activity counters
+        self.slot = [[[0] * p for _ in range(buffers)] for _ in range(p)]
+        self.writing = [[[0] * p for _ in range(buffers)] for _ in range(p)]
+        self.reading = [[[0] * p for _ in range(buffers)] for _ in range(p)]
+        self.flag = [[[0] * p for _ in range(buffers)] for _ in range(p)]
+
+    def key(self):
+        return (tuple(self.pc), repr(self.slot), repr(self.writing), repr(self.reading), repr(self.flag))
+
+    def copy(self, p, buffers):
+        s = _State.__new__(_State)
+        s.pc = list(self.pc)
+        for name in ("slot", "writing", "reading", "flag"):
+            setattr(s, name, [[list(x) for x in o] for o in getattr(self, name)])
+        return s
+
+
+def _enabled(st: _State, progs, r: int, p: int) -> bool:
+    if st.pc[r] >= len(progs[r]):
+        return False
+    ev = progs[r][st.pc[r]]
+    if ev[0] == "wait":
+        _, b, epoch = ev
+        return all(st.flag[r][b][q] >= epoch for q in range(p) if q != r)
+    return True
+
+
+def _apply(st: _State, progs, r: int) -> None:
+    ev = progs[r][st.pc[r]]
+    kind = ev[0]
+    if kind == "wbeg":
+        _, owner, b, src, epoch = ev
+        if st.reading[owner][b][src]:
+            raise ProtocolViolation(f"rank {src} starts writing op {epoch} into a slot rank {owner} is reading")
+        st.writing[owner][b][src] += 1
+    elif kind == "wend":
+        _, owner, b, src, epoch = ev
+        st.writing[owner][b][src] -= 1
+        st.slot[owner][b][src] = epoch
+    elif kind == "flag":
+        _, owner, b, src, epoch = ev
+        if st.flag[owner][b][src] >= epoch:
+            raise ProtocolViolation("flags must increase")
+        st.flag[owner][b][src] = epoch
+    elif kind == "rbeg":
+        _, b, src, epoch = ev
+        if st.writing[r][b][src]:
+            raise ProtocolViolation(f"rank {r} reads slot of rank {src} for op {epoch} while it is being written")
+        if st.slot[r][b][src] != epoch:
+            raise ProtocolViolation(
+                f"rank {r} expected data of op {epoch} from rank {src}, slot holds op {st.slot[r][b][src]}")
+        st.reading[r][b][src] += 1
+    elif kind == "rend":
+        _, b, src, epoch = ev
+        if st.writing[r][b][src] or st.slot[r][b][src] != epoch:
+            raise ProtocolViolation(f"slot of rank {src} on rank {r} changed during the read of op {epoch}")
+        st.reading[r][b][src] -= 1
+    st.pc[r] += 1
+
+
+def check_exhaustive(program: Sequence[str], p: int = 2, buffers: int = 2, max_states: int = 2_000_000) -> int:
+    """Explore every interleaving (memoised); returns the number of distinct states visited.
+
+    Raises :class:`ProtocolViolation` on a race or stale read, ``RuntimeError`` on deadlock."""
+    progs = [expand_program(program, p, r, buffers) for r in range(p)]
+    start = _State(p, buffers)
+    seen = {start.key()}
+    stack = [start]
+    while stack:
+        st = stack.pop()
+        moves = [r for r in range(p) if _enabled(st, progs, r, p)]
+        if not moves:
+            if any(st.pc[r] < len(progs[r]) for r in range(p)):
+                raise RuntimeError(f"deadlock at {st.pc}")
+            continue
+        for r in moves:
+            nxt = st.copy(p, buffers)
+            _apply(nxt, progs, r)
+            k = nxt.key()
+            if k not in seen:
+                seen.add(k)
+                if len(seen) > max_states:
+                    raise RuntimeError("state space larger than max_states")
+                stack.append(nxt)
+    return len(seen)
+
+
+def check_random(program: Sequence[str], p: int, buffers: int = 2, schedules: int = 2000, seed: int = 0) -> None:
+    """Random interleavings, biased so that some ranks race ahead of others."""
+    rng = random.Random(seed)
+    progs = [expand_program(program, p, r, buffers) for r in range(p)]
+    for _ in range(schedules):
+        st = _State(p, buffers)
+        weight = [rng.choice((1, 1, 4, 16)) for _ in range(p)]
+        while True:
+            moves = [r for r in range(p) if _enabled(st, progs, r, p)]
+            if not moves:
+                if any(st.pc[r] < len(progs[r]) for r in range(p)):
+                    raise RuntimeError(f"deadlock at {st.pc}")
+                break
+            r = rng.choices(moves, [weight[m] for m in moves])[0]
+            _apply(st, progs, r)
