@@ -135,3 +135,19 @@ def test_weight_shard_init_equals_slices_of_the_full_matrix():
                 for d in range(depth):
                     got = init_weight_shard(in_ch, out_ch, layer, seed, i * lr, o * lc, lc, d * per, per, "cpu")
                     assert torch.equal(got, block[d * per:(d + 1) * per]), (inner, outer, depth, i, o, d)
+
+
+def test_two_shot_row_segments_cover_the_rows_exactly_once():
+    from types import SimpleNamespace
+
+    from plexus_b200.parallel.fused import _segment
+
+    for p in (2, 3, 4, 8):
+        for rows in (0, 1, 5, 7, 8, 1003, 4096):
+            seg, ranges = _segment(SimpleNamespace(p=p), rows)
+            assert seg * p >= rows and len(ranges) == p
+            covered = []
+            for q, (r0, n) in enumerate(ranges):
+                assert 0 <= n <= seg and r0 == min(q * seg, rows)
+                covered += list(range(r0, r0 + n))
+            assert covered == list(range(rows)), (p, rows)
