@@ -21,7 +21,13 @@ from .grid import group_size
 
 
 def _fused(t: torch.Tensor) -> bool:
-    return runtime.flags.comm == "fused" and t.is_cuda
+    if runtime.flags.comm != "fused":
+        return False
+    if t.is_cuda:
+        return True
+    from . import emulator
+
+    return emulator.active()
 
 _bytes_moved = {"gather": 0, "all-reduce": 0, "reduce-scatter": 0}
 

@@ -26,8 +26,22 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _ext
-from ..ops import cuda as opc
-from . import symm
+from ..ops import cuda as _cuda_ops
+from . import emulator, symm
+
+
+class _Backend:
+    """Kernels (`C()`) and compute ops (attribute access) of the device, or of the host emulation."""
+
+    @staticmethod
+    def load():
+        return emulator.C if emulator.active() else _ext.load()
+
+    def __getattr__(self, name):
+        return getattr(emulator.ops if emulator.active() else _cuda_ops, name)
+
+
+opc = _Backend()
 
 import os
 
@@ -53,7 +67,8 @@ def _push_path(ax, nbytes: int) -> bool:
 
 
 def _two_shot_path(ax, rows: int, cols: int, dtype) -> bool:
-    return ax.same_host and TWO_SHOT and dtype == torch.bfloat16 and cols % 8 == 0 and rows >= ax.p
+    ok = emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+    return ax.same_host and TWO_SHOT and ok and rows >= ax.p
 
 
 def _segment(ax, rows: int):
@@ -73,7 +88,7 @@ def _two_shot_begin(ax, rows: int, cols: int, esz: int):
 
 def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
     """Reduce this rank's segment and broadcast it (op ``epoch``), then land the peers' (next op)."""
-    C = _ext.load()
+    C = _Backend.load()
     st = opc.status_buffer(out.device)
     cols, esz = out.shape[1], out.element_size()
     assert out.stride(0) == cols and out.stride(1) == 1
@@ -94,7 +109,7 @@ def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
 
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
     remote, local = ax.sync(buf)
-    _ext.load().reduce_slots(out, ax.recv_slots(buf), out.stride(0), bool(relu), mask, remote, local,
+    _Backend.load().reduce_slots(out, ax.recv_slots(buf), out.stride(0), bool(relu), mask, remote, local,
                              epoch, ax.timeout_ms, kid, opc.status_buffer(out.device))
     opc._count(1)
 
@@ -151,11 +166,11 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
         code = 1
     else:
         raise NotImplementedError("fused all-reduce supports SUM and MAX")
-    assert t.dtype == torch.float32 and t.is_contiguous()
+    assert (t.dtype == torch.float32 or emulator.active()) and t.is_contiguous()
     if t.numel() == 0:
         return t
     ax = symm.axis_for(group)
-    C = _ext.load()
+    C = _Backend.load()
     if not _push_path(ax, t.numel() * 4):
         dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=group)
         return t
@@ -172,7 +187,7 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
 def all_gather(t: torch.Tensor, group) -> torch.Tensor:
     """Concatenate every rank's contiguous ``t`` along dim 0 (group-rank order)."""
     ax = symm.axis_for(group)
-    C = _ext.load()
+    C = _Backend.load()
     t = t.contiguous()
     nbytes = t.numel() * t.element_size()
     if nbytes % 4:
@@ -196,7 +211,7 @@ def all_gather(t: torch.Tensor, group) -> torch.Tensor:
 
 def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
     """In-place SUM all-reduce of a contiguous bf16 matrix whose width is a multiple of 8."""
-    assert t.dtype == torch.bfloat16 and t.is_contiguous()
+    assert (t.dtype == torch.bfloat16 or emulator.active()) and t.is_contiguous()
     t2 = t.view(-1, t.shape[-1]) if t.dim() > 1 else t.view(1, -1)
     if t2.numel() == 0:
         return t
@@ -205,7 +220,7 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
         if _two_shot_path(ax, t2.shape[0], t2.shape[1], t2.dtype):
             # stand-alone two-shot: scatter the rows to their owners with a copy kernel per peer
             seg, ranges, epoch, buf = _two_shot_begin(ax, t2.shape[0], t2.shape[1], 2)
-            C = _ext.load()
+            C = _Backend.load()
             for q in ax.peers:
                 r0, n = ranges[q]
                 if n:
@@ -217,7 +232,7 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
         return t
     ax.ensure(t2.numel() * 2)
     epoch, buf = ax.next_op()
-    _ext.load().push_copy(t2, ax.push_targets(buf))
+    _Backend.load().push_copy(t2, ax.push_targets(buf))
     opc._count(1)
     _reduce(ax, t2, buf, epoch, False, None, KID_BARRIER)
     return t
@@ -225,6 +240,8 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
 
 def supports(t: torch.Tensor) -> bool:
     """Whether ``t`` can go through the peer-memory all-reduce."""
+    if emulator.active():
+        return t.is_contiguous() and t.is_floating_point()
     if not t.is_cuda or not t.is_contiguous():
         return False
     if t.dtype == torch.float32:

@@ -22,6 +22,17 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _ext
+from . import emulator
+
+
+def _C():
+    """The extension, or its host emulation when that is enabled (CPU ranks, tests)."""
+    return emulator.C if emulator.active() else _ext.load()
+
+
+def _device_sync() -> None:
+    if not emulator.active():
+        torch.cuda.synchronize()
 
 FLAG_BYTES = 1024
 MAX_GROUP = 8
@@ -53,30 +64,30 @@ class AxisComm:
         slot_bytes = (int(slot_bytes) + 1023) // 1024 * 1024
         if slot_bytes <= self.slot_bytes:
             return
-        C = _ext.load()
-        dev = torch.device("cuda", torch.cuda.current_device())
+        C = _C()
+        dev = torch.device("cpu") if emulator.active() else torch.device("cuda", torch.cuda.current_device())
         # nobody may still be using the old workspace
-        torch.cuda.synchronize()
+        _device_sync()
         dist.barrier(group=self.group)
         self.release()
         total = FLAG_BYTES + 2 * self.p * slot_bytes
         ptr, handle = C.symm_alloc(total)
         mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
-        allh = torch.empty((self.p, 64), dtype=torch.uint8, device=dev)
+        allh = torch.empty(self.p * 64, dtype=torch.uint8, device=dev)
         dist.all_gather_into_tensor(allh, mine, group=self.group)
-        allh = allh.cpu()
+        allh = allh.cpu().view(self.p, 64)
         self.ptrs = []
         for q in range(self.p):
             self.ptrs.append(ptr if q == self.rank else C.symm_open(bytes(allh[q].tolist())))
         self.local_ptr, self.slot_bytes = ptr, slot_bytes
-        torch.cuda.synchronize()
+        _device_sync()
         dist.barrier(group=self.group)
 
     def release(self) -> None:
         """Unmap the peers' buffers, then (after everybody did) free the local one."""
         if not self.ptrs:
             return
-        C = _ext.load()
+        C = _C()
         for q, ptr in enumerate(self.ptrs):
             if q != self.rank:
                 C.symm_close(ptr)
@@ -133,7 +144,7 @@ def setup(grid) -> None:
 
 def teardown() -> None:
     if _axes:
-        torch.cuda.synchronize()
+        _device_sync()
     for ax in _axes.values():
         try:
             ax.release()

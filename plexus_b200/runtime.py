@@ -94,7 +94,11 @@ def init(
     if flags.comm not in ("nccl", "fused"):
         raise ValueError("comm must be 'nccl' or 'fused'")
     if flags.comm == "fused" and not use_cuda:
-        raise ValueError("comm='fused' needs CUDA devices with peer access")
+        from .parallel import emulator
+
+        if not emulator.active():
+            raise ValueError("comm='fused' needs CUDA devices with peer access "
+                             "(or parallel.emulator.enable() to emulate them on CPU ranks)")
     flags.dtype = dtype if dtype is not None else (torch.bfloat16 if use_cuda else torch.float32)
     flags.channel_align = (
         channel_align if channel_align is not None else (8 if use_cuda else 1)

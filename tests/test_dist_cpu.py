@@ -14,9 +14,19 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
     from plexus_b200.utils.dataloader import DataLoader
 
     torch.manual_seed(0)
+    comm = None
+    if flags.get("emulate_peer_memory"):
+        # the fused collectives' host code against the shared-memory emulation of the kernels
+        from plexus_b200.parallel import emulator, fused
+
+        emulator.enable()
+        comm = "fused"
+        fused.SMALL_MESSAGE_BYTES = flags.get("small_bytes", fused.SMALL_MESSAGE_BYTES)
+        fused.ONE_SHOT_MAX_RANKS = flags.get("one_shot_ranks", fused.ONE_SHOT_MAX_RANKS)
+        fused.TWO_SHOT = flags.get("two_shot", False)
     plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
              block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
-             tune_gemms=flags.get("tune", False))
+             tune_gemms=flags.get("tune", False), comm=comm)
     if flags.get("block"):
         from plexus_b200.models import gcn_conv
         gcn_conv.MAX_ROWS_PER_CHUNK = 17
@@ -37,6 +47,12 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
         assert torch.allclose(got, want, rtol=1e-8, atol=1e-11), f"layer {l} weight grad"
     want_x = _cut_features(ref_gx, feats)
     assert torch.allclose(feats.grad, want_x, rtol=1e-8, atol=1e-11), "feature grad"
+    if flags.get("emulate_peer_memory"):
+        from plexus_b200.parallel import emulator
+
+        emulator.ops.check_status()
+        assert emulator.ops.launch_count > 0  # the emulated kernels really carried the collectives
+        plx.shutdown()  # unmaps and unlinks the shared-memory workspaces
 
 
 GRIDS = [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2), (2, 1, 2), (4, 1, 1), (1, 1, 4)]
@@ -128,3 +144,26 @@ def _axis_host_check(rank, world, split):
 @pytest.mark.parametrize("split", [False, True])
 def test_peer_memory_axes_are_limited_to_one_host(split):
     run_distributed(_axis_host_check, 4, split)
+
+
+EMU = {"emulate_peer_memory": True}
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 1, 2), (4, 1, 1)])
+def test_fused_host_code_on_emulated_peer_memory_one_shot(grid):
+    """symm.py / fused.py (slots, flags, op parity, workspace growth) with the one-shot push on every axis."""
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, False, dict(EMU, one_shot_ranks=8))
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 1, 4), (2, 2, 2), (4, 2, 1)])
+def test_fused_host_code_on_emulated_peer_memory_two_shot(grid):
+    """Every message through the two-shot form: reduce-scatter push, segment reduce + broadcast, landing."""
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, 3, True, 53, 9, 7, 8, False,
+                    dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1))
+
+
+def test_fused_host_code_default_policy_mixes_push_and_library_paths():
+    """Default thresholds on a 4-rank axis: small messages pushed, large ones reduced by the library."""
+    run_distributed(_worker, 4, (4, 1, 1), 2, True, 61, 10, 5, 12, False, dict(EMU, small_bytes=2048))
