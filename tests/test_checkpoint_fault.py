@@ -201,3 +201,33 @@ def test_device_status_decoding():
     with pytest.raises(PlexusCommTimeout):
         raise_on_device_status(st)
     assert int(st[0]) == 0  # cleared for the next step
+
+
+def _silent_peer_worker(rank, world):
+    """Rank 1 never runs its second collective: rank 0's bounded wait must end in a status word."""
+    import plexus_b200 as plx
+    from plexus_b200.parallel import emulator, fused, symm
+    from plexus_b200.parallel.watchdog import PlexusCommTimeout
+
+    emulator.enable()
+    grid = plx.init(2, 1, 1, device="cpu", comm="fused")
+    g = grid.group("x")
+    t = torch.full((16,), float(rank + 1))
+    fused.all_reduce_f32(t, g)                      # both ranks: sets up the workspace, op 1
+    assert torch.equal(t, torch.full((16,), 3.0))
+    ax = symm.axis_for(g)
+    ax.timeout_ms = 300.0
+    if rank == 0:
+        u = torch.ones(16)
+        t0 = time.time()
+        fused.all_reduce_f32(u, g)                  # op 2: the peer never publishes its flag
+        assert time.time() - t0 < 5.0
+        with pytest.raises(PlexusCommTimeout, match="peer/slot 0, expected 2, seen 0"):
+            emulator.ops.check_status()
+        emulator.ops.check_status()                 # cleared; the rank is still usable
+    dist.barrier()
+    plx.shutdown()
+
+
+def test_peer_that_never_raises_its_flag_ends_in_a_status_word():
+    run_distributed(_silent_peer_worker, 2)
