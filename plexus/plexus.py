@@ -10,9 +10,11 @@ overlap_agg = False
 tune_gemm = False
 
 
-def init(*args, **kwargs):
+def init(G_intra_r=1, G_intra_c=1, G_intra_d=1, gpus_per_node=None, enable_internal_timers=False,
+         block_aggregation=False, overlap_aggregation=False, tune_gemms=False, **kwargs):
     global block_agg, overlap_agg, tune_gemm
-    grid = _rt.init(*args, **kwargs)
+    grid = _rt.init(G_intra_r, G_intra_c, G_intra_d, gpus_per_node, enable_internal_timers,
+                    block_aggregation, overlap_aggregation, tune_gemms, **kwargs)
     block_agg, overlap_agg, tune_gemm = _rt.flags.block_agg, _rt.flags.overlap_agg, _rt.flags.tune_gemm
     return grid
 
