@@ -26,7 +26,8 @@ from plexus_b200.utils.general import set_seed  # noqa: E402
 def create_parser():
     p = argparse.ArgumentParser()
     p.add_argument("--seed", type=int, default=0)
-    p.add_argument("--data_dir", type=str, default=None)
+    p.add_argument("--data_dir", "--download_path", dest="data_dir", type=str, default=None,
+                   help="directory with one processed .pt file (--download_path is the reference's name for it)")
     p.add_argument("--synthetic", type=str, default=None, help="nodes,undirected_edges,features,classes")
     p.add_argument("--num_epochs", type=int, default=10)
     p.add_argument("--num_gcn_layers", type=int, default=3)
