@@ -14,6 +14,11 @@
 // warps 2..5 = epilogue (each owns one 32-lane TMEM quadrant).
 // No TMA load uses cluster multicast.  Every mbarrier wait is bounded.
 //
+// Fused collective: gemm_nt's epilogue can store each finished row, besides (or instead of) the
+// local output, into receive slots in other GPUs' memory with plain 16-byte stores over NVLink -
+// to every peer (one-shot all-reduce) or only to the rank that owns the row (the reduce-scatter
+// half of a two-shot all-reduce); see PushTargets and comm_fused.cu for the receive side.
+//
 // Reference call sites replaced: plexus/gcn_conv.py:211 (OUT), :237 (gradW), :256 (gradAGG),
 // which go to cuBLAS SGEMM through torch.mm.
 
