@@ -226,6 +226,9 @@ def run_ours(args):
     plx.init(*grid, gpus_per_node=torch.cuda.device_count(), enable_internal_timers=args.timers, comm=comm)
     device = torch.device("cuda", local)
 
+    # the global path holds the whole int64 edge list (and its sort buffers) on every GPU
+    if not args.sharded_data and 2 * args.edges + args.nodes > 1_500_000_000:
+        args.sharded_data = True
     if args.sharded_data:
         from plexus_b200.data.sharded_synthetic import ShardedSyntheticGraph
 
