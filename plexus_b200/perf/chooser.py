@@ -1,8 +1,11 @@
-"""Pick the grid shape from the three cost models.
+"""Pick the grid shape from the cost models.
 
-Grids whose estimated memory exceeds the device are dropped; the rest are
-ranked by estimated communication time plus the bandwidth-model SpMM time on
-this machine.
+Grids whose estimated memory exceeds the device are dropped.  ``model="volume"`` (the default, and
+the ranking whose choices have been measured on 1, 2, 4 and 8 GPUs) orders the rest by estimated
+communication time plus the bandwidth-model SpMM time, the reference's way of combining its models;
+``model="epoch"`` (``b200_nvl8`` only) orders them by the per-region epoch-time model of
+``perf/epoch_model.py``, which prices every kernel and collective of the executed schedule with
+measured constants.
 """
 
 from __future__ import annotations
@@ -16,10 +19,16 @@ from .mem_model import compute_config_mem_b200
 
 
 def choose_grid(G: int, N: int, NNZ: int, D_list: List[int], machine: str = "b200_nvl8",
-                mem_limit_gb: float = 170.0) -> List[Tuple[int, int, int]]:
+                mem_limit_gb: float = 170.0, model: str = "volume") -> List[Tuple[int, int, int]]:
     """Grids ordered best first."""
-    comm = compute_config_costs(G, N, D_list, "v3", machine)
     mem = compute_config_mem_b200(G, N, NNZ, D_list)
+    if machine == "b200_nvl8" and model == "epoch":
+        from .epoch_model import predict_epoch_ms
+
+        fits = [g for g in split_into_three_powers_of_two(G) if mem[f"X{g[0]}Y{g[1]}Z{g[2]}"] <= mem_limit_gb]
+        ranked = sorted((predict_epoch_ms(g, N, NNZ, D_list)["total"], g) for g in fits)
+        return [g for _, g in ranked] or [(G, 1, 1)]
+    comm = compute_config_costs(G, N, D_list, "v3", machine)
     hbm = load_measured_peaks().get("hbm_gbs", 6555.0)
     scored = []
     for X, Y, Z in split_into_three_powers_of_two(G):

@@ -112,3 +112,14 @@ def test_epoch_model_tracks_the_measured_epochs():
     ranked = rank_grids(8, N, NNZ, D)
     assert ranked[0][1] == (2, 2, 2)
     assert dict((g, t) for t, g in ranked)[(8, 1, 1)] > 1.5 * ranked[0][0]
+
+
+def test_chooser_models():
+    N, NNZ, D = 2449029, 123717823, [100, 256, 256, 47]
+    # default ranking: the grids that were measured on 2, 4 and 8 GPUs
+    assert chooser.choose_grid(2, N, NNZ, D)[0] == (1, 1, 2)
+    assert chooser.choose_grid(4, N, NNZ, D)[0] == (2, 1, 2)
+    assert chooser.choose_grid(8, N, NNZ, D)[0] == (2, 2, 2)
+    # the epoch model agrees on 8 GPUs and returns every grid that fits
+    ep = chooser.choose_grid(8, N, NNZ, D, model="epoch")
+    assert ep[0] == (2, 2, 2) and len(ep) == 10
