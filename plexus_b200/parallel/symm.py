@@ -14,6 +14,7 @@ the axis asks for the same size at the same point of the program).
 
 from __future__ import annotations
 
+import hashlib
 import os
 import socket
 from typing import Dict, List, Optional
@@ -47,10 +48,17 @@ class AxisComm:
         if self.p > MAX_GROUP:
             raise ValueError(f"peer-memory collectives support at most {MAX_GROUP} ranks per axis")
         self.peers = [q for q in range(self.p) if q != self.rank]
-        # CUDA-IPC handles only open inside one host: an axis that spans hosts keeps the library path
-        hosts: List[Optional[str]] = [None] * self.p
-        dist.all_gather_object(hosts, os.environ.get("PLEXUS_HOST_ID") or socket.gethostname(), group=group)
-        self.same_host = len(set(hosts)) == 1
+        # CUDA-IPC handles only open inside one host: an axis that spans hosts keeps the library path.
+        # Host names are compared through a fixed-size byte all-gather (the same collective the
+        # workspace set-up uses for the IPC handles).
+        host = os.environ.get("PLEXUS_HOST_ID") or socket.gethostname()
+        dev = (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl"
+               else torch.device("cpu"))
+        mine = torch.frombuffer(bytearray(hashlib.sha1(host.encode()).digest()[:16]), dtype=torch.uint8).to(dev)
+        allh = torch.empty(self.p * 16, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allh, mine, group=group)
+        allh = allh.cpu().view(self.p, 16)
+        self.same_host = bool((allh == allh[0]).all())
         self.epoch = 0
         self.slot_bytes = 0
         self.local_ptr = 0
@@ -65,7 +73,8 @@ class AxisComm:
         if slot_bytes <= self.slot_bytes:
             return
         C = _C()
-        dev = torch.device("cpu") if emulator.active() else torch.device("cuda", torch.cuda.current_device())
+        dev = (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(self.group) == "nccl"
+               else torch.device("cpu"))
         # nobody may still be using the old workspace
         _device_sync()
         dist.barrier(group=self.group)
