@@ -22,6 +22,8 @@ These replace the NCCL calls of ``parallel.collectives`` when ``init(comm="fused
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -42,8 +44,6 @@ class _Backend:
 
 
 opc = _Backend()
-
-import os
 
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
 
