@@ -149,14 +149,15 @@ def test_peer_memory_axes_are_limited_to_one_host(split):
 EMU = {"emulate_peer_memory": True}
 
 
-@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 1, 2), (4, 1, 1)])
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 1, 2), (2, 2, 1), (1, 2, 2), (4, 1, 1),
+                                  (2, 2, 2), (1, 4, 2), (8, 1, 1)])
 def test_fused_host_code_on_emulated_peer_memory_one_shot(grid):
     """symm.py / fused.py (slots, flags, op parity, workspace growth) with the one-shot push on every axis."""
     world = grid[0] * grid[1] * grid[2]
     run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, False, dict(EMU, one_shot_ranks=8))
 
 
-@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 1, 4), (2, 2, 2), (4, 2, 1)])
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 1, 4), (1, 4, 1), (2, 2, 2), (4, 2, 1), (1, 1, 8), (2, 4, 1)])
 def test_fused_host_code_on_emulated_peer_memory_two_shot(grid):
     """Every message through the two-shot form: reduce-scatter push, segment reduce + broadcast, landing."""
     world = grid[0] * grid[1] * grid[2]
@@ -167,3 +168,10 @@ def test_fused_host_code_on_emulated_peer_memory_two_shot(grid):
 def test_fused_host_code_default_policy_mixes_push_and_library_paths():
     """Default thresholds on a 4-rank axis: small messages pushed, large ones reduced by the library."""
     run_distributed(_worker, 4, (4, 1, 1), 2, True, 61, 10, 5, 12, False, dict(EMU, small_bytes=2048))
+
+
+@pytest.mark.parametrize("num_layers,double_perm", [(1, True), (2, False), (4, True), (5, False)])
+def test_fused_host_code_layer_counts_and_permutations(num_layers, double_perm):
+    """Role rotation wrap-around and both permutation schemes through the emulated two-shot path."""
+    run_distributed(_worker, 4, (2, 1, 2), num_layers, double_perm, 50, 6, 4, 8, False,
+                    dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1))
