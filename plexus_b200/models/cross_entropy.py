@@ -7,9 +7,10 @@ classes over the outer axis of the last layer.  The loss is
 
 where a row is valid if it is a real node (not padding) and its label is
 non-negative.  Per row, each class shard contributes ``(max, sum exp)``; the
-pair is combined over the class axis (one MAX and one SUM reduction of a
-length-``rows`` vector, or a single peer-memory exchange in fused mode) and the
-scalar loss is summed over both axes.
+pairs of all class shards are exchanged once over the class axis (an all-gather
+of ``2 x rows`` floats, through peer memory in fused mode) and combined locally;
+the scalar loss is summed over both axes.  The reference issues three
+class-axis all-reduces of ``rows`` floats (plexus/cross_entropy.py:46-92).
 
 Reference: plexus/cross_entropy.py:13-120.  Unlike the reference this
 implementation never writes into ``logits`` or ``target``, stores neither a
@@ -42,12 +43,14 @@ class TensorParallelCrossEntropy(torch.autograd.Function):
         logits = logits.contiguous()
         gmax, gsum = ops.xent_local_stats(logits, class_offset, num_classes)
         if group_size(class_group) > 1:
-            lmax = gmax.clone()
-            coll.all_reduce(gmax, class_group, op=dist.ReduceOp.MAX)
-            # rescale the local sum to the global max before summing
-            scale = torch.exp(torch.where(torch.isinf(lmax), torch.full_like(lmax, -1e30), lmax) - gmax)
-            gsum = gsum * scale
-            coll.all_reduce(gsum, class_group)
+            # one exchange over the class axis: every shard's (max, sum exp) pair per row, combined
+            # locally in rank order (so all class shards hold bitwise identical statistics)
+            pairs = coll.all_gather(torch.stack([gmax, gsum]).unsqueeze(0), dim=0, process_group=class_group)
+            lmax, lsum = pairs[:, 0], pairs[:, 1]
+            gmax = lmax.max(dim=0).values
+            # a shard holding only padded classes reports (-inf, 0)
+            finite = torch.where(torch.isinf(lmax), torch.full_like(lmax, -1e30), lmax)
+            gsum = (lsum * torch.exp(finite - gmax)).sum(dim=0)
         loss = ops.xent_combine_loss(
             logits, target, gmax, gsum, row_offset, class_offset, num_nodes, row_weight
         ).reshape(1)
