@@ -308,15 +308,22 @@ def layer_backward(grad_out, AGG, weight, A_t, spec: LayerSpec, input_relu_mask=
     if runtime.flags.comm == "fused" and depth_p > 1:
         from ..parallel import fused
 
-        grad_x = fused.spmm_all_reduce(A_t, grad_agg, spec.depth_group, relu_mask=input_relu_mask)
-        timers.stop("GRAD_H = A.T * GRAD_AGG")
+        grad_x = None
         if spec.gather_features:
-            # the features are a flat depth shard: keep this rank's slice of the reduced gradient
-            flat = grad_x.reshape(-1)
-            pad = (-flat.numel()) % depth_p
-            if pad:
-                flat = torch.nn.functional.pad(flat, (0, pad))
-            grad_x = depth_slice(flat, depth_p, group_rank(spec.depth_group)).clone()
+            # the features are a flat depth shard: only this rank's row segment of the reduced
+            # gradient is needed, so the epilogue reduce-scatters instead of all-reducing
+            seg = fused.spmm_reduce_scatter(A_t, grad_agg, spec.depth_group, relu_mask=input_relu_mask)
+            if seg is not None:
+                grad_x = seg.reshape(-1).clone()
+        if grad_x is None:
+            grad_x = fused.spmm_all_reduce(A_t, grad_agg, spec.depth_group, relu_mask=input_relu_mask)
+            if spec.gather_features:
+                flat = grad_x.reshape(-1)
+                pad = (-flat.numel()) % depth_p
+                if pad:
+                    flat = torch.nn.functional.pad(flat, (0, pad))
+                grad_x = depth_slice(flat, depth_p, group_rank(spec.depth_group)).clone()
+        timers.stop("GRAD_H = A.T * GRAD_AGG")
     else:
         grad_x = ops.spmm(A_t, grad_agg, relu_mask=input_relu_mask)
         timers.stop("GRAD_H = A.T * GRAD_AGG")

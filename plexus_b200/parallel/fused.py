@@ -61,6 +61,10 @@ SMALL_MESSAGE_BYTES = 1 << 20
 TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 
 
+# how often each form carried a matrix collective (for tests and the metrics sink)
+op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0}
+
+
 def _push_path(ax, nbytes: int) -> bool:
     # an axis that spans hosts has no peer-memory workspace: everything goes through NCCL
     return ax.same_host and (ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES)
@@ -123,7 +127,9 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
             seg, ranges, epoch, buf = _two_shot_begin(ax, rows, D, H.element_size())
             out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D, push_seg=(seg, ax.rank))
             _two_shot_finish(ax, out, seg, ranges, epoch, buf, False, relu_mask, KID_SPMM)
+            op_counts["two_shot"] += 1
             return out
+        op_counts["library"] += 1
         out = opc.spmm(A, H)
         dist.all_reduce(out, group=group)
         return out if relu_mask is None else opc.relu_backward(out, relu_mask)
@@ -133,7 +139,39 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     if relu_mask is not None and relu_mask.dtype != out.dtype:
         relu_mask = relu_mask.to(out.dtype)
     _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
+    op_counts["one_shot"] += 1
     return out
+
+
+def spmm_reduce_scatter(A, H, group, relu_mask=None):
+    """This rank's row segment of ``sum over ranks (A @ H)``, or ``None`` if the peer-memory path does
+    not apply (rows not divisible by the group, axis across hosts, large message on a big axis).
+
+    The SpMM epilogue stores each row only where it is reduced (own rows locally, the others into
+    the owner's receive slot) and one flagged kernel sums the own segment: half the link traffic
+    and a third of the reduce traffic of the all-reduce.  Used for the gradient of the
+    depth-sharded input features (reference: the reduce-scatter at plexus/gcn_conv.py:268-274).
+    """
+    ax = symm.axis_for(group)
+    rows, D = A.shape[0], H.shape[1]
+    nbytes = rows * D * H.element_size()
+    if rows % ax.p or not ax.same_host:
+        return None
+    if not (ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES or TWO_SHOT):
+        return None
+    if not (emulator.active() or (H.dtype == torch.bfloat16 and D % 8 == 0)):
+        return None
+    seg, ranges, epoch, buf = _two_shot_begin(ax, rows, D, H.element_size())
+    out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D, push_seg=(seg, ax.rank))
+    if relu_mask is not None and relu_mask.dtype != out.dtype:
+        relu_mask = relu_mask.to(out.dtype)
+    remote, local = ax.sync(buf)
+    r0, n = ranges[ax.rank]
+    _Backend.load().reduce_segment(out, r0, n, ax.recv_slots(buf), D, False, relu_mask, [], remote, local,
+                                   epoch, ax.timeout_ms, KID_SPMM, opc.status_buffer(out.device))
+    opc._count(1)
+    op_counts["reduce_scatter"] += 1
+    return out[r0 : r0 + n]
 
 
 def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
@@ -147,7 +185,9 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
             out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
                            push_seg=(seg, ax.rank))
             _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, None, KID_GEMM)
+            op_counts["two_shot"] += 1
             return out
+        op_counts["library"] += 1
         out = opc.gemm(a, W, trans_b=trans_b, relu=False)
         dist.all_reduce(out, group=group)
         return torch.relu_(out) if relu else out
@@ -155,6 +195,7 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
     epoch, buf = ax.next_op()
     out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
     _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
+    op_counts["one_shot"] += 1
     return out
 
 

@@ -50,8 +50,13 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
     if flags.get("emulate_peer_memory"):
         from plexus_b200.parallel import emulator
 
+        from plexus_b200.parallel import fused
+
         emulator.ops.check_status()
         assert emulator.ops.launch_count > 0  # the emulated kernels really carried the collectives
+        want = flags.get("expect_ops", {})
+        for kind, positive in want.items():
+            assert (fused.op_counts[kind] > 0) == positive, (kind, fused.op_counts)
         plx.shutdown()  # unmaps and unlinks the shared-memory workspaces
 
 
@@ -154,20 +159,25 @@ EMU = {"emulate_peer_memory": True}
 def test_fused_host_code_on_emulated_peer_memory_one_shot(grid):
     """symm.py / fused.py (slots, flags, op parity, workspace growth) with the one-shot push on every axis."""
     world = grid[0] * grid[1] * grid[2]
-    run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, False, dict(EMU, one_shot_ranks=8))
+    # 64 nodes divide by every axis size, so a depth axis reduce-scatters the feature gradient
+    expect = {"one_shot": True, "two_shot": False, "library": False, "reduce_scatter": grid[2] > 1}
+    run_distributed(_worker, world, grid, 3, True, 64, 10, 5, 12, False,
+                    dict(EMU, one_shot_ranks=8, expect_ops=expect))
 
 
 @pytest.mark.parametrize("grid", [(2, 1, 1), (1, 1, 4), (1, 4, 1), (2, 2, 2), (4, 2, 1), (1, 1, 8), (2, 4, 1)])
 def test_fused_host_code_on_emulated_peer_memory_two_shot(grid):
     """Every message through the two-shot form: reduce-scatter push, segment reduce + broadcast, landing."""
     world = grid[0] * grid[1] * grid[2]
+    expect = {"one_shot": False, "two_shot": True, "library": False}
     run_distributed(_worker, world, grid, 3, True, 53, 9, 7, 8, False,
-                    dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1))
+                    dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1, expect_ops=expect))
 
 
 def test_fused_host_code_default_policy_mixes_push_and_library_paths():
     """Default thresholds on a 4-rank axis: small messages pushed, large ones reduced by the library."""
-    run_distributed(_worker, 4, (4, 1, 1), 2, True, 61, 10, 5, 12, False, dict(EMU, small_bytes=2048))
+    run_distributed(_worker, 4, (4, 1, 1), 2, True, 61, 10, 5, 12, False,
+                    dict(EMU, small_bytes=3000, expect_ops={"one_shot": True, "library": True, "two_shot": False}))
 
 
 @pytest.mark.parametrize("num_layers,double_perm", [(1, True), (2, False), (4, True), (5, False)])
