@@ -152,9 +152,15 @@ def _combine_first_forward(H, A, weight, spec: LayerSpec):
     timers.start("gcn conv fwd")
     W = _full_weight(weight, spec, H.dtype)
     timers.start("OUT = AGG * W")
-    T = tuned_matmul(H, W, "H * W " + str(spec.layer_num))
-    timers.stop("OUT = AGG * W")
-    coll.all_reduce(T, spec.inner_group)
+    if runtime.flags.comm == "fused" and group_size(spec.inner_group) > 1:
+        from ..parallel import fused
+
+        T = fused.gemm_all_reduce(H, W, spec.inner_group)  # push fused in the GEMM epilogue
+        timers.stop("OUT = AGG * W")
+    else:
+        T = tuned_matmul(H, W, "H * W " + str(spec.layer_num))
+        timers.stop("OUT = AGG * W")
+        coll.all_reduce(T, spec.inner_group)
     outer_p = group_size(spec.outer_group)
     if runtime.flags.comm == "fused" and outer_p > 1:
         from ..parallel import fused
