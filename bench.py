@@ -283,7 +283,12 @@ def run_ours(args):
 
     rec = base_record(args, world, grid, nnz)
     rec.update({"impl": "plexus_b200", "value": ms / 1e3, "ms_per_step": ms, "dtype": "bf16",
-                "clocks": clocks, "gpu_launches": launches, "comm": comm, "final_loss": float(loss)})
+                "clocks": clocks, "gpu_launches": launches, "comm": comm, "final_loss": float(loss.detach())})
+    if comm == "fused":
+        from plexus_b200.parallel import fused
+
+        # how many matrix collectives of the whole run (warm-up included) took each form
+        rec["fused_collective_forms"] = dict(fused.op_counts)
 
     # ---- end to end through the public API: H2D labels from pinned memory + D2H loss per epoch
     if not args.no_e2e:
