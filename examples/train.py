@@ -30,6 +30,8 @@ from plexus_b200.parallel.watchdog import EpochWatchdog, Heartbeat  # noqa: E402
 from plexus_b200.utils import checkpoint as ckpt  # noqa: E402
 from plexus_b200.utils.dataloader import DataLoader  # noqa: E402
 from plexus_b200.utils.general import print_axonn_timer_data, set_seed  # noqa: E402
+from plexus_b200.parallel import collectives as coll  # noqa: E402
+from plexus_b200.perf.epoch_model import predict_epoch_ms  # noqa: E402
 from plexus_b200.utils.metrics import MetricsSink, max_over_ranks, peak_memory_gb, shard_nnz_imbalance  # noqa: E402
 from plexus_b200.utils.timers import get_timers  # noqa: E402
 
@@ -175,8 +177,17 @@ def main(argv=None):
         start_epoch = ckpt.load_consolidated(args.consolidated, model, optimizer, features)
 
     sink = MetricsSink(args.metrics_file)
+    # global nonzeros: the layer-0 blocks tile the matrix once per inner-axis replica
+    nnz = torch.tensor([float(adj_shards[0][0].values().numel())], dtype=torch.float64,
+                       device=adj_shards[0][0].values().device)
+    if dist.is_initialized() and world > 1:
+        dist.all_reduce(nnz)
+    total_nnz = int(nnz.item()) // max(1, grid[1])
+    dims = [num_features] + [args.hidden_size] * (args.num_gcn_layers - 1) + [num_classes]
+    model_ms = predict_epoch_ms(grid, num_nodes, total_nnz, dims)
     sink.log(event="start", grid=list(grid), world=world, num_nodes=num_nodes, num_features=num_features,
-             num_classes=num_classes, nnz_imbalance=shard_nnz_imbalance(adj_shards))
+             num_classes=num_classes, nnz=total_nnz, nnz_imbalance=shard_nnz_imbalance(adj_shards),
+             model_epoch_ms={k: round(v, 3) for k, v in model_ms.items()})
     row_weight = None
     if args.train_mask_only and "train_mask" in loader.masks:
         row_weight = loader.masks["train_mask"].to(torch.float32)
@@ -219,10 +230,13 @@ def main(argv=None):
             watchdog.end()
         if rank == 0:
             print("Epoch: {:03d}, Train Loss: {:.4f}".format(i, loss_val))
-        rec = dict(event="epoch", epoch=i, loss=loss_val, peak_mem_gb=peak_memory_gb())
+        rec = dict(event="epoch", epoch=i, loss=loss_val, peak_mem_gb=peak_memory_gb(),
+                   collective_bytes=coll.bytes_moved(reset=True))
         if use_cuda:
             torch.cuda.synchronize()
             rec["epoch_ms_max"] = max_over_ranks(ev0.elapsed_time(ev1))
+            # measured epoch against the per-region model of this machine (1.0 = as modelled)
+            rec["model_over_measured"] = round(model_ms["total"] / max(rec["epoch_ms_max"], 1e-9), 3)
         if args.eval:
             for m in ("train_mask", "val_mask", "test_mask"):
                 if m in loader.masks:

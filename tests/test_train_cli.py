@@ -49,6 +49,8 @@ def test_two_rank_grid_matches_serial_run_and_logs_parse(tmp_path):
     assert epoch_ms > 0 and 0 < comm_ms < epoch_ms
     recs = [json.loads(l) for l in metrics.read_text().splitlines()]
     assert recs[0]["event"] == "start" and recs[0]["grid"] == [2, 1, 1]
+    assert recs[0]["nnz"] > 2 * 200000 and recs[0]["model_epoch_ms"]["total"] > 0
+    assert recs[-1]["collective_bytes"]["all-reduce"] > 0
     assert recs[-1]["event"] == "epoch" and 0.0 <= recs[-1]["acc_train"] <= 1.0
 
 
