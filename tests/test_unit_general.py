@@ -151,3 +151,29 @@ def test_two_shot_row_segments_cover_the_rows_exactly_once():
                 assert 0 <= n <= seg and r0 == min(q * seg, rows)
                 covered += list(range(r0, r0 + n))
             assert covered == list(range(rows)), (p, rows)
+
+
+def test_emulator_and_extension_expose_the_same_peer_memory_api():
+    """Every kernel entry point the fused collectives call exists in the emulation, and (when the
+    extension is built) in the extension under the same name."""
+    import os
+    import re
+
+    from plexus_b200.ops import _ext
+    from plexus_b200.parallel import emulator
+
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    names = set()
+    for f in ("fused.py", "symm.py"):
+        src = open(os.path.join(here, "plexus_b200", "parallel", f)).read()
+        names |= set(re.findall(r"\b(?:C|_Backend\.load\(\)|_C\(\))\.([a-z_0-9]+)\(", src))
+    assert {"symm_alloc", "symm_open", "push_copy", "reduce_slots", "reduce_segment", "gather_segments"} <= names
+    for n in sorted(names):
+        assert hasattr(emulator.C, n), f"emulator lacks {n}"
+    if _ext.available():
+        try:
+            ext = _ext.load()
+        except (ImportError, OSError):  # no CUDA runtime libraries on this machine
+            return
+        for n in sorted(names):
+            assert hasattr(ext, n), f"extension lacks {n}"
