@@ -92,6 +92,17 @@ def train(model, optimizer, features_local, adj_shards, labels, num_nodes, num_c
     return loss, output
 
 
+def _parse_injection(spec):
+    """``rank:epoch[:kind]`` with kind ``exit`` (default), ``raise`` or ``stall``; None if unset."""
+    if not spec:
+        return None
+    parts = spec.split(":")
+    kind = parts[2] if len(parts) > 2 else "exit"
+    if kind not in ("exit", "raise", "stall"):
+        raise SystemExit("PLEXUS_INJECT_FAILURE kind must be exit, raise or stall")
+    return int(parts[0]), int(parts[1]), kind
+
+
 def _parse_grid(args, world):
     if args.grid and args.grid != "auto":
         x, y, z = (int(v) for v in args.grid.lower().split("x"))
@@ -171,10 +182,24 @@ def main(argv=None):
     optimizer = FusedAdamW(list(model.parameters()) + [features], lr=args.lr, weight_decay=args.weight_decay)
 
     start_epoch = 0
-    if args.resume and args.checkpoint_dir and os.path.exists(os.path.join(args.checkpoint_dir, "meta.json")):
-        start_epoch = ckpt.load_sharded(args.checkpoint_dir, model, optimizer, features)
-    elif args.resume and args.consolidated and os.path.exists(args.consolidated):
-        start_epoch = ckpt.load_consolidated(args.consolidated, model, optimizer, features)
+    if args.resume:
+        import json
+
+        meta = os.path.join(args.checkpoint_dir, "meta.json") if args.checkpoint_dir else None
+        same_grid = False
+        if meta and os.path.exists(meta):
+            with open(meta) as f:
+                same_grid = tuple(json.load(f)["grid"]) == tuple(grid)
+        if same_grid:
+            start_epoch = ckpt.load_sharded(args.checkpoint_dir, model, optimizer, features)
+        elif args.consolidated and os.path.exists(args.consolidated):
+            # a different grid (or no sharded checkpoint): re-shard the grid-independent form
+            start_epoch = ckpt.load_consolidated(args.consolidated, model, optimizer, features)
+            if rank == 0:
+                print(f"resumed from the consolidated checkpoint at epoch {start_epoch} on grid {tuple(grid)}")
+        elif meta and os.path.exists(meta):
+            raise SystemExit("the sharded checkpoint was written on another grid; pass --consolidated FILE "
+                             "(saved with --checkpoint_every) to resume on this one")
 
     sink = MetricsSink(args.metrics_file)
     # global nonzeros: the layer-0 blocks tile the matrix once per inner-axis replica
@@ -205,7 +230,22 @@ def main(argv=None):
     t0 = args.timing_start_epoch if args.timing_start_epoch is not None else 0
     t1 = args.timing_end_epoch if args.timing_end_epoch is not None else args.num_epochs - 1
     timers = get_timers()
+    inject = _parse_injection(os.environ.get("PLEXUS_INJECT_FAILURE"))
     for i in range(start_epoch, args.num_epochs):
+        if inject is not None and inject[0] == rank and inject[1] == i:
+            # host-side fault injection, between steps: no kernel or collective of this rank is in flight
+            if heartbeat is not None and inject[2] == "exit":
+                heartbeat.announce_exit("injected failure")
+            if inject[2] == "exit":
+                print(f"[rank {rank}] injected failure: exiting before epoch {i}", flush=True)
+                os._exit(3)
+            if inject[2] == "raise":
+                raise RuntimeError(f"injected failure on rank {rank} before epoch {i}")
+            if inject[2] == "stall":
+                import time as _time
+
+                print(f"[rank {rank}] injected failure: stalling before epoch {i}", flush=True)
+                _time.sleep(10 ** 6)
         if heartbeat is not None:
             heartbeat.beat(i)
             heartbeat.check_peers(max_age_s=max(60.0, 4 * args.epoch_timeout))
@@ -245,9 +285,14 @@ def main(argv=None):
             if rank == 0:
                 print("  " + ", ".join(f"{k}: {v:.4f}" for k, v in rec.items() if k.startswith("acc_")))
         sink.log(**rec)
-        if args.checkpoint_dir and args.checkpoint_every and (i + 1) % args.checkpoint_every == 0:
-            ckpt.save_sharded(args.checkpoint_dir, model, optimizer, features, i)
-    if args.consolidated and not args.resume:
+        if args.checkpoint_every and (i + 1) % args.checkpoint_every == 0:
+            if args.checkpoint_dir:
+                ckpt.save_sharded(args.checkpoint_dir, model, optimizer, features, i)
+            if args.consolidated:
+                # grid-independent copy as well, so a restart may use fewer or more GPUs
+                ckpt.save_consolidated(args.consolidated, model, optimizer, features, num_nodes, num_features,
+                                       epoch=i)
+    if args.consolidated:
         ckpt.save_consolidated(args.consolidated, model, optimizer, features, num_nodes, num_features,
                                epoch=args.num_epochs - 1)
     if watchdog is not None:

@@ -76,3 +76,40 @@ def test_rank_local_synthetic_shards_train_like_one_process(tmp_path):
     four = _losses(_run(base + ["--G_intra_r", "2", "--G_intra_d", "2"], 4, tmp_path, 29618))
     assert len(one) == len(four) == 3
     assert all(abs(a - b) <= 2e-4 for a, b in zip(one, four)), (one, four)
+
+
+def test_supervisor_restarts_from_the_last_checkpoint_after_a_lost_rank(tmp_path):
+    """Rank 1 exits before epoch 2 (host-side injection); the supervisor resumes and the losses of the
+    interrupted run continue exactly where an uninterrupted run goes."""
+    base = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
+            "--dtype", "fp32", "--num_epochs", "4", "--G_intra_r", "2", "--backend", "gloo"]
+    clean = _losses(_run(base, 2, tmp_path, 29621))
+    env = dict(os.environ, OMP_NUM_THREADS="2", PLEXUS_INJECT_FAILURE="1:2:exit")
+    cmd = [sys.executable, os.path.join(ROOT, "examples", "supervise.py"), "--nproc", "2", "--max_restarts", "2",
+           "--master_port", "29630", "--"] + base + ["--checkpoint_dir", str(tmp_path / "ck"), "--checkpoint_every", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "injected failure: exiting before epoch 2" in r.stdout
+    assert "[supervise] attempt 0 ended with exit code" in r.stdout and "finished after 1 restart(s)" in r.stdout
+    got = _losses(r.stdout)
+    assert len(got) == 4, r.stdout[-2000:]          # epochs 0, 1 from the first attempt, 2, 3 after the restart
+    assert all(abs(a - b) < 1e-4 for a, b in zip(clean, got)), (clean, got)
+
+
+def test_supervisor_can_restart_on_a_different_grid(tmp_path):
+    """After the failure the job continues on another grid shape from the grid-independent
+    checkpoint that is written next to the sharded one."""
+    base = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
+            "--dtype", "fp32", "--num_epochs", "4", "--backend", "gloo"]
+    clean = _losses(_run(base + ["--G_intra_r", "2"], 2, tmp_path, 29641))
+    env = dict(os.environ, OMP_NUM_THREADS="2", PLEXUS_INJECT_FAILURE="0:2:raise")
+    cmd = [sys.executable, os.path.join(ROOT, "examples", "supervise.py"), "--nproc", "2", "--max_restarts", "1",
+           "--master_port", "29650", "--restart_grid", "1x1x2", "--"] + base + [
+        "--grid", "2x1x1", "--checkpoint_dir", str(tmp_path / "ck"), "--consolidated", str(tmp_path / "full.pt"),
+        "--checkpoint_every", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "resumed from the consolidated checkpoint at epoch 2 on grid (1, 1, 2)" in r.stdout
+    got = _losses(r.stdout)
+    assert len(got) == 4, r.stdout[-2000:]
+    assert all(abs(a - b) < 2e-4 for a, b in zip(clean, got)), (clean, got)
