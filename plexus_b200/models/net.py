@@ -63,6 +63,20 @@ class SerialGCN(torch.nn.Module):
             for i in range(num_gcn_layers)
         )
 
+    @classmethod
+    def from_consolidated(cls, path: str, dtype=torch.float32):
+        """``(model, features)`` from a grid-independent checkpoint written by a parallel run
+        (``utils.checkpoint.save_consolidated``): the trained weights, unpadded, and the trained
+        input features in the processed (permuted) node order - for single-process evaluation or
+        inference of a model that was trained on any grid."""
+        ck = torch.load(path, weights_only=False, map_location="cpu")
+        ws = [w.to(dtype) for w in ck["weights"]]
+        model = cls.__new__(cls)
+        torch.nn.Module.__init__(model)
+        model.weights = torch.nn.ParameterList(torch.nn.Parameter(w.clone()) for w in ws)
+        feats = ck.get("features")
+        return model, (None if feats is None else feats.to(dtype))
+
     def forward(self, x, adjs: List[torch.Tensor]):
         """``adjs[l % len(adjs)]`` is the (square, unsharded) adjacency used at layer ``l``."""
         L = len(self.weights)

@@ -66,9 +66,14 @@ def _save_consolidated_worker(rank, world, grid, path, out):
     for _ in range(2):
         _step(model, opt, adj, feats, labels, N, C)
     ck.save_consolidated(path, model, opt, feats, N, F, epoch=1)
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+
+    with torch.no_grad():
+        at_save = parallel_cross_entropy(model(feats, adj), labels, 3, N, C).item()
     nxt = [_step(model, opt, adj, feats, labels, N, C) for _ in range(2)]
     if rank == 0:
         torch.save(nxt, out)
+        torch.save(at_save, out + ".loss")
 
 
 def _load_consolidated_worker(rank, world, grid, path, out):
@@ -86,6 +91,18 @@ def test_consolidated_checkpoint_resumes_on_a_different_grid(tmp_path):
     run_distributed(_save_consolidated_worker, 2, (2, 1, 1), path, out)
     run_distributed(_load_consolidated_worker, 4, (1, 2, 2), path, out)
     run_distributed(_load_consolidated_worker, 1, (1, 1, 1), path, out)
+    # the same file gives a single-process model for evaluation: its loss on the processed graph
+    # equals the parallel model's loss at the moment of saving
+    from helpers import dense_adj
+    from plexus_b200.models.net import SerialGCN, serial_loss
+
+    model, feats = SerialGCN.from_consolidated(path, dtype=torch.float64)
+    data, nc = small_processed_graph(n=64, e=300, f=10, c=5, seed=8)
+    adjs = [dense_adj(data.edge_index, data.edge_weight, 64).to_sparse(),
+            dense_adj(data.edge_index_2, data.edge_weight_2, 64).to_sparse()]
+    with torch.no_grad():
+        loss = serial_loss(model(feats, adjs), data.y, 64).item()
+    assert abs(loss - torch.load(out + ".loss")) < 2e-5
 
 
 def test_truncated_or_mismatched_checkpoint_is_rejected(tmp_path):
