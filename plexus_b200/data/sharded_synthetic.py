@@ -229,3 +229,52 @@ class ShardedSyntheticGraph:
         if name == "test_mask":
             return u >= 0.75
         raise KeyError(name)
+
+
+def write_partition_tree(source: ShardedSyntheticGraph, num_partitions: int, output_dir: str,
+                         blocks_per_pass: int = 8) -> None:
+    """Write the ``p x p`` partition tree the loader reads (``metadata.pt``, ``edge_index/{0,1}/i_j.pt``
+    with global indices, ``input_features/i_j.pt``, ``output_labels/{0,1}/i.pt``, ``extra.pt``) straight
+    from the generator: no process builds the global graph.  With a process group the ranks split the
+    blocks between them (rank ``r`` writes blocks ``r, r + world, ...``), ``blocks_per_pass`` block
+    positions (both permutation versions of each) are produced by one pass over the raw edge stream.
+
+    Same files as ``utils.dataset.partition_graph_2d`` writes from a processed file
+    (reference: plexus/utils/dataset.py:370-566).
+    """
+    import os
+
+    from ..parallel.sharding import pad_dimension
+    from ..utils.dataset import _atomic_save
+
+    p = int(num_partitions)
+    N, F = source.num_nodes, source.num_features
+    chunk_n, chunk_f = pad_dimension(N, p) // p, pad_dimension(F, p) // p
+    rank, world = source._world()
+    for sub in ("edge_index/0", "edge_index/1", "input_features", "output_labels/0", "output_labels/1"):
+        os.makedirs(os.path.join(output_dir, sub), exist_ok=True)
+    mine = [(i, j) for k, (i, j) in enumerate((i, j) for i in range(p) for j in range(p)) if k % world == rank]
+    source.inverse_sqrt_degree()  # collective: every rank takes part even if it writes no block
+    for start in range(0, len(mine), blocks_per_pass):
+        group = mine[start : start + blocks_per_pass]
+        want = [(v, i * chunk_n, (i + 1) * chunk_n, j * chunk_n, (j + 1) * chunk_n) for i, j in group for v in (0, 1)]
+        built = source.build_blocks(want)
+        for i, j in group:
+            for v in (0, 1):
+                A = built[(v, i * chunk_n, (i + 1) * chunk_n, j * chunk_n, (j + 1) * chunk_n)]
+                crow, col, val = A.crow_indices().to(torch.int64), A.col_indices().to(torch.int64), A.values()
+                rows = torch.repeat_interleave(torch.arange(crow.numel() - 1, device=crow.device), crow[1:] - crow[:-1])
+                ei = torch.stack([rows + i * chunk_n, col + j * chunk_n]).cpu()
+                _atomic_save((ei, val.cpu()), os.path.join(output_dir, "edge_index", str(v), f"{i}_{j}.pt"))
+            r0, r1 = i * chunk_n, min((i + 1) * chunk_n, N)
+            f0, f1 = j * chunk_f, min((j + 1) * chunk_f, F)
+            x = source.feature_block(r0, max(r0, r1), f0, max(f0, f1)).cpu()
+            _atomic_save(x, os.path.join(output_dir, "input_features", f"{i}_{j}.pt"))
+            if j == 0:
+                for v in (0, 1):
+                    _atomic_save(source.labels(v, r0, r1).cpu(), os.path.join(output_dir, "output_labels", str(v), f"{i}.pt"))
+    if rank == 0:
+        _atomic_save({"symmetric": True}, os.path.join(output_dir, "extra.pt"))
+        _atomic_save((N, F, source.num_classes), os.path.join(output_dir, "metadata.pt"))
+    if world > 1:
+        dist.barrier(group=source.group)

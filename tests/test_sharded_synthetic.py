@@ -57,3 +57,31 @@ def test_degrees_do_not_depend_on_chunking_or_rank_count():
     b = ShardedSyntheticGraph(N, RAW, F, C, seed=SEED, chunk=1 << 20).inverse_sqrt_degree()
     assert torch.equal(a, b)
     assert a.shape == (N,) and bool((a > 0).all()) and bool((a <= 1).all())
+
+
+def _partition_worker(rank, world, outdir):
+    import plexus_b200 as plx
+    from plexus_b200.data.sharded_synthetic import ShardedSyntheticGraph, write_partition_tree
+    from plexus_b200.utils.dataloader import DataLoader
+
+    plx.init(2, 1, 2, dtype=torch.float32)
+    src = ShardedSyntheticGraph(N, RAW, F, C, seed=SEED, chunk=700)
+    write_partition_tree(src, 3, outdir, blocks_per_pass=2)   # 3 x 3 files, written by 4 ranks
+    from_files = DataLoader(outdir, 3)
+    adj_f, x_f, y_f, n_f, f_f, c_f = from_files.load()
+    direct = DataLoader(None, 3, source=ShardedSyntheticGraph(N, RAW, F, C, seed=SEED))
+    adj_d, x_d, y_d, n_d, f_d, c_d = direct.load()
+    assert (n_f, f_f, c_f) == (n_d, f_d, c_d) and from_files.symmetric and from_files.double_perm
+    for (A, At), (B, Bt) in zip(adj_f, adj_d):
+        _shards_equal(A, B)
+        _shards_equal(At, Bt)
+    assert torch.equal(x_f.detach(), x_d.detach()) and torch.equal(y_f, y_d)
+    plx.shutdown()
+
+
+def test_partition_tree_written_from_the_generator_loads_like_the_direct_source(tmp_path):
+    run_distributed(_partition_worker, 4, str(tmp_path / "parts"))
+    import os
+
+    assert os.path.exists(tmp_path / "parts" / "metadata.pt")
+    assert len(os.listdir(tmp_path / "parts" / "edge_index" / "1")) == 9
