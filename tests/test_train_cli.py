@@ -113,3 +113,19 @@ def test_supervisor_can_restart_on_a_different_grid(tmp_path):
     got = _losses(r.stdout)
     assert len(got) == 4, r.stdout[-2000:]
     assert all(abs(a - b) < 2e-4 for a, b in zip(clean, got)), (clean, got)
+
+
+def test_grid_sweep_tool_runs_every_grid_on_one_generated_graph(tmp_path):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+           "--master-addr", "127.0.0.1", "--master-port", "29661", os.path.join(ROOT, "benchmarking", "grid_sweep.py"),
+           "--backend", "gloo", "--dtype", "fp32", "--nodes", "500", "--edges", "3000", "--features", "12",
+           "--hidden", "16", "--classes", "4", "--grids", "4x1x1,2x2x1,1x2x2", "--steps", "2", "--warmup", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=str(tmp_path),
+                       env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    recs = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [tuple(x["grid"]) for x in recs[:3]] == [(4, 1, 1), (2, 2, 1), (1, 2, 2)]
+    # same graph, same seed, same initial weights: the loss after 3 epochs does not depend on the grid
+    assert max(x["loss"] for x in recs[:3]) - min(x["loss"] for x in recs[:3]) < 1e-4
+    assert sorted(map(tuple, recs[3]["ranking"])) == [(1, 2, 2), (2, 2, 1), (4, 1, 1)]
+    assert all(x["epoch_ms"] > 0 and x["model_ms"] > 0 for x in recs[:3])
