@@ -185,3 +185,35 @@ def test_fused_host_code_layer_counts_and_permutations(num_layers, double_perm):
     """Role rotation wrap-around and both permutation schemes through the emulated two-shot path."""
     run_distributed(_worker, 4, (2, 1, 2), num_layers, double_perm, 50, 6, 4, 8, False,
                     dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1))
+
+
+def _random_configs(seed, count):
+    import random
+
+    rng = random.Random(seed)
+    grids = [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2), (2, 1, 2), (4, 1, 1), (1, 4, 1), (1, 1, 4),
+             (2, 2, 2), (4, 2, 1), (1, 4, 2), (2, 1, 4), (8, 1, 1), (1, 8, 1), (1, 1, 8)]
+    out = []
+    for _ in range(count):
+        flags = {}
+        if rng.random() < 0.3:
+            flags["align"] = rng.choice([2, 8])
+        if rng.random() < 0.3:
+            flags["order"] = rng.choice(["aggregate_first", "auto"])
+        mode = rng.random()
+        if mode < 0.35:
+            flags.update(EMU, one_shot_ranks=8)
+        elif mode < 0.7:
+            flags.update(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1)
+        out.append((rng.choice(grids), rng.choice([1, 2, 3, 4, 5]), rng.choice([True, False]),
+                    rng.choice([9, 17, 33, 50, 64, 97]), rng.choice([1, 3, 7, 10, 16]), rng.choice([2, 3, 5, 9]),
+                    rng.choice([1, 4, 6, 12]), rng.choice([True, False]), flags))
+    return out
+
+
+@pytest.mark.parametrize("cfg", _random_configs(2024, 10), ids=lambda c: "x".join(map(str, c[0])) + f"-L{c[1]}-n{c[3]}")
+def test_random_configurations(cfg):
+    """Seeded random draws of grid, depth, sizes (down to 9 nodes on 8 ranks, 1 feature, 1 hidden
+    channel), permutation scheme, layer fusion, alignment, order and collective path."""
+    grid, layers, double_perm, n, f, c, hidden, fuse, flags = cfg
+    run_distributed(_worker, grid[0] * grid[1] * grid[2], grid, layers, double_perm, n, f, c, hidden, fuse, flags)
