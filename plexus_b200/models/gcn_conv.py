@@ -86,7 +86,7 @@ def chunked_spmm_all_reduce(csr_matrix, H, ar_group, max_rows_per_chunk: Optiona
         ops.spmm(csr_matrix, H, row_range=(r0, r1), out=AGG[r0:r1])
         if not overlap:
             timers.stop("AGG = A * H")
-        if p > 1:
+        if p > 1 and not runtime.flags.skip_collectives:
             if overlap:
                 handles.append(dist.all_reduce(AGG[r0:r1], group=ar_group, async_op=True))
             else:

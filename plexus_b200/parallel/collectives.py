@@ -46,6 +46,10 @@ def all_gather(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.Tenso
     p = group_size(process_group)
     if p == 1:
         return t
+    if runtime.flags.skip_collectives:
+        reps = [1] * t.dim()
+        reps[dim] = p
+        return t.repeat(*reps)
     timers = get_timers()
     timers.start("gather")
     t = t.contiguous()
@@ -67,7 +71,7 @@ def all_gather(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.Tenso
 
 def all_reduce(t: torch.Tensor, process_group=None, op=None) -> torch.Tensor:
     """In-place SUM (or ``op``) all-reduce; returns ``t``."""
-    if group_size(process_group) == 1:
+    if group_size(process_group) == 1 or runtime.flags.skip_collectives:
         return t
     timers = get_timers()
     timers.start("all-reduce")
@@ -101,6 +105,8 @@ def reduce_scatter(t: torch.Tensor, dim: int = 0, process_group=None) -> torch.T
         raise NotImplementedError("reduce_scatter is only used along dim 0")
     if t.shape[0] % p != 0:
         raise ValueError(f"reduce_scatter: leading size {t.shape[0]} not divisible by {p}")
+    if runtime.flags.skip_collectives:
+        return t[: t.shape[0] // p].clone()
     timers = get_timers()
     timers.start("reduce-scatter")
     t = t.contiguous()
@@ -160,6 +166,8 @@ def reduce_grad_async(t: torch.Tensor, process_group=None, scatter: bool = False
     p = group_size(process_group)
     if p == 1:
         return PendingReduce(t)
+    if runtime.flags.skip_collectives:
+        return PendingReduce(reduce_scatter(t, 0, process_group) if scatter else t)
     if _fused(t) or t.device.type == "cpu" or get_timers().enabled:
         # in-line: peer-memory kernels are stream-ordered already; timed runs keep the
         # collective inside its own timer region

@@ -65,6 +65,12 @@ TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0}
 
 
+def _skip() -> bool:
+    from .. import runtime
+
+    return runtime.flags.skip_collectives
+
+
 def _push_path(ax, nbytes: int) -> bool:
     # an axis that spans hosts has no peer-memory workspace: everything goes through NCCL
     return ax.same_host and (ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES)
@@ -120,6 +126,9 @@ def _reduce(ax, out, buf, epoch, relu, mask, kid):
 
 def spmm_all_reduce(A, H, group, relu_mask=None):
     """``all_reduce_sum(A @ H)`` over ``group`` with the push fused in the SpMM epilogue."""
+    if _skip():
+        out = opc.spmm(A, H)
+        return out if relu_mask is None else opc.relu_backward(out, relu_mask)
     ax = symm.axis_for(group)
     rows, D = A.shape[0], H.shape[1]
     if not _push_path(ax, rows * D * H.element_size()):
@@ -152,6 +161,8 @@ def spmm_reduce_scatter(A, H, group, relu_mask=None):
     and a third of the reduce traffic of the all-reduce.  Used for the gradient of the
     depth-sharded input features (reference: the reduce-scatter at plexus/gcn_conv.py:268-274).
     """
+    if _skip():
+        return None  # the caller's all-reduce path computes without communicating
     ax = symm.axis_for(group)
     rows, D = A.shape[0], H.shape[1]
     nbytes = rows * D * H.element_size()
@@ -176,6 +187,8 @@ def spmm_reduce_scatter(A, H, group, relu_mask=None):
 
 def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
     """``act(all_reduce_sum(a @ op(W)))`` with the push fused in the tcgen05 GEMM epilogue."""
+    if _skip():
+        return opc.gemm(a, W, trans_b=trans_b, relu=relu)
     ax = symm.axis_for(group)
     rows = a.shape[0]
     N = W.shape[0] if trans_b else W.shape[1]

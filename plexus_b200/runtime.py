@@ -37,6 +37,10 @@ class Flags:
     dtype: torch.dtype = torch.float32
     channel_align: int = 1
     initialized: bool = False
+    # measurement aid: every collective becomes a local stand-in of the same shapes (results are
+    # then wrong); epoch time with it on = compute-only time of the same shards, and
+    # "exposed communication" = normal epoch time minus that
+    skip_collectives: bool = False
 
 
 flags = Flags()

@@ -217,3 +217,37 @@ def test_random_configurations(cfg):
     channel), permutation scheme, layer fusion, alignment, order and collective path."""
     grid, layers, double_perm, n, f, c, hidden, fuse, flags = cfg
     run_distributed(_worker, grid[0] * grid[1] * grid[2], grid, layers, double_perm, n, f, c, hidden, fuse, flags)
+
+
+def _skip_worker(rank, world, emulate):
+    import plexus_b200 as plx
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net
+    from plexus_b200.parallel import collectives as coll
+    from plexus_b200.utils.dataloader import DataLoader
+
+    comm = None
+    if emulate:
+        from plexus_b200.parallel import emulator
+
+        emulator.enable()
+        comm = "fused"
+    plx.init(2, 2, 2, device="cpu", dtype=torch.float64, comm=comm)
+    data, nc = small_processed_graph(n=64, e=300, f=10, c=5, seed=5)
+    adj, feats, labels, N, F, C = DataLoader(None, 3, data=(data, nc), dtype=torch.float64).load()
+    model = Net(3, F, 12, C, seed=11).double()
+    coll.bytes_moved(reset=True)
+    plx.runtime.flags.skip_collectives = True
+    loss = parallel_cross_entropy(model(feats, adj), labels, 3, N, C)
+    loss.backward()
+    assert torch.isfinite(loss) and all(torch.isfinite(l.weight.grad).all() for l in model.layers)
+    assert feats.grad.shape == feats.shape
+    assert sum(coll.bytes_moved().values()) == 0      # nothing was handed to a collective
+    plx.runtime.flags.skip_collectives = False
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("emulate", [False, True])
+def test_compute_only_mode_runs_the_same_shapes_without_communication(emulate):
+    """``flags.skip_collectives`` (used to measure exposed communication) keeps every shape."""
+    run_distributed(_skip_worker, 8, emulate)
