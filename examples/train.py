@@ -57,6 +57,8 @@ def create_parser():
     parser.add_argument("--num_gcn_layers", type=int, default=3)
     parser.add_argument("--hidden_size", type=int, default=128)
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--dropout", type=float, default=0.0,
+                        help="dropout probability on the hidden activations (0 = the reference model)")
     # additions
     parser.add_argument("--grid", type=str, default=None, help="'auto' or 'XxYxZ'")
     parser.add_argument("--backend", type=str, default=None, help="nccl (GPU) or gloo (CPU)")
@@ -178,7 +180,8 @@ def main(argv=None):
         loader = DataLoader(args.data_dir, args.num_gcn_layers)
     adj_shards, features, labels, num_nodes, num_features, num_classes = loader.load()
 
-    model = Net(args.num_gcn_layers, num_features, args.hidden_size, num_classes, seed=args.seed)
+    model = Net(args.num_gcn_layers, num_features, args.hidden_size, num_classes, seed=args.seed,
+                dropout=args.dropout)
     optimizer = FusedAdamW(list(model.parameters()) + [features], lr=args.lr, weight_decay=args.weight_decay)
 
     start_epoch = 0

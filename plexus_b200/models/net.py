@@ -13,17 +13,25 @@ from typing import List, Optional
 import torch
 import torch.nn.functional as F
 
+from ..ops.dropout import relu_dropout_2d
 from .gcn_conv import GCNConv, GCNStackFunction, init_full_weight
 
 
 class Net(torch.nn.Module):
     def __init__(self, num_gcn_layers, input_size, hidden_size, output_size, fuse_layers: bool = True,
-                 seed: Optional[int] = None, order: str = "auto"):
+                 seed: Optional[int] = None, order: str = "auto", dropout: float = 0.0):
         """``order``: per-layer multiplication order, see :class:`GCNConv` (``"auto"`` aggregates
-        after the transform wherever that makes the sparse product narrower)."""
+        after the transform wherever that makes the sparse product narrower).
+        ``dropout``: probability of dropping a hidden activation (after the ReLU, training mode only;
+        the reference model has none).  The mask of an element depends on its position in the
+        unsharded activation, the layer, the seed and the number of training steps taken, so every
+        grid shape - and the serial model - drops the same elements."""
         super().__init__()
         self.num_gcn_layers = num_gcn_layers
-        self.fuse_layers = fuse_layers
+        self.dropout = float(dropout)
+        self.dropout_seed = 0 if seed is None else int(seed)
+        self.steps_taken = 0
+        self.fuse_layers = fuse_layers and self.dropout == 0.0
         dims = [input_size] + [hidden_size] * (num_gcn_layers - 1) + [output_size]
         self.dims = dims
         self.layers = torch.nn.ModuleList(
@@ -40,11 +48,25 @@ class Net(torch.nn.Module):
                 specs.append(layer.spec(pair[0], relu=(i != L - 1)))
                 adjs.append(pair)
             return GCNStackFunction.apply(specs, adjs, x, *[l.weight for l in self.layers])
+        drop = self.dropout > 0 and self.training
         for i, layer in enumerate(self.layers):
             x = layer(x, edge_index_shards)
             if i != L - 1:
-                x = F.relu(x)
+                if drop:
+                    # the activation is sharded by rows over the layer's depth axis and by columns
+                    # over its outer axis
+                    x = relu_dropout_2d(x, self.dropout, dropout_seed(self.dropout_seed, i, self.steps_taken),
+                                        layer.depth_rank * x.shape[0], layer.outer_rank * x.shape[1],
+                                        layer.true_out_channels)
+                else:
+                    x = F.relu(x)
+        if drop:
+            self.steps_taken += 1
         return x
+
+
+def dropout_seed(seed: int, layer: int, step: int) -> int:
+    return (seed * 1000003 + layer * 7919 + step * 104729 + 17) % (1 << 62)
 
 
 class SerialGCN(torch.nn.Module):
@@ -77,14 +99,20 @@ class SerialGCN(torch.nn.Module):
         feats = ck.get("features")
         return model, (None if feats is None else feats.to(dtype))
 
-    def forward(self, x, adjs: List[torch.Tensor]):
-        """``adjs[l % len(adjs)]`` is the (square, unsharded) adjacency used at layer ``l``."""
+    def forward(self, x, adjs: List[torch.Tensor], dropout: float = 0.0, seed: int = 0, step: int = 0):
+        """``adjs[l % len(adjs)]`` is the (square, unsharded) adjacency used at layer ``l``.
+
+        With ``dropout`` the same position-keyed masks as the parallel :class:`Net` (same ``seed``,
+        ``step`` = number of training forwards taken) are applied."""
         L = len(self.weights)
         for l, w in enumerate(self.weights):
             A = adjs[l % len(adjs)]
             x = torch.sparse.mm(A, x) @ w
             if l != L - 1:
-                x = torch.relu(x)
+                if dropout > 0:
+                    x = relu_dropout_2d(x, dropout, dropout_seed(seed, l, step), 0, 0, x.shape[1])
+                else:
+                    x = torch.relu(x)
         return x
 
 

@@ -251,3 +251,48 @@ def _skip_worker(rank, world, emulate):
 def test_compute_only_mode_runs_the_same_shapes_without_communication(emulate):
     """``flags.skip_collectives`` (used to measure exposed communication) keeps every shape."""
     run_distributed(_skip_worker, 8, emulate)
+
+
+def _dropout_worker(rank, world, grid):
+    import plexus_b200 as plx
+    from helpers import dense_adj
+    from plexus_b200.models.cross_entropy import parallel_cross_entropy
+    from plexus_b200.models.net import Net, SerialGCN, serial_loss
+    from plexus_b200.utils.checkpoint import _cut_features, _cut_weight
+    from plexus_b200.utils.dataloader import DataLoader
+
+    plx.init(*grid, device="cpu", dtype=torch.float64)
+    data, nc = small_processed_graph(n=61, e=300, f=10, c=5, seed=5)
+    adj, feats, labels, N, F, C = DataLoader(None, 3, data=(data, nc), dtype=torch.float64).load()
+    model = Net(3, F, 12, C, seed=11, dropout=0.4).double()
+    assert not model.fuse_layers
+    serial = SerialGCN(3, F, 12, C, seed=11, dtype=torch.float64)
+    adjs = [dense_adj(data.edge_index, data.edge_weight, N).to_sparse(),
+            dense_adj(data.edge_index_2, data.edge_weight_2, N).to_sparse()]
+    for step in range(2):  # the masks change from step to step, identically on both sides
+        feats.grad = None
+        for p_ in model.parameters():
+            p_.grad = None
+        loss = parallel_cross_entropy(model(feats, adj), labels, 3, N, C)
+        loss.backward()
+        x = data.x.double().clone().requires_grad_()
+        for w in serial.weights:
+            w.grad = None
+        ref = serial_loss(serial(x, adjs, dropout=0.4, seed=11, step=step), data.y, N)
+        ref.backward()
+        assert torch.allclose(loss.detach(), ref.detach(), rtol=1e-9), (step, loss.item(), ref.item())
+        for l, layer in enumerate(model.layers):
+            assert torch.allclose(layer.weight.grad, _cut_weight(layer, serial.weights[l].grad), rtol=1e-8, atol=1e-11)
+        assert torch.allclose(feats.grad, _cut_features(x.grad, feats), rtol=1e-8, atol=1e-11)
+    first = loss.item()
+    model.eval()  # no dropout in evaluation mode
+    with torch.no_grad():
+        ev = parallel_cross_entropy(model(feats, adj), labels, 3, N, C).item()
+        want = serial_loss(serial(data.x.double(), adjs), data.y, N).item()
+    assert abs(ev - want) < 1e-9 and abs(ev - first) > 1e-6
+
+
+@pytest.mark.parametrize("grid", [(1, 1, 1), (2, 1, 2), (2, 2, 2), (1, 4, 1)])
+def test_dropout_masks_do_not_depend_on_the_grid(grid):
+    """Net(dropout=p): every grid drops the same elements as the serial model with the same seed."""
+    run_distributed(_dropout_worker, grid[0] * grid[1] * grid[2], grid)

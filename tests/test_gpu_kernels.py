@@ -327,3 +327,19 @@ def test_weight_shard_kernel_equals_the_host_hash():
                 per = block.numel() // 2
                 got = init_weight_shard(in_ch, out_ch, layer, seed, i * lr, o * lc, lc, d * per, per, _dev())
                 assert torch.equal(got.cpu(), block[d * per:(d + 1) * per]), (i, o, d)
+
+
+def test_position_keyed_dropout_mask_is_the_same_on_cpu_and_gpu():
+    from plexus_b200.ops.dropout import keep_mask_2d, relu_dropout_2d
+
+    a = keep_mask_2d(300, 40, 0.25, 9, 1000, 8, 64)
+    b = keep_mask_2d(300, 40, 0.25, 9, 1000, 8, 64, device=_dev())
+    assert torch.equal(a, b.cpu()) and 0.6 < a.float().mean() < 0.9
+    x = torch.randn(300, 40).to(torch.bfloat16)
+    y_cpu = relu_dropout_2d(x, 0.25, 9, 1000, 8, 64)
+    xg = x.to(_dev()).requires_grad_()
+    y_gpu = relu_dropout_2d(xg, 0.25, 9, 1000, 8, 64)
+    assert torch.equal(y_cpu, y_gpu.detach().cpu())
+    y_gpu.float().sum().backward()
+    want = ((y_cpu > 0).float() / 0.75).to(torch.bfloat16)
+    assert torch.equal(xg.grad.cpu(), want)
