@@ -1,4 +1,7 @@
-"""``process_log_file(filename, warmup) -> (epoch_ms, comm_ms)``; CLI prints both."""
+"""``process_log_file(filename, warmup) -> (epoch_ms, comm_ms)``; CLI prints both.
+
+Same entry point as the reference's ``examples/parse_results.py``; implementation:
+``plexus_b200/utils/parse_results.py``."""
 
 import os
 import sys

@@ -1,0 +1,1 @@
+"""Utility modules under the reference's ``plexus.utils`` names."""
