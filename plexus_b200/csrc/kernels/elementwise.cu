@@ -1,5 +1,9 @@
 // Small elementwise kernels: ReLU derivative, weight preparation (fp32 -> bf16 and its
 // transpose in one pass), dtype casts, and the bounded flag wait used by the fault tests.
+//
+// Reference sites: the ReLU between layers and its autograd derivative (examples/train.py:78) and
+// the operand re-layout copies of the GEMM tuner (plexus/utils/matmul_tuning.py:30-51), which
+// prep_weight replaces by one cast + transpose of the small operand.
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
