@@ -177,3 +177,150 @@ def check_random(program: Sequence[str], p: int, buffers: int = 2, schedules: in
                 break
             r = rng.choices(moves, [weight[m] for m in moves])[0]
             _apply(st, progs, r)
+
+
+# ------------------------------------------------------------------------------------------------
+# Tile-granular variant: the reduction is finished inside the compute kernel.
+#
+# Every rank runs C persistent CTAs per op; CTA c owns tiles c, c + C, ...  For tile t it stores its
+# partial into slot tile t of every peer and raises the per-tile flag there, then - one tile behind -
+# waits for the peers' flags of its previous tile and reads their partials.  Ops alternate between
+# two buffers; a rank's CTAs all finish op e before any starts op e + 1 (kernel boundary).  The
+# questions the model answers: can the waits deadlock (they are on other GPUs' kernels), and can a
+# fast rank's op e + 2 overwrite a slot tile that a slow peer still reads for op e?
+def expand_tile_program(num_ops: int, p: int, me: int, cta: int, ctas: int, tiles: int, buffers: int = 2,
+                        lag: int = 1) -> List[Event]:
+    peers = [q for q in range(p) if q != me]
+    mine = list(range(cta, tiles, ctas))
+    ev: List[Event] = []
+
+    def consume(e, b, t):
+        ev.append(("twait", b, t, e))
+        for q in peers:
+            ev.append(("trbeg", b, q, t, e))
+            ev.append(("trend", b, q, t, e))
+
+    for e in range(1, num_ops + 1):
+        b = e % buffers
+        for k, t in enumerate(mine):
+            for q in peers:
+                ev.append(("twbeg", q, b, me, t, e))
+                ev.append(("twend", q, b, me, t, e))
+            for q in peers:
+                ev.append(("tflag", q, b, me, t, e))
+            if k >= lag:
+                consume(e, b, mine[k - lag])
+        for t in mine[max(0, len(mine) - lag):]:
+            consume(e, b, t)
+        ev.append(("kbar", e))  # end of this CTA's part of the kernel
+    return ev
+
+
+def check_tile_protocol(num_ops: int = 3, p: int = 2, ctas: int = 2, tiles: int = 4, buffers: int = 2,
+                        lag: int = 1, max_states: int = 3_000_000, schedules: int = 0, seed: int = 0) -> int:
+    """Exhaustive (``schedules == 0``) or random exploration of the tile-granular protocol.
+
+    Returns the number of distinct states (exhaustive) or of schedules run.  Raises
+    :class:`ProtocolViolation` on a race / stale read and ``RuntimeError`` on deadlock."""
+    threads = [(r, c) for r in range(p) for c in range(ctas)]
+    progs = [expand_tile_program(num_ops, p, r, c, ctas, tiles, buffers, lag) for r, c in threads]
+    nthreads = len(threads)
+
+    def enabled(pc, slot, flag, arrived, i):
+        if pc[i] >= len(progs[i]):
+            return False
+        ev = progs[i][pc[i]]
+        r = threads[i][0]
+        if ev[0] == "twait":
+            _, b, t, e = ev
+            return all(flag.get((r, b, q, t), 0) >= e for q in range(p) if q != r)
+        return True
+
+    def apply(pc, slot, busy, flag, arrived, i):
+        ev = progs[i][pc[i]]
+        r = threads[i][0]
+        kind = ev[0]
+        if kind == "twbeg":
+            _, owner, b, src, t, e = ev
+            cell = (owner, b, src, t)
+            if busy.get(("r",) + cell, 0):
+                raise ProtocolViolation(f"rank {src} op {e} overwrites tile {t} that rank {owner} is still reading")
+            busy[("w",) + cell] = busy.get(("w",) + cell, 0) + 1
+        elif kind == "twend":
+            _, owner, b, src, t, e = ev
+            cell = (owner, b, src, t)
+            busy[("w",) + cell] -= 1
+            slot[cell] = e
+        elif kind == "tflag":
+            _, owner, b, src, t, e = ev
+            if flag.get((owner, b, src, t), 0) >= e:
+                raise ProtocolViolation("flags must increase")
+            flag[(owner, b, src, t)] = e
+        elif kind == "trbeg":
+            _, b, src, t, e = ev
+            cell = (r, b, src, t)
+            if busy.get(("w",) + cell, 0) or slot.get(cell, 0) != e:
+                raise ProtocolViolation(f"rank {r} op {e} tile {t}: slot of rank {src} holds op {slot.get(cell, 0)}"
+                                        " or is being written")
+            busy[("r",) + cell] = busy.get(("r",) + cell, 0) + 1
+        elif kind == "trend":
+            _, b, src, t, e = ev
+            cell = (r, b, src, t)
+            if busy.get(("w",) + cell, 0) or slot.get(cell, 0) != e:
+                raise ProtocolViolation(f"rank {r} op {e} tile {t}: slot changed during the read")
+            busy[("r",) + cell] -= 1
+        elif kind == "kbar":
+            arrived[(r, ev[1])] = arrived.get((r, ev[1]), 0) + 1
+        pc[i] += 1
+
+    def blocked_at_barrier(pc, arrived, i):
+        # a CTA that finished op e may only start op e + 1 when all CTAs of its rank finished op e
+        if pc[i] == 0 or pc[i] >= len(progs[i]):
+            return False
+        prev = progs[i][pc[i] - 1]
+        return prev[0] == "kbar" and arrived.get((threads[i][0], prev[1]), 0) < ctas
+
+    def freeze(d):
+        return tuple(sorted((k, v) for k, v in d.items() if v))
+
+    def moves(pc, slot, flag, arrived):
+        return [i for i in range(nthreads)
+                if not blocked_at_barrier(pc, arrived, i) and enabled(pc, slot, flag, arrived, i)]
+
+    def done(pc):
+        return all(pc[i] >= len(progs[i]) for i in range(nthreads))
+
+    if schedules:
+        rng = random.Random(seed)
+        for _ in range(schedules):
+            pc, slot, busy, flag, arrived = [0] * nthreads, {}, {}, {}, {}
+            weight = [rng.choice((1, 1, 4, 16)) for _ in range(nthreads)]
+            while True:
+                mv = moves(pc, slot, flag, arrived)
+                if not mv:
+                    if not done(pc):
+                        raise RuntimeError(f"deadlock at {pc}")
+                    break
+                apply(pc, slot, busy, flag, arrived, rng.choices(mv, [weight[m] for m in mv])[0])
+        return schedules
+
+    start = ([0] * nthreads, {}, {}, {}, {})
+    seen = {(tuple(start[0]), (), (), (), ())}
+    stack = [start]
+    while stack:
+        pc, slot, busy, flag, arrived = stack.pop()
+        mv = moves(pc, slot, flag, arrived)
+        if not mv:
+            if not done(pc):
+                raise RuntimeError(f"deadlock at {pc}")
+            continue
+        for i in mv:
+            n = (list(pc), dict(slot), dict(busy), dict(flag), dict(arrived))
+            apply(*n, i)
+            key = (tuple(n[0]), freeze(n[1]), freeze(n[2]), freeze(n[3]), freeze(n[4]))
+            if key not in seen:
+                seen.add(key)
+                if len(seen) > max_states:
+                    raise RuntimeError("state space larger than max_states")
+                stack.append(n)
+    return len(seen)

@@ -39,3 +39,30 @@ def test_single_buffering_is_caught_as_a_race():
         check_exhaustive(["one", "one"], p=2, buffers=1)
     with pytest.raises(ProtocolViolation):
         check_exhaustive(["two"], p=2, buffers=1)
+
+
+# ---- tile-granular protocol (reduction finished inside the compute kernel, one tile behind)
+@pytest.mark.parametrize("kw", [
+    dict(num_ops=3, p=2, ctas=2, tiles=3),
+    dict(num_ops=2, p=2, ctas=2, tiles=4),
+    dict(num_ops=4, p=2, ctas=1, tiles=2),
+    dict(num_ops=3, p=3, ctas=1, tiles=2),
+], ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items()))
+def test_tile_granular_protocol_is_race_and_deadlock_free(kw):
+    from plexus_b200.parallel.protocol_model import check_tile_protocol
+
+    assert check_tile_protocol(**kw) > 300
+
+
+def test_tile_granular_protocol_random_schedules_on_larger_groups():
+    from plexus_b200.parallel.protocol_model import check_tile_protocol
+
+    check_tile_protocol(num_ops=4, p=4, ctas=3, tiles=7, schedules=150, seed=1)
+    check_tile_protocol(num_ops=3, p=8, ctas=2, tiles=5, schedules=40, seed=2, lag=2)
+
+
+def test_tile_granular_protocol_needs_double_buffering():
+    from plexus_b200.parallel.protocol_model import ProtocolViolation, check_tile_protocol
+
+    with pytest.raises(ProtocolViolation):
+        check_tile_protocol(num_ops=3, p=2, ctas=1, tiles=2, buffers=1)
