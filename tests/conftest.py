@@ -36,3 +36,4 @@ def _reset_runtime():
     runtime.flags.initialized = False
     runtime.flags.comm = "nccl"
     runtime.flags.block_agg = runtime.flags.overlap_agg = runtime.flags.tune_gemm = False
+    runtime.flags.skip_collectives = False
