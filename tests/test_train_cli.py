@@ -78,15 +78,26 @@ def test_rank_local_synthetic_shards_train_like_one_process(tmp_path):
     assert all(abs(a - b) <= 2e-4 for a, b in zip(one, four)), (one, four)
 
 
+_CLEAN = {}
+
+
+def _clean_two_rank_losses(tmp_path, base):
+    """Losses of the uninterrupted 2-rank run (computed once for both supervisor tests)."""
+    if "losses" not in _CLEAN:
+        _CLEAN["losses"] = _losses(_run(base + ["--G_intra_r", "2"], 2, tmp_path, 29621))
+    return _CLEAN["losses"]
+
+
 def test_supervisor_restarts_from_the_last_checkpoint_after_a_lost_rank(tmp_path):
     """Rank 1 exits before epoch 2 (host-side injection); the supervisor resumes and the losses of the
     interrupted run continue exactly where an uninterrupted run goes."""
     base = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
-            "--dtype", "fp32", "--num_epochs", "4", "--G_intra_r", "2", "--backend", "gloo"]
-    clean = _losses(_run(base, 2, tmp_path, 29621))
+            "--dtype", "fp32", "--num_epochs", "4", "--backend", "gloo"]
+    clean = _clean_two_rank_losses(tmp_path, base)
     env = dict(os.environ, OMP_NUM_THREADS="2", PLEXUS_INJECT_FAILURE="1:2:exit")
     cmd = [sys.executable, os.path.join(ROOT, "examples", "supervise.py"), "--nproc", "2", "--max_restarts", "2",
-           "--master_port", "29630", "--"] + base + ["--checkpoint_dir", str(tmp_path / "ck"), "--checkpoint_every", "1"]
+           "--master_port", "29630", "--"] + base + ["--G_intra_r", "2", "--checkpoint_dir", str(tmp_path / "ck"),
+                                                      "--checkpoint_every", "1"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=str(tmp_path))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "injected failure: exiting before epoch 2" in r.stdout
@@ -101,7 +112,7 @@ def test_supervisor_can_restart_on_a_different_grid(tmp_path):
     checkpoint that is written next to the sharded one."""
     base = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
             "--dtype", "fp32", "--num_epochs", "4", "--backend", "gloo"]
-    clean = _losses(_run(base + ["--G_intra_r", "2"], 2, tmp_path, 29641))
+    clean = _clean_two_rank_losses(tmp_path, base)
     env = dict(os.environ, OMP_NUM_THREADS="2", PLEXUS_INJECT_FAILURE="0:2:raise")
     cmd = [sys.executable, os.path.join(ROOT, "examples", "supervise.py"), "--nproc", "2", "--max_restarts", "1",
            "--master_port", "29650", "--restart_grid", "1x1x2", "--"] + base + [
