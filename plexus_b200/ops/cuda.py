@@ -208,9 +208,11 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
 
 
 def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0,
-         push_ptrs=(), push_ld=0, relu_mask=None, push_seg=(0, 0)):
+         push_ptrs=(), push_ld=0, relu_mask=None, push_seg=(0, 0), out=None):
     """``relu_mask`` (shape of the result): zero the result where the mask is not positive.
-    ``push_ptrs`` / ``push_seg``: fused-collective epilogue, see :func:`spmm`."""
+    ``push_ptrs`` / ``push_seg``: fused-collective epilogue, see :func:`spmm`.
+    ``out``: optional destination of ``op(a) @ op(b)`` for the non-transposed-``a`` forms (rows
+    contiguous, e.g. a row block of a larger matrix)."""
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas, nb = GEMM_VARIANTS[variant]
@@ -243,7 +245,10 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         bt = torch.empty((b.shape[1], b.shape[0]), dtype=torch.bfloat16, device=b.device)
         C.prep_weight(b.contiguous(), None, bt)
         _count(1)
-    out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    if out is None:
+        out = torch.empty((a.shape[0], bt.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    elif tuple(out.shape) != (a.shape[0], bt.shape[0]) or out.stride(-1) != 1:
+        raise ValueError("gemm: out has the wrong shape or layout")
     if relu_mask is not None and relu_mask.dtype != out.dtype:
         relu_mask = relu_mask.to(out.dtype)
     C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask,

@@ -193,17 +193,23 @@ class _Ops:
         from ..ops import reference
 
         res = reference.spmm(A, H, relu_mask=relu_mask, row_range=row_range, out_dtype=out_dtype).contiguous()
+        if out is not None:
+            out.copy_(res)
+            res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
         self._count(1)
         return res
 
     def gemm(self, a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant=0, push_ptrs=(),
-             push_ld=0, relu_mask=None, push_seg=(0, 0)):
+             push_ld=0, relu_mask=None, push_seg=(0, 0), out=None):
         from ..ops import reference
 
         res = reference.gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype).contiguous()
         if relu_mask is not None:
             res = reference.relu_backward(res, relu_mask)
+        if out is not None:
+            out.copy_(res)
+            res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
         self._count(1)
         return res

@@ -59,10 +59,26 @@ KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
 ONE_SHOT_MAX_RANKS = int(os.environ.get("PLEXUS_ONE_SHOT_MAX_RANKS", "2"))
 SMALL_MESSAGE_BYTES = 1 << 20
 TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
+# Largest message one op carries; a larger matrix is processed in row blocks, one op each, so the
+# receive slots (2 buffers x p slots per axis) stay bounded however large the activations are
+# (a 55M x 86 bf16 matrix is 9.5 GB; unblocked its slots alone would take 38 GB per axis).
+MAX_MESSAGE_BYTES = int(os.environ.get("PLEXUS_MAX_MESSAGE_BYTES", str(2 << 30)))
+ROW_BLOCK_MULTIPLE = 128  # row blocks start on a GEMM tile boundary
+
+
+def _row_blocks(rows: int, row_bytes: int):
+    """Row ranges of at most ``MAX_MESSAGE_BYTES`` each, starting on multiples of ``ROW_BLOCK_MULTIPLE``."""
+    m = ROW_BLOCK_MULTIPLE
+    per = max(m, MAX_MESSAGE_BYTES // max(1, row_bytes) // m * m)
+    if rows <= per:
+        return [(0, rows)]
+    n = -(-rows // per)
+    step = -(-(-(-rows // n)) // m) * m
+    return [(r, min(rows, r + step)) for r in range(0, rows, step)]
 
 
 # how often each form carried a matrix collective (for tests and the metrics sink)
-op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0}
+op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0}
 
 
 def _skip() -> bool:
@@ -142,12 +158,23 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
         out = opc.spmm(A, H)
         dist.all_reduce(out, group=group)
         return out if relu_mask is None else opc.relu_backward(out, relu_mask)
-    ax.ensure(rows * D * H.element_size())
-    epoch, buf = ax.next_op()
-    out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
-    if relu_mask is not None and relu_mask.dtype != out.dtype:
-        relu_mask = relu_mask.to(out.dtype)
-    _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
+    blocks = _row_blocks(rows, D * H.element_size())
+    if relu_mask is not None and relu_mask.dtype != H.dtype:
+        relu_mask = relu_mask.to(H.dtype)
+    if len(blocks) == 1:
+        ax.ensure(rows * D * H.element_size())
+        epoch, buf = ax.next_op()
+        out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
+        _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
+    else:
+        # one op per row block: the receive slots stay bounded
+        op_counts["row_blocked"] += 1
+        out = torch.empty((rows, D), dtype=H.dtype, device=H.device)
+        ax.ensure(max(r1 - r0 for r0, r1 in blocks) * D * H.element_size())
+        for r0, r1 in blocks:
+            epoch, buf = ax.next_op()
+            opc.spmm(A, H, row_range=(r0, r1), out=out[r0:r1], push_ptrs=ax.push_targets(buf), push_ld=D)
+            _reduce(ax, out[r0:r1], buf, epoch, False, None if relu_mask is None else relu_mask[r0:r1], KID_SPMM)
     op_counts["one_shot"] += 1
     return out
 
@@ -204,10 +231,21 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
         out = opc.gemm(a, W, trans_b=trans_b, relu=False)
         dist.all_reduce(out, group=group)
         return torch.relu_(out) if relu else out
-    ax.ensure(rows * N * a.element_size())
-    epoch, buf = ax.next_op()
-    out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
-    _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
+    blocks = _row_blocks(rows, N * a.element_size())
+    if len(blocks) == 1:
+        ax.ensure(rows * N * a.element_size())
+        epoch, buf = ax.next_op()
+        out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
+        _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
+    else:
+        op_counts["row_blocked"] += 1
+        out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+        ax.ensure(max(r1 - r0 for r0, r1 in blocks) * N * a.element_size())
+        for r0, r1 in blocks:
+            epoch, buf = ax.next_op()
+            opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
+                     out=out[r0:r1])
+            _reduce(ax, out[r0:r1], buf, epoch, relu, None, KID_GEMM)
     op_counts["one_shot"] += 1
     return out
 

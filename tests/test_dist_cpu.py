@@ -24,6 +24,8 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
         fused.SMALL_MESSAGE_BYTES = flags.get("small_bytes", fused.SMALL_MESSAGE_BYTES)
         fused.ONE_SHOT_MAX_RANKS = flags.get("one_shot_ranks", fused.ONE_SHOT_MAX_RANKS)
         fused.TWO_SHOT = flags.get("two_shot", False)
+        fused.MAX_MESSAGE_BYTES = flags.get("max_message_bytes", fused.MAX_MESSAGE_BYTES)
+        fused.ROW_BLOCK_MULTIPLE = flags.get("row_block_multiple", fused.ROW_BLOCK_MULTIPLE)
     plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
              block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
              tune_gemms=flags.get("tune", False), comm=comm)
@@ -296,3 +298,12 @@ def _dropout_worker(rank, world, grid):
 def test_dropout_masks_do_not_depend_on_the_grid(grid):
     """Net(dropout=p): every grid drops the same elements as the serial model with the same seed."""
     run_distributed(_dropout_worker, grid[0] * grid[1] * grid[2], grid)
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 2)])
+def test_fused_host_code_row_blocked_messages(grid):
+    """A cap on the bytes per op splits every fused all-reduce in row blocks (one op each)."""
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, False,
+                    dict(EMU, one_shot_ranks=8, max_message_bytes=1200, row_block_multiple=8,
+                         expect_ops={"one_shot": True, "library": False, "row_blocked": True}))
