@@ -290,14 +290,22 @@ def all_gather(t: torch.Tensor, group) -> torch.Tensor:
     if not ax.same_host:
         dist.all_gather_into_tensor(out, t, group=group)
         return out
-    ax.ensure(nbytes)
-    epoch, buf = ax.next_op()
     base = out.data_ptr()
-    C.push_copy(t, ax.push_targets(buf) + [base + ax.rank * nbytes])
-    remote, local = ax.sync(buf)
-    C.gather_slots(ax.recv_slots(buf), [base + q * nbytes for q in ax.peers], nbytes, remote, local,
-                   epoch, ax.timeout_ms, KID_GATHER, opc.status_buffer(t.device))
-    opc._count(2)
+    st = opc.status_buffer(t.device)
+    # pieces of at most MAX_MESSAGE_BYTES (16-byte multiples), one op each: bounded receive slots
+    piece = max(16, MAX_MESSAGE_BYTES // 16 * 16)
+    ax.ensure(min(nbytes, piece))
+    flat = t.view(-1)
+    esz = t.element_size()
+    for off in range(0, nbytes, piece):
+        n = min(piece, nbytes - off)
+        epoch, buf = ax.next_op()
+        src = flat[off // esz : (off + n) // esz]
+        C.push_copy(src, ax.push_targets(buf) + [base + ax.rank * nbytes + off])
+        remote, local = ax.sync(buf)
+        C.gather_slots(ax.recv_slots(buf), [base + q * nbytes + off for q in ax.peers], n, remote, local,
+                       epoch, ax.timeout_ms, KID_GATHER, st)
+        opc._count(2)
     return out
 
 

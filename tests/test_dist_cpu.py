@@ -307,3 +307,26 @@ def test_fused_host_code_row_blocked_messages(grid):
     run_distributed(_worker, world, grid, 3, True, 61, 10, 5, 12, False,
                     dict(EMU, one_shot_ranks=8, max_message_bytes=1200, row_block_multiple=8,
                          expect_ops={"one_shot": True, "library": False, "row_blocked": True}))
+
+
+def _gather_pieces_worker(rank, world):
+    import plexus_b200 as plx
+    from plexus_b200.parallel import emulator, fused
+
+    emulator.enable()
+    fused.MAX_MESSAGE_BYTES = 64  # 4 pieces of 64 bytes + a remainder
+    grid = plx.init(world, 1, 1, device="cpu", comm="fused")
+    g = grid.group("x")
+    for n in (70, 16, 3):
+        mine = torch.arange(n, dtype=torch.float32) + 1000 * rank
+        got = fused.all_gather(mine, g)
+        want = torch.cat([torch.arange(n, dtype=torch.float32) + 1000 * r for r in range(world)])
+        assert torch.equal(got, want), n
+    two_d = fused.all_gather(torch.full((5, 6), float(rank)), g)
+    assert two_d.shape == (5 * world, 6) and torch.equal(two_d[5 * rank], torch.full((6,), float(rank)))
+    emulator.ops.check_status()
+    plx.shutdown()
+
+
+def test_fused_all_gather_in_pieces():
+    run_distributed(_gather_pieces_worker, 3)
