@@ -51,9 +51,10 @@ def parse_args():
     p.add_argument("--classes", type=int, default=CONFIG["classes"])
     p.add_argument("--layers", type=int, default=CONFIG["layers"])
     p.add_argument("--no_e2e", action="store_true")
-    p.add_argument("--exposed_comm", action="store_true",
-                   help="after the timed regions, time the same epochs with collectives skipped and report "
-                        "exposed communication = epoch time minus that (N > 1)")
+    p.add_argument("--exposed_comm", action="store_true", help="(default for N > 1; kept for old command lines)")
+    p.add_argument("--no_exposed_comm", action="store_true",
+                   help="skip the extra phase that, after the timed regions, times the same epochs with "
+                        "collectives skipped and reports exposed communication = epoch time minus that")
     p.add_argument("--sharded_data", action="store_true",
                    help="every rank generates only its own shards; --edges then counts raw generator edges "
                         "before de-duplication (for graphs whose global edge list does not fit one GPU)")
@@ -308,7 +309,7 @@ def run_ours(args):
                       "d2h_bytes_per_step": 4, "last_loss": loss_host}
     # ---- exposed communication: the same epochs with every collective replaced by a local stand-in
     # of the same shapes (results are wrong, kernel times are the same); outside the timed regions
-    if world > 1 and args.exposed_comm:
+    if world > 1 and not args.no_exposed_comm:
         compute_ms = -1.0
         try:
             plx.runtime.flags.skip_collectives = True
@@ -347,8 +348,12 @@ def run_reference(args):
         return
     rank, world, local = setup_distributed(args)
     sys.path.insert(0, ROOT)
-    # shard construction uses this repository's data pipeline (the reference's own loader needs
-    # torch_geometric / ogb datasets); everything inside the timed step is reference code
+    # Shard construction uses this repository's data pipeline as plain torch ops (the reference's
+    # own loader needs torch_geometric / ogb datasets).  The compiled extension stays out of this
+    # process: with the switch below every start-up op takes its torch implementation on the GPU
+    # and a kernel of this package could not be launched even by accident.  Everything inside the
+    # timed step is reference code.
+    os.environ["PLEXUS_DISABLE_NATIVE"] = "1"
     from plexus_b200.parallel import grid as pgrid
     from plexus_b200 import runtime as prt
     from plexus_b200.utils.dataloader import DataLoader as ShardBuilder
@@ -411,8 +416,11 @@ def run_reference(args):
     clocks = sampler.stop()
     ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
     rec = base_record(args, world, grid, nnz)
+    with open("/proc/self/maps") as f:
+        own_native = any("plexus_b200/_C" in line for line in f)
     rec.update({"impl": "reference", "value": ms / 1e3, "ms_per_step": ms, "dtype": "fp32",
                 "clocks": clocks, "gpu_launches": 0, "final_loss": float(loss),
+                "plexus_b200_extension_mapped": own_native,
                 "note": "reference example keeps its layers in a plain list, so its optimizer "
                         "updates only the input features"})
     if not args.no_e2e:

@@ -17,13 +17,24 @@ def so_path() -> str:
     return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
 
 
+def disabled() -> bool:
+    """``PLEXUS_DISABLE_NATIVE=1`` keeps the extension out of the process: the start-up data ops
+    then run as plain torch ops (on whatever device their tensors live on) and any attempt to
+    launch one of the package's kernels raises.  Used by tools that must not map ``_C.so``, such
+    as the baseline arm of ``bench.py`` while it builds its input shards."""
+    return os.environ.get("PLEXUS_DISABLE_NATIVE", "0") not in ("", "0")
+
+
 def available() -> bool:
-    return os.path.exists(so_path())
+    return not disabled() and os.path.exists(so_path())
 
 
 def load():
     global _mod
     if _mod is None:
+        if disabled():
+            raise RuntimeError("plexus_b200's native extension is disabled in this process "
+                               "(PLEXUS_DISABLE_NATIVE is set)")
         import torch  # noqa: F401  (libtorch must be loaded before the extension)
 
         if not available():
