@@ -2,11 +2,13 @@
 
 Two on-disk forms:
 
-* **sharded** (``<dir>/rank{r}.pt`` + ``meta.json``): each rank writes its own
-  model ``state_dict`` (keys ``layers.{l}.weight``), optimizer state, feature
-  shard, RNG state and epoch.  Files are written to a temporary name and
-  renamed, so a crash mid-write never leaves a truncated checkpoint under the
-  final name.  Resuming needs the same grid.
+* **sharded** (``<dir>/step_<epoch>/rank{r}.pt`` + ``<dir>/meta.json``): each rank
+  writes its own model ``state_dict`` (keys ``layers.{l}.weight``), optimizer
+  state, feature shard, RNG state and epoch.  Files are written to a temporary
+  name and renamed, every save goes to its own sub-directory, and ``meta.json``
+  (replaced atomically after all ranks finished) names the sub-directory of
+  the last complete save - so a crash at any point of a save leaves the
+  previous checkpoint intact and consistent.  Resuming needs the same grid.
 * **consolidated** (one file): the full unpadded weight matrices ``W_l``, the
   full feature matrix and, optionally, the Adam moments in the same full
   layout.  It does not depend on the grid, so a run can resume on a different
@@ -55,10 +57,26 @@ def _barrier():
 
 
 # ------------------------------------------------------------------ sharded
-def save_sharded(ckpt_dir: str, model, optimizer, features, epoch: int, extra: Optional[dict] = None):
+def _step_dir(epoch: int) -> str:
+    return f"step_{int(epoch):08d}"
+
+
+def save_sharded(ckpt_dir: str, model, optimizer, features, epoch: int, extra: Optional[dict] = None,
+                 keep: int = 2):
+    """Write one checkpoint as ``<dir>/step_<epoch>/rank{r}.pt`` and publish it in ``meta.json``.
+
+    A checkpoint becomes visible only when ``meta.json`` is replaced (atomically, by rank 0,
+    after every rank has finished its file), and the files of the previously published
+    checkpoint are never touched by a later save: a rank that dies while saving leaves the old
+    ``meta.json`` pointing at a complete, consistent set of rank files.  The last ``keep``
+    published checkpoints are kept on disk.
+    """
+    import shutil
+
     rank, world = _world()
     g = get_grid()
-    os.makedirs(ckpt_dir, exist_ok=True)
+    sub = _step_dir(epoch)
+    os.makedirs(os.path.join(ckpt_dir, sub), exist_ok=True)
     state = {
         "model": {k: v.detach().cpu() for k, v in model.state_dict().items()},
         "optimizer": optimizer.state_dict() if optimizer is not None else None,
@@ -72,20 +90,31 @@ def save_sharded(ckpt_dir: str, model, optimizer, features, epoch: int, extra: O
         "grid": (g.X, g.Y, g.Z),
         "rank": rank,
     }
-    _atomic_torch_save(state, os.path.join(ckpt_dir, f"rank{rank}.pt"))
+    _atomic_torch_save(state, os.path.join(ckpt_dir, sub, f"rank{rank}.pt"))
     _barrier()
     if rank == 0:
-        meta = {"grid": [g.X, g.Y, g.Z], "world_size": world, "epoch": epoch, "format": 1}
+        meta = {"grid": [g.X, g.Y, g.Z], "world_size": world, "epoch": epoch, "format": 2, "dir": sub}
         meta.update(extra or {})
         tmp = os.path.join(ckpt_dir, "meta.json.tmp")
         with open(tmp, "w") as f:
             json.dump(meta, f)
+            f.flush()
+            os.fsync(f.fileno())
         os.replace(tmp, os.path.join(ckpt_dir, "meta.json"))
+        # drop checkpoints older than the last `keep` (the one just published included)
+        steps = sorted(d for d in os.listdir(ckpt_dir) if d.startswith("step_") and d <= sub)
+        for d in steps[: max(0, len(steps) - max(1, keep))]:
+            shutil.rmtree(os.path.join(ckpt_dir, d), ignore_errors=True)
     _barrier()
 
 
 def load_sharded(ckpt_dir: str, model, optimizer, features) -> int:
-    """Restore this rank's shard; returns the epoch to resume from."""
+    """Restore this rank's shard; returns the epoch to resume from.
+
+    Raises :class:`CheckpointError` if the rank file does not belong to the published checkpoint
+    (other epoch or grid than ``meta.json`` states) or if the ranks would resume from different
+    epochs.
+    """
     rank, world = _world()
     g = get_grid()
     meta_path = os.path.join(ckpt_dir, "meta.json")
@@ -98,11 +127,23 @@ def load_sharded(ckpt_dir: str, model, optimizer, features) -> int:
             f"sharded checkpoint was written on grid {meta['grid']}, current grid is "
             f"{[g.X, g.Y, g.Z]}; use the consolidated form to change the grid"
         )
-    path = os.path.join(ckpt_dir, f"rank{rank}.pt")
+    # format 1 kept the rank files next to meta.json
+    path = os.path.join(ckpt_dir, meta.get("dir", ""), f"rank{rank}.pt")
     try:
         state = torch.load(path, weights_only=False, map_location="cpu")
     except Exception as e:
         raise CheckpointError(f"cannot read {path}: {e}") from e
+    if int(state["epoch"]) != int(meta["epoch"]) or tuple(state["grid"]) != tuple(meta["grid"]):
+        raise CheckpointError(
+            f"{path} holds epoch {state['epoch']} on grid {list(state['grid'])}, but meta.json publishes "
+            f"epoch {meta['epoch']} on grid {meta['grid']}: the checkpoint is inconsistent")
+    if world > 1:
+        # every rank must resume from the same epoch, or their collective sequences diverge
+        dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+        lo_hi = torch.tensor([-int(state["epoch"]), int(state["epoch"])], dtype=torch.int64, device=dev)
+        dist.all_reduce(lo_hi, op=dist.ReduceOp.MAX)
+        if -int(lo_hi[0]) != int(lo_hi[1]):
+            raise CheckpointError(f"ranks hold checkpoints of different epochs ({-int(lo_hi[0])} .. {int(lo_hi[1])})")
     model.load_state_dict(state["model"])
     if optimizer is not None and state["optimizer"] is not None:
         optimizer.load_state_dict(state["optimizer"])

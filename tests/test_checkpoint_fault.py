@@ -55,8 +55,9 @@ def _sharded_worker(rank, world, grid, ckdir):
 
 def test_sharded_checkpoint_resume(tmp_path):
     run_distributed(_sharded_worker, 2, (2, 1, 1), str(tmp_path / "ck"))
-    assert (tmp_path / "ck" / "meta.json").exists() and (tmp_path / "ck" / "rank1.pt").exists()
-    assert not [f for f in os.listdir(tmp_path / "ck") if ".tmp" in f]
+    assert (tmp_path / "ck" / "meta.json").exists()
+    assert (tmp_path / "ck" / "step_00000001" / "rank1.pt").exists()
+    assert not [f for _, _, fs in os.walk(tmp_path / "ck") for f in fs if ".tmp" in f]
 
 
 def _save_consolidated_worker(rank, world, grid, path, out):
@@ -112,8 +113,9 @@ def test_truncated_or_mismatched_checkpoint_is_rejected(tmp_path):
     _step(model, opt, adj, feats, labels, N, C)
     d = str(tmp_path / "ck")
     ck.save_sharded(d, model, opt, feats, epoch=0)
-    blob = open(os.path.join(d, "rank0.pt"), "rb").read()
-    open(os.path.join(d, "rank0.pt"), "wb").write(blob[: len(blob) // 2])  # crash mid-write of a later save
+    f0 = os.path.join(d, "step_00000000", "rank0.pt")
+    blob = open(f0, "rb").read()
+    open(f0, "wb").write(blob[: len(blob) // 2])  # a damaged file under the published name
     with pytest.raises(ck.CheckpointError, match="cannot read"):
         ck.load_sharded(d, model, opt, feats)
     os.remove(os.path.join(d, "meta.json"))
@@ -127,6 +129,44 @@ def test_truncated_or_mismatched_checkpoint_is_rejected(tmp_path):
     json.dump(meta, open(os.path.join(d, "meta.json"), "w"))
     with pytest.raises(ck.CheckpointError, match="grid"):
         ck.load_sharded(d, model, opt, feats)
+
+
+def test_interrupted_save_keeps_the_previous_checkpoint(tmp_path):
+    """A save that dies before publishing (rank files of the new epoch exist, meta.json still names
+    the old one) must not be picked up, and a rank file from another epoch placed under the
+    published directory is rejected instead of being mixed in."""
+    import shutil
+
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup((1, 1, 1))
+    _step(model, opt, adj, feats, labels, N, C)
+    d = str(tmp_path / "ck")
+    ck.save_sharded(d, model, opt, feats, epoch=0)
+    w0 = {k: v.clone() for k, v in model.state_dict().items()}
+    meta_before = open(os.path.join(d, "meta.json")).read()
+    _step(model, opt, adj, feats, labels, N, C)
+    ck.save_sharded(d, model, opt, feats, epoch=1)
+    # undo the publication of epoch 1: this is what the directory looks like when a rank died
+    # after writing its epoch-1 file and before rank 0 replaced meta.json
+    open(os.path.join(d, "meta.json"), "w").write(meta_before)
+    assert ck.load_sharded(d, model, opt, feats) == 1
+    assert all(torch.equal(v, w0[k]) for k, v in model.state_dict().items())
+    # a later epoch's file under the published directory: refuse to mix epochs
+    shutil.copy(os.path.join(d, "step_00000001", "rank0.pt"), os.path.join(d, "step_00000000", "rank0.pt"))
+    with pytest.raises(ck.CheckpointError, match="inconsistent"):
+        ck.load_sharded(d, model, opt, feats)
+
+
+def test_sharded_save_prunes_old_steps(tmp_path):
+    from plexus_b200.utils import checkpoint as ck
+
+    plx, model, opt, adj, feats, labels, N, F, C = _setup((1, 1, 1))
+    d = str(tmp_path / "ck")
+    for e in range(4):
+        ck.save_sharded(d, model, opt, feats, epoch=e)
+    assert sorted(x for x in os.listdir(d) if x.startswith("step_")) == ["step_00000002", "step_00000003"]
+    assert ck.load_sharded(d, model, opt, feats) == 4
 
 
 # ------------------------------------------------------------------ failure detection
