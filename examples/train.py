@@ -95,13 +95,16 @@ def train(model, optimizer, features_local, adj_shards, labels, num_nodes, num_c
 
 
 def _parse_injection(spec):
-    """``rank:epoch[:kind]`` with kind ``exit`` (default), ``raise`` or ``stall``; None if unset."""
+    """``rank:epoch[:kind]`` with kind ``exit`` (default), ``raise``, ``stall`` or ``status``; None if unset.
+
+    ``status`` fakes, on the host, what a kernel leaves behind when one of its bounded waits gives
+    up: a TIMEOUT record in the status words, which the check after the step must turn into an error."""
     if not spec:
         return None
     parts = spec.split(":")
     kind = parts[2] if len(parts) > 2 else "exit"
-    if kind not in ("exit", "raise", "stall"):
-        raise SystemExit("PLEXUS_INJECT_FAILURE kind must be exit, raise or stall")
+    if kind not in ("exit", "raise", "stall", "status"):
+        raise SystemExit("PLEXUS_INJECT_FAILURE kind must be exit, raise, stall or status")
     return int(parts[0]), int(parts[1]), kind
 
 
@@ -244,6 +247,8 @@ def main(argv=None):
                 os._exit(3)
             if inject[2] == "raise":
                 raise RuntimeError(f"injected failure on rank {rank} before epoch {i}")
+            if inject[2] == "status":
+                plx.runtime.inject_status_timeout()
             if inject[2] == "stall":
                 import time as _time
 
@@ -271,6 +276,10 @@ def main(argv=None):
         loss_val = float(loss)
         if watchdog is not None:
             watchdog.end()
+        # a kernel whose bounded wait gave up returned without its result: stop here, before the
+        # loss is reported as valid and before a checkpoint could persist the damaged state (the
+        # supervisor then restarts from the last good checkpoint)
+        plx.check_status()
         if rank == 0:
             print("Epoch: {:03d}, Train Loss: {:.4f}".format(i, loss_val))
         rec = dict(event="epoch", epoch=i, loss=loss_val, peak_mem_gb=peak_memory_gb(),

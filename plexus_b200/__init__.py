@@ -12,7 +12,7 @@ under the module names of hpcgroup/plexus):
 """
 
 from . import runtime
-from .runtime import flags, init, shutdown, choose_grid  # noqa: F401
+from .runtime import flags, init, shutdown, choose_grid, check_status  # noqa: F401
 from .models.gcn_conv import GCNConv, GCNConvFunction, GCNStackFunction  # noqa: F401
 from .models.cross_entropy import parallel_cross_entropy, parallel_accuracy  # noqa: F401
 from .models.net import Net, SerialGCN  # noqa: F401

@@ -116,6 +116,46 @@ def init(
     return g
 
 
+def check_status() -> None:
+    """Raise :class:`plexus_b200.parallel.watchdog.PlexusCommTimeout` if a kernel's bounded wait (on a
+    peer's flag, or on one of its own asynchronous copies) gave up since the last check.
+
+    Such a kernel returns without producing its result, so everything computed after it in the step
+    is garbage: call this after each step (it synchronises the device) and before anything derived
+    from the step is persisted - a checkpoint above all.
+    """
+    if flags.comm == "fused":
+        from .parallel import emulator
+
+        if emulator.active():
+            emulator.ops.check_status()
+            return
+    if torch.cuda.is_available():
+        from .ops import cuda as _opc
+
+        _opc.check_status()
+
+
+def inject_status_timeout(kernel_id: int = 99) -> None:
+    """Host-side fault injection: write the record a kernel leaves when a bounded wait runs out
+    (``TIMEOUT, kernel, peer, expected, seen``) into the status words, without running any kernel."""
+    from .parallel.watchdog import STATUS_TIMEOUT
+
+    rec = torch.tensor([STATUS_TIMEOUT, kernel_id, 0, 1, 0], dtype=torch.int32)
+    if flags.comm == "fused":
+        from .parallel import emulator
+
+        if emulator.active():
+            emulator.ops.status_buffer()[:5] = rec
+            return
+    if torch.cuda.is_available():
+        from .ops import cuda as _opc
+
+        _opc.status_buffer()[:5] = rec.to(_opc.status_buffer().device)
+        return
+    raise RuntimeError("no status words on this path (CPU ranks without the peer-memory emulation)")
+
+
 def shutdown() -> None:
     """Forget the grid (process groups are left to ``destroy_process_group``)."""
     if flags.comm == "fused":

@@ -88,6 +88,29 @@ def _clean_two_rank_losses(tmp_path, base):
     return _CLEAN["losses"]
 
 
+def test_a_wait_that_gave_up_stops_the_run_before_the_next_checkpoint(tmp_path):
+    """Emulated peer memory on two CPU ranks; the status words get a TIMEOUT record before epoch 2
+    (what a kernel leaves when a bounded wait runs out).  The check after the step must end the run
+    with an error, and the checkpoint due after epoch 2 must not exist: the published one stays
+    that of epoch 1."""
+    args = ["--synthetic", "600,4000,12,4", "--num_gcn_layers", "3", "--hidden_size", "16", "--seed", "2",
+            "--dtype", "fp32", "--G_intra_d", "2", "--comm", "fused", "--num_epochs", "4",
+            "--checkpoint_dir", str(tmp_path / "ck"), "--checkpoint_every", "1"]
+    env = dict(os.environ, OMP_NUM_THREADS="2", PLEXUS_EMULATE_PEER_MEMORY="1", PLEXUS_INJECT_FAILURE="0:2:status")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29619", os.path.join(ROOT, "examples", "train.py"),
+           "--backend", "gloo"] + args
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(tmp_path))
+    assert r.returncode != 0
+    assert "PlexusCommTimeout" in r.stderr + r.stdout
+    assert len(_losses(r.stdout)) == 2  # epochs 0 and 1 were reported, epoch 2 was not
+    meta = json.loads((tmp_path / "ck" / "meta.json").read_text())
+    assert meta["epoch"] == 1
+    # the healthy rank may have started its own file of epoch 2; the failed rank wrote none and the
+    # save was never published
+    assert not (tmp_path / "ck" / "step_00000002" / "rank0.pt").exists()
+
+
 def test_supervisor_restarts_from_the_last_checkpoint_after_a_lost_rank(tmp_path):
     """Rank 1 exits before epoch 2 (host-side injection); the supervisor resumes and the losses of the
     interrupted run continue exactly where an uninterrupted run goes."""
