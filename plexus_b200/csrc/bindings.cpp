@@ -127,6 +127,40 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
                              s, scr, scr_n, push.n ? &push : nullptr, static_cast<int>(variant), stream()));
 }
 
+// Tensor-core SpMM (bf16): block_start covers every row of [row_begin, row_begin + out.size(0)).
+void spmm_mma(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
+              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
+              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t staging, int64_t push_seg_rows,
+              int64_t push_me, const Tensor& status) {
+  TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
+  TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
+              "spmm: int32 CSR indices required");
+  TORCH_CHECK(val.scalar_type() == at::kFloat, "spmm: fp32 CSR values required");
+  TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && val.is_contiguous());
+  TORCH_CHECK(H.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "spmm_mma: bf16 features required");
+  TORCH_CHECK(H.dim() == 2 && out.dim() == 2 && H.stride(1) == 1 && out.stride(1) == 1);
+  const int64_t D = H.size(1);
+  TORCH_CHECK(out.size(1) == D, "spmm: bad output shape");
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == H.scalar_type() && mask->size(1) == D &&
+                mask->size(0) == out.size(0) && mask->stride(1) == 1, "spmm: bad mask");
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  const int nb = block_start.numel() > 0 ? static_cast<int>(block_start.numel()) - 1 : 0;
+  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
+  TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
+              "spmm: row segments do not cover the output");
+  c10::cuda::CUDAGuard guard(H.device());
+  check(plx::launch_spmm_mma(rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(), H.data_ptr(),
+                             H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm, static_cast<int>(D),
+                             static_cast<int>(row_begin), int_ptr(block_start), nb, push.n ? &push : nullptr,
+                             static_cast<int>(staging), status_ptr(status), stream()));
+}
+
 int64_t spmm_scratch_per_piece(const Tensor& H) {
   return plx::spmm_scratch_per_piece(dtype_of(H), static_cast<int>(H.size(1)));
 }
@@ -500,6 +534,7 @@ std::vector<int64_t> gemm_prof() {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("spmm_csr", &spmm_csr, "CSR SpMM, bf16/fp32 features, fp32 accumulate");
+  m.def("spmm_mma", &spmm_mma, "CSR SpMM on the tensor cores (bf16 features, fp32 accumulate)");
   m.def("spmm_piece_size", &plx::spmm_piece_size);
   m.def("spmm_scratch_per_piece", &spmm_scratch_per_piece);
   m.def("gemm_nt", &gemm_nt, "C = A . B^T on tcgen05 (bf16 in, fp32 accumulate)");

@@ -54,6 +54,15 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
 // memory and summed by warp-level MMAs (bf16 features up to 256 columns; other cases use FMA).
 enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
 
+// ---- spmm_mma.cu
+// Tensor-core SpMM for bf16 features (any D that is a multiple of 8): every row of
+// block_start[0] .. block_start[num_blocks] in one launch, rows of any length (no pieces, no
+// scratch).  staging: 0 = 16-byte cp.async copies, 1 = one bulk copy per gathered row.
+const char* launch_spmm_mma(const int* rowptr, const int* col, const float* val, const void* H, int64_t ldh,
+                            void* out, int64_t ldo, const void* mask, int64_t ldm, int D, int row_begin,
+                            const int* block_start, int num_blocks, const PushTargets* push, int staging,
+                            int* status, cudaStream_t stream);
+
 // ---- gemm_tcgen05.cu
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,

@@ -64,9 +64,16 @@ def _csr_parts(A):
     return crow, col, val
 
 
-# default accumulation variant of the SpMM kernels: 1 = packed-FMA (fastest measured), 0 = warp-MMA
-# (staged rows + tensor-core sum; correct but measured ~2x slower, kept selectable for tuning)
-SPMM_VARIANT = int(__import__("os").environ.get("PLEXUS_SPMM_VARIANT", "1"))
+# SpMM kernel variants:
+#   1 = CUDA-core kernel (packed fp32x2 multiply-adds; also the only one for fp32 features),
+#   2 = tensor-core kernel, gathered rows staged by 16-byte cp.async copies,
+#   3 = tensor-core kernel, one bulk copy (cp.async.bulk) per gathered row,
+#   0 = the older warp-MMA accumulation inside the CUDA-core kernel's structure (kept for comparison).
+SPMM_VARIANT = int(os.environ.get("PLEXUS_SPMM_VARIANT", "3"))
+# rows longer than this stay with the CUDA-core kernel, which cuts them in pieces across warps; the
+# tensor-core kernel walks a row with one warp
+SPMM_MMA_MAX_ROW = int(os.environ.get("PLEXUS_SPMM_MMA_MAX_ROW", str(1 << 17)))
+SPMM_MMA_BLOCK_COST = int(os.environ.get("PLEXUS_SPMM_MMA_BLOCK_COST", "4096"))
 
 # per-row constant added to the nonzero count when balancing row blocks, and the cost of a block
 SPMM_ROW_COST = 8
@@ -143,6 +150,44 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
     return sch
 
 
+def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None):
+    """``block_start`` for the tensor-core kernel: consecutive rows of about ``SPMM_MMA_BLOCK_COST``
+    nonzeros (+ a per-row constant) each, every row included; ``None`` if a row is longer than
+    ``SPMM_MMA_MAX_ROW`` (the caller then uses the CUDA-core kernel)."""
+    cache = None
+    if owner is not None:
+        cache = getattr(owner, "_plx_spmm_mma_schedules", None)
+        if cache is None:
+            cache = {}
+            try:
+                owner._plx_spmm_mma_schedules = cache
+            except Exception:
+                cache = None
+    key = (r0, r1, SPMM_MMA_BLOCK_COST)
+    if cache is not None and key in cache:
+        return cache[key]
+    dev = crow.device
+    rows = r1 - r0
+    if rows <= 0:
+        res = torch.empty(0, dtype=torch.int32, device=dev)
+    else:
+        deg = (crow[r0 + 1 : r1 + 1] - crow[r0:r1]).to(torch.int64)
+        if int(deg.max()) > SPMM_MMA_MAX_ROW:
+            res = None
+        else:
+            wcum = torch.cumsum(deg + SPMM_ROW_COST, 0)
+            total = int(wcum[-1])
+            nb = max(1, min(rows, total // SPMM_MMA_BLOCK_COST))
+            targets = (torch.arange(1, nb, device=dev, dtype=torch.float64) * (total / nb)).to(torch.int64)
+            inner = torch.searchsorted(wcum, targets, right=True)
+            res = (torch.unique_consecutive(torch.cat([
+                torch.zeros(1, dtype=torch.int64, device=dev), inner,
+                torch.full((1,), rows, dtype=torch.int64, device=dev)])) + r0).to(torch.int32)
+    if cache is not None:
+        cache[key] = res
+    return res
+
+
 DEBUG = os.environ.get("PLEXUS_DEBUG", "0") not in ("", "0")
 
 
@@ -162,7 +207,7 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
     ``push_seg = (rows per owner, this rank's position)``: reduce-scatter push (each row goes only
     to the rank that owns it) instead of the broadcast push.
-    ``variant``: 1 = packed-FMA accumulation (default), 0 = warp-MMA accumulation."""
+    ``variant``: see ``SPMM_VARIANT`` (default: the tensor-core kernel for bf16 features)."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -182,12 +227,24 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
         out = torch.empty((r1 - r0, H.shape[1]), dtype=H.dtype, device=H.device)
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
+    variant = SPMM_VARIANT if variant is None else int(variant)
+    if variant in (2, 3) and H.dtype == torch.bfloat16 and H.shape[1] % 8 == 0 and r1 > r0:
+        blocks = spmm_mma_schedule(crow, r0, r1, owner=A)
+        if blocks is not None:
+            C.spmm_mma(crow, col, val, H, out, relu_mask, r0, blocks, list(push_ptrs), int(push_ld),
+                       1 if variant == 3 else 0, int(push_seg[0]), int(push_seg[1]), status_buffer(H.device))
+            _count(-(-H.shape[1] // 256))
+            if out_dtype is not None and out_dtype != out.dtype:
+                out = out.to(out_dtype)
+            return out
+    if variant in (2, 3):
+        variant = 1
     sch = spmm_schedule(crow, r0, r1, owner=A)
     npieces = sch.piece_beg.numel()
     scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
     C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
                sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld),
-               SPMM_VARIANT if variant is None else int(variant), int(push_seg[0]), int(push_seg[1]))
+               variant, int(push_seg[0]), int(push_seg[1]))
     _count(sch.launches)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)

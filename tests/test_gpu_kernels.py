@@ -28,7 +28,8 @@ def _random_csr(rows, cols, mean_deg, long_row=None, empty_every=7, seed=0):
     return torch.sparse_csr_tensor(crow.int(), col.int(), val, size=(rows, cols), check_invariants=False)
 
 
-@pytest.mark.parametrize("variant", [0, 1])  # 0: warp-MMA accumulation, 1: packed-FMA accumulation
+# 0: warp-MMA accumulation, 1: packed-FMA accumulation, 2 / 3: tensor-core kernel (cp.async / bulk copies)
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("D", [8, 24, 48, 104, 128, 256, 304, 608])
 def test_spmm_bf16_matches_fp32_reference(D, variant):
     from plexus_b200.ops import cuda as opc
@@ -38,6 +39,7 @@ def test_spmm_bf16_matches_fp32_reference(D, variant):
     Hb = H.to(torch.bfloat16)
     ref = torch.sparse.mm(A, Hb.float())
     out = opc.spmm(A.to(_dev()), Hb.to(_dev()), variant=variant)
+    opc.check_status()
     assert out.dtype == torch.bfloat16
     err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
     assert err < 1e-2, err
@@ -62,6 +64,61 @@ def test_spmm_long_rows_and_mask_and_row_range():
     assert (masked - want).abs().max() / ref.abs().max() < 1e-2
     part = ops.spmm(Ad, Hd, row_range=(3, 111)).float().cpu()
     assert (part - ref[3:111]).abs().max() / ref.abs().max() < 1e-2
+
+
+def _csr_from_degrees(deg, cols, seed):
+    g = torch.Generator().manual_seed(seed)
+    rows = deg.numel()
+    crow = torch.zeros(rows + 1, dtype=torch.int64)
+    crow[1:] = torch.cumsum(deg, 0)
+    nnz = int(crow[-1])
+    col = torch.randint(0, cols, (nnz,), generator=g)
+    val = torch.randn(nnz, generator=g)
+    return torch.sparse_csr_tensor(crow.int(), col.int(), val, size=(rows, cols), check_invariants=False)
+
+
+@pytest.mark.parametrize("variant", [2, 3])
+@pytest.mark.parametrize("D", [16, 48, 56, 128, 256])
+def test_spmm_tensor_core_row_patterns(D, variant):
+    """Runs of tiny rows (several rows per 16-nonzero stage, more than four: forced flushes inside a
+    stage), empty rows at the start, in the middle and at the end, rows that end exactly on a stage
+    boundary, one long row, a mask and a row range."""
+    from plexus_b200.ops import cuda as opc
+
+    g = torch.Generator().manual_seed(D)
+    cols = 3000
+    deg = torch.cat([
+        torch.zeros(5, dtype=torch.long),                      # leading empty rows
+        torch.randint(0, 4, (400,), generator=g),              # tiny rows, some empty
+        torch.full((40,), 16, dtype=torch.long),               # rows ending on stage boundaries
+        torch.randint(1, 3, (300,), generator=g),
+        torch.tensor([2500, 0, 0, 1, 33, 0]),                  # a long row among empty ones
+        torch.randint(20, 60, (500,), generator=g),            # typical rows
+        torch.zeros(9, dtype=torch.long),                      # trailing empty rows
+    ])
+    A = _csr_from_degrees(deg, cols, seed=D + 1)
+    rows = deg.numel()
+    H = torch.randn(cols, D, generator=g).to(torch.bfloat16)
+    mask = torch.randn(rows, D, generator=g).to(torch.bfloat16)
+    ref = torch.sparse.mm(A, H.float())
+    scale = ref.abs().amax(dim=1, keepdim=True).clamp_min(1e-3)
+    Ad, Hd = A.to(_dev()), H.to(_dev())
+    for block_cost in (64, 4096):
+        opc.SPMM_MMA_BLOCK_COST = block_cost
+        try:
+            out = opc.spmm(Ad, Hd, variant=variant).float().cpu()
+            opc.check_status()
+            assert ((out - ref).abs() / scale).max() < 3e-2, block_cost
+            assert float(out[deg == 0].abs().max()) == 0.0
+            masked = opc.spmm(Ad, Hd, relu_mask=mask.to(_dev()), variant=variant).float().cpu()
+            assert (((masked - ref * (mask.float() > 0)).abs()) / scale).max() < 3e-2
+            part = opc.spmm(Ad, Hd, row_range=(3, 777), variant=variant).float().cpu()
+            assert ((part - ref[3:777]).abs() / scale[3:777]).max() < 3e-2
+        finally:
+            opc.SPMM_MMA_BLOCK_COST = 4096
+    # same sums as the CUDA-core kernel up to the 2^-17 relative rounding of the split edge weights
+    base = opc.spmm(Ad, Hd, variant=1).float().cpu()
+    assert ((out - base).abs() / scale).max() < 1e-2
 
 
 def test_spmm_fp32_features_and_empty_matrix():
