@@ -44,8 +44,9 @@ plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t
   return p;
 }
 
-plx::SlotList make_slots(const std::vector<int64_t>& ptrs) {
+plx::SlotList make_slots(const std::vector<int64_t>& ptrs, int64_t me = -1) {
   plx::SlotList s;
+  s.me = static_cast<int>(me);
   TORCH_CHECK(ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS + 1), "too many slots");
   s.n = static_cast<int>(ptrs.size());
   for (int i = 0; i < s.n; ++i) s.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
@@ -342,7 +343,7 @@ void wait_flag(const Tensor& flag, int64_t expected, int64_t max_polls, Tensor& 
 void reduce_slots(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t slot_ld, bool relu,
                   const c10::optional<Tensor>& mask, const std::vector<int64_t>& remote_flags,
                   const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms,
-                  int64_t kernel_id, const Tensor& status) {
+                  int64_t kernel_id, const Tensor& status, int64_t me) {
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
   const void* mptr = nullptr;
   int64_t ldm = 0;
@@ -352,7 +353,7 @@ void reduce_slots(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t sl
     ldm = mask->stride(0);
   }
   c10::cuda::CUDAGuard guard(out.device());
-  check(plx::launch_reduce_slots_bf16(out.data_ptr(), out.stride(0), make_slots(slot_ptrs), slot_ld,
+  check(plx::launch_reduce_slots_bf16(out.data_ptr(), out.stride(0), make_slots(slot_ptrs, me), slot_ld,
                                       out.size(0), static_cast<int>(out.size(1)), relu, mptr, ldm,
                                       make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
                                       stream()));
@@ -364,7 +365,7 @@ void reduce_segment(Tensor& out, int64_t row0, int64_t rows, const std::vector<i
                     int64_t slot_ld, bool relu, const c10::optional<Tensor>& mask,
                     const std::vector<int64_t>& bcast_ptrs, const std::vector<int64_t>& remote_flags,
                     const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms,
-                    int64_t kernel_id, const Tensor& status) {
+                    int64_t kernel_id, const Tensor& status, int64_t me) {
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
   TORCH_CHECK(row0 >= 0 && rows >= 0 && row0 + rows <= out.size(0), "reduce_segment: bad row range");
   const void* mptr = nullptr;
@@ -375,7 +376,7 @@ void reduce_segment(Tensor& out, int64_t row0, int64_t rows, const std::vector<i
     ldm = mask->stride(0);
   }
   c10::cuda::CUDAGuard guard(out.device());
-  check(plx::launch_reduce_segment_bf16(out.data_ptr(), out.stride(0), row0, make_slots(slot_ptrs), slot_ld,
+  check(plx::launch_reduce_segment_bf16(out.data_ptr(), out.stride(0), row0, make_slots(slot_ptrs, me), slot_ld,
                                         rows, static_cast<int>(out.size(1)), relu, mptr, ldm,
                                         make_slots(bcast_ptrs),
                                         make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
@@ -397,10 +398,10 @@ void gather_segments(const std::vector<int64_t>& src_ptrs, const std::vector<int
 
 void reduce_slots_f32(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t op,
                       const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
-                      int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status) {
+                      int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status, int64_t me) {
   TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kFloat);
   c10::cuda::CUDAGuard guard(out.device());
-  check(plx::launch_reduce_slots_f32(out.data_ptr<float>(), make_slots(slot_ptrs), out.numel(),
+  check(plx::launch_reduce_slots_f32(out.data_ptr<float>(), make_slots(slot_ptrs, me), out.numel(),
                                      static_cast<int>(op),
                                      make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
                                      stream()));

@@ -121,6 +121,11 @@ const char* launch_wait_flag(const int* flag, int expected, unsigned max_polls, 
 struct SlotList {
   int n;
   void* ptr[MAX_PEERS + 1];
+  // For the reducing kernels: ptr[] lists the peers' partials in group-rank order with this rank
+  // left out, and `me` is this rank's position in the group.  The local partial is added at that
+  // position, so every rank of the group sums in the same order and replicas stay bitwise equal.
+  // me < 0: local partial first.
+  int me;
 };
 // Flags of one op: remote_flag[q] is this rank's entry in peer q's flag array (written here),
 // local_flag[q] is peer q's entry in this rank's flag array (polled here).

@@ -71,6 +71,16 @@ __device__ __forceinline__ bool signal_and_wait(const PeerSync& s) {
   return ok_flag != 0;
 }
 
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    acc[2 * k] += f.x;
+    acc[2 * k + 1] += f.y;
+  }
+}
+
 // out[r, c] = act( out[r, c] + sum_q slot_q[r, c] ) with fp32 accumulation, bf16 storage.
 // act = optional ReLU, then optional multiplication by (mask > 0).
 __global__ void __launch_bounds__(256)
@@ -78,34 +88,30 @@ reduce_slots_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const Slo
                          int64_t lds, int64_t rows, int cols, int relu,
                          const __nv_bfloat16* __restrict__ mask, int64_t ldm, const PeerSync sync) {
   if (!signal_and_wait(sync)) return;
+  const int my_pos = slots.me;
   const int vec_per_row = cols / 8;
   const int64_t total = rows * vec_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / vec_per_row;
     const int c = static_cast<int>(i % vec_per_row) * 8;
-    float acc[8];
-    {
-      const uint4 v = *reinterpret_cast<const uint4*>(out + r * ldo + c);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    // all loads first (they are independent), then one summation order for the whole group: the
+    // peers before this rank, the local partial, the peers after it
+    const uint4 own = *reinterpret_cast<const uint4*>(out + r * ldo + c);
+    uint4 pv[MAX_PEERS];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
-        acc[2 * k] = f.x;
-        acc[2 * k + 1] = f.y;
-      }
-    }
+    for (int q = 0; q < MAX_PEERS; ++q)
+      if (q < slots.n)
+        pv[q] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    if (my_pos <= 0) add_bf16x8(acc, own);
 #pragma unroll
     for (int q = 0; q < MAX_PEERS; ++q) {
-      if (q >= slots.n) break;
-      const uint4 v = *reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
-        acc[2 * k] += f.x;
-        acc[2 * k + 1] += f.y;
+      if (q < slots.n) {
+        add_bf16x8(acc, pv[q]);
+        if (q + 1 == my_pos) add_bf16x8(acc, own);
       }
     }
     if (relu) {
@@ -139,34 +145,30 @@ reduce_segment_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, int64_t
                            const __nv_bfloat16* __restrict__ mask, int64_t ldm, const SlotList bcast,
                            const PeerSync sync) {
   if (!signal_and_wait(sync)) return;
+  const int my_pos = slots.me;
   const int vec_per_row = cols / 8;
   const int64_t total = rows * vec_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / vec_per_row;
     const int c = static_cast<int>(i % vec_per_row) * 8;
-    float acc[8];
-    {
-      const uint4 v = *reinterpret_cast<const uint4*>(out + (row0 + r) * ldo + c);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    // all loads first (they are independent), then one summation order for the whole group: the
+    // peers before this rank, the local partial, the peers after it
+    const uint4 own = *reinterpret_cast<const uint4*>(out + (row0 + r) * ldo + c);
+    uint4 pv[MAX_PEERS];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
-        acc[2 * k] = f.x;
-        acc[2 * k + 1] = f.y;
-      }
-    }
+    for (int q = 0; q < MAX_PEERS; ++q)
+      if (q < slots.n)
+        pv[q] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    if (my_pos <= 0) add_bf16x8(acc, own);
 #pragma unroll
     for (int q = 0; q < MAX_PEERS; ++q) {
-      if (q >= slots.n) break;
-      const uint4 v = *reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
-        acc[2 * k] += f.x;
-        acc[2 * k + 1] += f.y;
+      if (q < slots.n) {
+        add_bf16x8(acc, pv[q]);
+        if (q + 1 == my_pos) add_bf16x8(acc, own);
       }
     }
     if (relu) {
@@ -219,10 +221,14 @@ reduce_slots_f32_kernel(float* __restrict__ out, const SlotList slots, int64_t n
   if (!signal_and_wait(sync)) return;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float a = out[i];
+    // group-rank order on every rank (see SlotList::me)
+    const float own = out[i];
+    float a = op == 0 ? 0.f : own;
+    if (op == 0 && slots.me <= 0) a += own;
     for (int q = 0; q < slots.n; ++q) {
       const float b = static_cast<const float*>(slots.ptr[q])[i];
       a = op == 0 ? a + b : fmaxf(a, b);
+      if (op == 0 && q + 1 == slots.me) a += own;
     }
     out[i] = a;
   }

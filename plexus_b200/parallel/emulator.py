@@ -99,14 +99,25 @@ class _Kernels:
         for a in dst_ptrs:
             _copy(a, src)
 
-    def reduce_slots(self, out, slot_ptrs, slot_ld, relu, mask, remote, local, epoch, timeout_ms, kid, status):
+    @staticmethod
+    def _ordered_sum(own, others, me, acc_dtype):
+        """Sum in group-rank order (the local operand at position ``me``), like the kernels do, in
+        ``acc_dtype``: every rank of the group then gets bitwise the same result."""
+        terms = list(others)
+        terms.insert(max(0, min(me, len(terms))) if me >= 0 else 0, own)
+        acc = torch.zeros_like(own, dtype=acc_dtype)
+        for t in terms:
+            acc = acc + t.to(acc_dtype)
+        return acc
+
+    def reduce_slots(self, out, slot_ptrs, slot_ld, relu, mask, remote, local, epoch, timeout_ms, kid, status,
+                     me=-1):
         if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
             return
         rows, cols = out.shape
-        acc = out.double()
-        for a in slot_ptrs:
-            acc += _view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols].double()
-        self._finish(out, acc, relu, mask)
+        acc_dtype = torch.float64 if out.dtype == torch.float64 else torch.float32
+        others = [_view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols] for a in slot_ptrs]
+        self._finish(out, self._ordered_sum(out, others, me, acc_dtype), relu, mask)
 
     @staticmethod
     def _finish(out, acc, relu, mask):
@@ -116,13 +127,16 @@ class _Kernels:
             acc = acc * (mask > 0)
         out.copy_(acc.to(out.dtype))
 
-    def reduce_slots_f32(self, out, slot_ptrs, op, remote, local, epoch, timeout_ms, kid, status):
+    def reduce_slots_f32(self, out, slot_ptrs, op, remote, local, epoch, timeout_ms, kid, status, me=-1):
         if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
             return
         n = out.numel()
-        for a in slot_ptrs:
-            other = _view(a, n, out.dtype)
-            out.copy_(out + other if op == 0 else torch.maximum(out, other))
+        others = [_view(a, n, out.dtype) for a in slot_ptrs]
+        if op == 0:
+            out.copy_(self._ordered_sum(out, others, me, out.dtype))
+        else:
+            for other in others:
+                out.copy_(torch.maximum(out, other))
 
     def gather_slots(self, src_ptrs, dst_ptrs, nbytes, remote, local, epoch, timeout_ms, kid, status):
         if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
@@ -131,14 +145,14 @@ class _Kernels:
             ctypes.memmove(d, s, nbytes)
 
     def reduce_segment(self, out, row0, rows, slot_ptrs, slot_ld, relu, mask, bcast_ptrs, remote, local, epoch,
-                       timeout_ms, kid, status):
+                       timeout_ms, kid, status, me=-1):
         if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
             return
         cols = out.shape[1]
         seg = out[row0 : row0 + rows]
-        acc = seg.double()
-        for a in slot_ptrs:
-            acc += _view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols].double()
+        acc_dtype = torch.float64 if out.dtype == torch.float64 else torch.float32
+        others = [_view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols] for a in slot_ptrs]
+        acc = self._ordered_sum(seg, others, me, acc_dtype)
         self._finish(seg, acc, relu, None if mask is None else mask[row0 : row0 + rows])
         for a in bcast_ptrs:
             _view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols].copy_(seg)

@@ -124,7 +124,7 @@ def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
     remote, local = ax.sync(buf)
     r0, n = ranges[ax.rank]
     C.reduce_segment(out, r0, n, ax.recv_slots(buf), cols, bool(relu), mask, ax.push_targets(buf2),
-                     remote, local, epoch, ax.timeout_ms, kid, st)
+                     remote, local, epoch, ax.timeout_ms, kid, st, ax.rank)
     remote2, local2 = ax.sync(buf2)
     base = out.data_ptr()
     C.gather_segments(ax.recv_slots(buf2), [base + ranges[q][0] * cols * esz for q in ax.peers],
@@ -136,7 +136,7 @@ def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
     remote, local = ax.sync(buf)
     _Backend.load().reduce_slots(out, ax.recv_slots(buf), out.stride(0), bool(relu), mask, remote, local,
-                             epoch, ax.timeout_ms, kid, opc.status_buffer(out.device))
+                             epoch, ax.timeout_ms, kid, opc.status_buffer(out.device), ax.rank)
     opc._count(1)
 
 
@@ -206,7 +206,7 @@ def spmm_reduce_scatter(A, H, group, relu_mask=None):
     remote, local = ax.sync(buf)
     r0, n = ranges[ax.rank]
     _Backend.load().reduce_segment(out, r0, n, ax.recv_slots(buf), D, False, relu_mask, [], remote, local,
-                                   epoch, ax.timeout_ms, KID_SPMM, opc.status_buffer(out.device))
+                                   epoch, ax.timeout_ms, KID_SPMM, opc.status_buffer(out.device), ax.rank)
     opc._count(1)
     op_counts["reduce_scatter"] += 1
     return out[r0 : r0 + n]
@@ -271,7 +271,7 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
     C.push_copy(t, ax.push_targets(buf))
     remote, local = ax.sync(buf)
     C.reduce_slots_f32(t.view(-1), ax.recv_slots(buf), code, remote, local, epoch, ax.timeout_ms,
-                       KID_XENT, opc.status_buffer(t.device))
+                       KID_XENT, opc.status_buffer(t.device), ax.rank)
     opc._count(2)
     return t
 

@@ -330,3 +330,43 @@ def _gather_pieces_worker(rank, world):
 
 def test_fused_all_gather_in_pieces():
     run_distributed(_gather_pieces_worker, 3)
+
+
+def _replica_worker(rank, world):
+    """One-shot sums on a 4-rank axis: every rank must add the partials in the same (group-rank)
+    order, so the replicas of an all-reduced fp32 tensor are bitwise equal."""
+    import torch.distributed as dist
+
+    import plexus_b200 as plx
+    from plexus_b200.parallel import emulator, fused
+
+    emulator.enable()
+    fused.ONE_SHOT_MAX_RANKS = 8
+    grid = plx.init(world, 1, 1, device="cpu", comm="fused")
+    g = grid.group("x")
+    gen = torch.Generator().manual_seed(100 + rank)
+    # magnitudes spread over many binades: a different summation order changes the last bits
+    t = torch.randn(4096, generator=gen) * torch.exp(8 * torch.randn(4096, generator=gen))
+    mine = t.clone()
+    fused.all_reduce_f32(mine, g)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    assert all(torch.equal(everyone[0], e) for e in everyone)
+    # and it is the sum in group-rank order
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t)
+    want = torch.zeros_like(t)
+    for p in parts:
+        want = want + p
+    assert torch.equal(mine, want)
+    m = torch.randn(64, 16, generator=gen).to(torch.bfloat16)
+    fused.all_reduce_bf16(m, g)
+    every_m = [torch.empty_like(m) for _ in range(world)]
+    dist.all_gather(every_m, m)
+    assert all(torch.equal(every_m[0], e) for e in every_m)
+    emulator.ops.check_status()
+    plx.shutdown()
+
+
+def test_one_shot_replicas_are_bitwise_equal_on_a_four_rank_axis():
+    run_distributed(_replica_worker, 4)
