@@ -29,7 +29,15 @@ def _lib():
                    ctypes.c_int]
     lib.plexus_gemm_tn_noalloc_parts.restype = ctypes.c_int
     lib.plexus_gemm_tn_noalloc_parts.argtypes = [ctypes.c_int64]
+    lib.plexus_noalloc_take_status.restype = ctypes.c_int
+    lib.plexus_noalloc_take_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     return lib
+
+
+def _status(lib):
+    words = (ctypes.c_int * 8)()
+    assert lib.plexus_noalloc_take_status(words) == 0
+    return list(words)
 
 
 def _call(lib, a, b, out):
@@ -40,11 +48,14 @@ def _call(lib, a, b, out):
     return rc, err.value.decode()
 
 
-def test_noalloc_gemm_tn_matches_regular_entry_point_twice():
+def _check_device(lib, index):
+    """Two calls in a row on one device: a large problem, then a small one that finds the shared
+    array full of the first call's partial sums.  Each result is compared with the regular entry
+    point and with the fp64 product; the second call must leave the driver's count of free device
+    memory (cudaMemGetInfo, which also sees allocations made behind torch's back) unchanged."""
     from plexus_b200 import ops
 
-    lib = _lib()
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", index)
     torch.cuda.set_device(dev)
     for seed, (R, Mw, Nw) in enumerate([(20000, 128, 64), (7001, 104, 48)]):
         torch.manual_seed(seed)
@@ -52,15 +63,40 @@ def test_noalloc_gemm_tn_matches_regular_entry_point_twice():
         b = torch.randn(R, Nw, device=dev).to(torch.bfloat16)
         want = ops.gemm(a, b, trans_a=True, out_dtype=torch.float32)
         out = torch.full((Mw, Nw), float("nan"), dtype=torch.float32, device=dev)
+        ref = a.double().t() @ b.double()
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info(dev)[0]
         rc, msg = _call(lib, a, b, out)
         torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info(dev)[0]
         assert rc == 0, msg
         assert torch.cuda.memory_allocated() == before
-        ref = a.double().t() @ b.double()
+        if seed > 0:  # the first call on a device may load the kernel's module lazily
+            assert free_after == free_before
+        assert _status(lib)[0] == 0
         assert (out.double() - ref).abs().max() / ref.abs().max() < 1e-3
         assert torch.allclose(out, want, rtol=1e-5, atol=1e-5)
+
+
+def test_noalloc_gemm_tn_matches_regular_entry_point_twice():
+    lib = _lib()
+    _check_device(lib, 0)
+    if torch.cuda.device_count() > 1:
+        # a second device has its own copy of the array and its own cached address
+        _check_device(lib, 1)
+        torch.cuda.set_device(0)
+
+
+def test_noalloc_rejects_bad_leading_dimensions():
+    lib = _lib()
+    dev = torch.device("cuda", 0)
+    a = torch.zeros(64, 16, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(16, 16, dtype=torch.float32, device=dev)
+    err = ctypes.create_string_buffer(256)
+    rc = lib.plexus_gemm_tn_noalloc(a.data_ptr(), 8, a.data_ptr(), 16, out.data_ptr(), 64, 16, 16,
+                                    torch.cuda.current_stream().cuda_stream, err, 256)
+    assert rc == 1 and b"leading" in err.value
 
 
 def test_noalloc_rejects_problems_beyond_the_builtin_scratch():
