@@ -44,6 +44,27 @@ plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t
   return p;
 }
 
+// In-kernel all-reduce description from Python lists of raw addresses (empty lists: off).
+plx::TileReduce make_tile_reduce(const std::vector<int64_t>& slots, const std::vector<int64_t>& remote_sig,
+                                 const std::vector<int64_t>& local_sig, int64_t base, int64_t me,
+                                 double timeout_ms, int64_t tile_rows = 0, int64_t local_done = 0) {
+  plx::TileReduce r = {};
+  TORCH_CHECK(slots.size() == remote_sig.size() && slots.size() == local_sig.size() &&
+              slots.size() <= static_cast<size_t>(plx::MAX_PEERS), "bad in-kernel all-reduce description");
+  r.n = static_cast<int>(slots.size());
+  for (int i = 0; i < r.n; ++i) {
+    r.slot[i] = reinterpret_cast<const void*>(slots[i]);
+    r.remote_sig[i] = reinterpret_cast<int*>(remote_sig[i]);
+    r.local_sig[i] = reinterpret_cast<int*>(local_sig[i]);
+  }
+  r.base = static_cast<int>(base);
+  r.me = static_cast<int>(me);
+  r.tile_rows = static_cast<int>(tile_rows);
+  r.local_done = reinterpret_cast<int*>(local_done);
+  r.timeout_ns = static_cast<unsigned long long>(timeout_ms * 1e6);
+  return r;
+}
+
 plx::SlotList make_slots(const std::vector<int64_t>& ptrs, int64_t me = -1) {
   plx::SlotList s;
   s.me = static_cast<int>(me);
@@ -128,11 +149,14 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
                              s, scr, scr_n, push.n ? &push : nullptr, static_cast<int>(variant), stream()));
 }
 
-// Tensor-core SpMM (bf16): block_start covers every row of [row_begin, row_begin + out.size(0)).
+// Tensor-core SpMM (bf16): the work items cover every row of [row_begin, row_begin + out.size(0)).
 void spmm_mma(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
-              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
-              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t staging, int64_t push_seg_rows,
-              int64_t push_me, const Tensor& status) {
+              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& items, int64_t num_pieces,
+              const Tensor& long_piece_start, Tensor& long_counter, const Tensor& scratch,
+              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t stages, int64_t push_seg_rows,
+              int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots,
+              const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
+              int64_t red_me, double red_timeout_ms, int64_t red_tile_rows, int64_t red_local_done) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -151,15 +175,32 @@ void spmm_mma(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
     mptr = mask->data_ptr();
     ldm = mask->stride(0);
   }
-  const int nb = block_start.numel() > 0 ? static_cast<int>(block_start.numel()) - 1 : 0;
+  TORCH_CHECK(items.numel() % 4 == 0, "spmm_mma: work items are 4 ints each");
+  const int num_items = static_cast<int>(items.numel() / 4);
+  float* scr = nullptr;
+  int64_t scr_n = 0;
+  if (scratch.defined() && scratch.numel() > 0) {
+    TORCH_CHECK(scratch.is_cuda() && scratch.scalar_type() == at::kFloat && scratch.is_contiguous());
+    scr = scratch.data_ptr<float>();
+    scr_n = scratch.numel();
+  }
+  int* counters = nullptr;
+  if (long_counter.defined() && long_counter.numel() > 0) {
+    TORCH_CHECK(long_counter.is_cuda() && long_counter.scalar_type() == at::kInt && long_counter.is_contiguous());
+    counters = long_counter.data_ptr<int>();
+  }
   plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
   TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
               "spmm: row segments do not cover the output");
+  plx::TileReduce red = make_tile_reduce(red_slots, red_remote_sig, red_local_sig, 0, red_me, red_timeout_ms,
+                                         red_tile_rows, red_local_done);
   c10::cuda::CUDAGuard guard(H.device());
   check(plx::launch_spmm_mma(rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(), H.data_ptr(),
                              H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm, static_cast<int>(D),
-                             static_cast<int>(row_begin), int_ptr(block_start), nb, push.n ? &push : nullptr,
-                             static_cast<int>(staging), status_ptr(status), stream()));
+                             static_cast<int>(row_begin), int_ptr(items), num_items, static_cast<int>(num_pieces),
+                             int_ptr(long_piece_start), counters, scr, scr_n, push.n ? &push : nullptr,
+                             static_cast<int>(stages), status_ptr(status), stream(), red.n ? &red : nullptr,
+                             static_cast<int>(out.size(0))));
 }
 
 int64_t spmm_scratch_per_piece(const Tensor& H) {
@@ -169,10 +210,13 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
              int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
              const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask,
-             int64_t push_seg_rows, int64_t push_me) {
+             int64_t push_seg_rows, int64_t push_me, const std::vector<int64_t>& red_slots,
+             const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
+             int64_t red_base, int64_t red_me, double red_timeout_ms) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
+  plx::TileReduce red = make_tile_reduce(red_slots, red_remote_sig, red_local_sig, red_base, red_me, red_timeout_ms);
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
@@ -190,7 +234,7 @@ void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tenso
                             C.stride(0), dtype_of(C), A.size(0), B.size(0), A.size(1), relu,
                             status_ptr(status), static_cast<int>(max_stages),
                             static_cast<int>(ctas_limit), static_cast<int>(nb_override),
-                            push.n ? &push : nullptr, mptr, ldm, stream()));
+                            push.n ? &push : nullptr, mptr, ldm, stream(), red.n ? &red : nullptr));
 }
 
 int64_t gemm_tn_parts(int64_t R) { return plx::gemm_tn_parts(R); }
@@ -439,6 +483,9 @@ int64_t symm_open(const std::string& handle) {
 
 void symm_close(int64_t ptr) { check(plx::symm_close(reinterpret_cast<void*>(ptr))); }
 void symm_free(int64_t ptr) { check(plx::symm_free(reinterpret_cast<void*>(ptr))); }
+void symm_clear(int64_t ptr, int64_t bytes) {
+  check(plx::symm_clear(reinterpret_cast<void*>(ptr), static_cast<size_t>(bytes)));
+}
 
 // ---- start-up kernels ---------------------------------------------------------------------
 std::tuple<Tensor, Tensor> rmat_edges(int64_t num_nodes, int64_t first_edge, int64_t n, int64_t seed,
@@ -520,17 +567,6 @@ void csr_validate(const Tensor& rowptr, const Tensor& col, int64_t nrows, int64_
                                  status_ptr(status), stream()));
 }
 
-#ifdef PLX_GEMM_PROF
-}  // namespace
-namespace plx { void gemm_prof_dump(long long* host); }
-namespace {
-std::vector<int64_t> gemm_prof() {
-  std::vector<long long> h(256);
-  plx::gemm_prof_dump(h.data());
-  return std::vector<int64_t>(h.begin(), h.end());
-}
-#endif
-
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -548,9 +584,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relu_bwd", &relu_bwd);
   m.def("prep_weight", &prep_weight);
   m.def("wait_flag", &wait_flag);
-#ifdef PLX_GEMM_PROF
-  m.def("gemm_prof", &gemm_prof);
-#endif
   m.def("rmat_edges", &rmat_edges);
   m.def("gcn_norm", &gcn_norm);
   m.def("coo_to_csr", &coo_to_csr);
@@ -567,4 +600,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_open", &symm_open);
   m.def("symm_close", &symm_close);
   m.def("symm_free", &symm_free);
+  m.def("symm_clear", &symm_clear);
 }

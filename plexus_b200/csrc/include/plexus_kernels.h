@@ -26,6 +26,28 @@ struct PushTargets {
   int me;                 // this rank's position in the group (seg_rows > 0 only)
 };
 
+// In-kernel all-reduce of a fused "compute + push" kernel (one-shot form): besides pushing its
+// partial result tiles into the peers' receive slots (PushTargets), the kernel reduces them itself.
+// Unit of exchange: a "tile" (GEMM: the 128-row tiles a CTA processes, in order; SpMM: fixed blocks
+// of consecutive output rows).  After storing a tile locally and into the peers' slots, the kernel
+// publishes it on every peer (release, system scope); it then waits (bounded) until the peers
+// published theirs, adds the received partials to its own in group-rank order, applies ReLU / the
+// mask and writes the final rows - no second launch.  Both ranks of a pair run the same grid, so
+// CTA c of one rank exchanges with CTA c of the other (GEMM) or tiles are tracked by row counters
+// (SpMM).  n == 0 switches it off.
+struct TileReduce {
+  int n;                               // peers
+  const void* slot[MAX_PEERS];         // this rank's receive slot of every peer (same layout as the push)
+  int* remote_sig[MAX_PEERS];          // this rank's signal array inside peer q's workspace (written here)
+  int* local_sig[MAX_PEERS];           // peer q's signal array inside this rank's workspace (polled here)
+  int base;                            // GEMM: tile k of a CTA publishes base + k + 1
+  int me;                              // position in the group (summation order)
+  int tile_rows;                       // SpMM: rows per exchange tile
+  int* local_done;                     // SpMM: rows of each tile this rank has finished (device-local)
+  unsigned long long timeout_ns;
+  int* status;
+};
+
 // ---- spmm.cu
 // Per-matrix work schedule (device arrays, built once per shard; see ops/cuda.py):
 //   block_start[num_blocks+1] : consecutive-row blocks of about equal cost
@@ -55,20 +77,28 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
 enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
 
 // ---- spmm_mma.cu
-// Tensor-core SpMM for bf16 features (any D that is a multiple of 8): every row of
-// block_start[0] .. block_start[num_blocks] in one launch, rows of any length (no pieces, no
-// scratch).  staging: 0 = 16-byte cp.async copies, 1 = one bulk copy per gathered row.
+// Tensor-core SpMM for bf16 features (any D that is a multiple of 8), one launch for rows of any
+// length.  Work items, 4 ints each: the pieces of the long rows first ({row, -(long id + 1), first
+// nonzero, last nonzero + 1}; a piece's index is also the index of its fp32 partial row in
+// `scratch`), then blocks of whole rows ({first row, last row + 1, 0, 0}).  long_piece_start
+// [num_long + 1] indexes the pieces of each long row; long_counter[num_long] must be zero and is
+// left zero.  stages: depth of the shared-memory ring of a warp (0 = chosen from the row size).
 const char* launch_spmm_mma(const int* rowptr, const int* col, const float* val, const void* H, int64_t ldh,
                             void* out, int64_t ldo, const void* mask, int64_t ldm, int D, int row_begin,
-                            const int* block_start, int num_blocks, const PushTargets* push, int staging,
-                            int* status, cudaStream_t stream);
+                            const int* items, int num_items, int num_pieces, const int* long_piece_start,
+                            int* long_counter, float* scratch, int64_t scratch_elems,
+                            const PushTargets* push, int stages, int* status, cudaStream_t stream,
+                            const TileReduce* reduce = nullptr, int out_rows = 0);
 
 // ---- gemm_tcgen05.cu
 // C[M,N] = A[M,K] . B[N,K]^T ; A, B bf16 row-major (lda/ldb in elements); C bf16 or fp32.
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
                            int* status, int max_stages, int ctas_limit, int nb_override,
-                           const PushTargets* push, const void* mask, int64_t ldm, cudaStream_t stream);
+                           const PushTargets* push, const void* mask, int64_t ldm, cudaStream_t stream,
+                           const TileReduce* reduce = nullptr);
+// Largest number of CTAs launch_gemm_nt uses (size of the per-CTA signal arrays of TileReduce).
+constexpr int GEMM_MAX_CTAS = 256;
 // mask (same dtype and shape as C, may be null): C = result where mask > 0, else 0.
 // out[Mw,Nw] fp32 = A[R,Mw]^T . B[R,Nw]; scratch >= gemm_tn_parts(R)*Mw*Nw floats.
 int gemm_tn_parts(int64_t R);
@@ -165,6 +195,7 @@ const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 const char* symm_open(const unsigned char* handle64, void** ptr);
 const char* symm_close(void* ptr);
 const char* symm_free(void* ptr);
+const char* symm_clear(void* ptr, size_t bytes);  // zero the first `bytes` of a local workspace
 
 // ---- graph_prep.cu (start-up kernels)
 const char* launch_rmat_edges(int64_t num_nodes, int64_t first_edge, int64_t n, uint64_t seed, double a,

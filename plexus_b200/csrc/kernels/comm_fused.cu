@@ -381,6 +381,11 @@ const char* symm_close(void* ptr) {
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
+const char* symm_clear(void* ptr, size_t bytes) {
+  cudaError_t e = cudaMemset(ptr, 0, bytes);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
 const char* symm_free(void* ptr) {
   cudaError_t e = cudaFree(ptr);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

@@ -41,13 +41,6 @@ constexpr int SMEM_LIMIT = 232448;        // 227 KB opt-in maximum per CTA
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID_GEMM = 6;
 
-#ifdef PLX_GEMM_PROF
-__device__ long long g_gemm_prof[32][8];
-#define PROF(t, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (t) < 32) g_gemm_prof[(t)][(slot)] = clock64(); } while (0)
-#else
-#define PROF(t, slot) do { } while (0)
-#endif
-
 struct alignas(8) GemmBarriers {
   uint64_t full[8];
   uint64_t empty[8];
@@ -56,6 +49,8 @@ struct alignas(8) GemmBarriers {
   uint64_t tempty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int wait_ok;
+  int pad;
 };
 
 // Epilogue staging: every epilogue warp owns 32 rows; a segment of SEG_BYTES per row goes
@@ -125,6 +120,107 @@ __device__ __forceinline__ void apply_relu_mask<float>(uint4& v, const uint4& m)
     if (!(mf[i] > 0.f)) vw[i] = 0u;
 }
 
+// ----- in-kernel all-reduce of finished tiles (see TileReduce)
+__device__ __forceinline__ unsigned long long gemm_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    acc[2 * k] += f.x;
+    acc[2 * k + 1] += f.y;
+  }
+}
+
+// The four epilogue warps (128 threads, `tid` 0..127) finish rows [r0, r0 + nrows) x columns
+// [n0, n0 + ncols): wait until every peer published tile number `expect` of this CTA, then
+// C = act(sum over the group of the partials), summed in group-rank order.  Returns false after a
+// timeout (recorded in the status words).
+__device__ __forceinline__ bool reduce_tile_bf16(__nv_bfloat16* __restrict__ C, int ldc, int r0, int nrows, int n0,
+                                                 int ncols, const TileReduce& red, int64_t slot_ld, int cta,
+                                                 int expect, int relu, const __nv_bfloat16* __restrict__ mask,
+                                                 int ldm, int tid, volatile int* wait_ok) {
+  if (tid == 0) {
+    int good = 1;
+    const unsigned long long t0 = gemm_global_ns();
+    for (int q = 0; q < red.n && good; ++q) {
+      int seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
+      while (seen - expect < 0) {
+        if (gemm_global_ns() - t0 > red.timeout_ns) {
+          report_status(red.status, ST_TIMEOUT, KERNEL_ID_GEMM, 20 + q, expect, seen);
+          good = 0;
+          break;
+        }
+        __nanosleep(32);
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
+      }
+    }
+    *wait_ok = good;
+  }
+  epi_bar_sync();
+  if (!*wait_ok) return false;
+  const int vpr = ncols >> 3;
+  const int total = nrows * vpr;
+  constexpr int UN = 4;
+  for (int v0 = tid; v0 < total; v0 += 128 * UN) {
+    int64_t off_c[UN], off_s[UN], off_m[UN];
+    bool live[UN];
+    uint4 own[UN];
+    float acc[UN][8];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int v = v0 + u * 128;
+      live[u] = v < total;
+      const int r = live[u] ? v / vpr : 0, c = live[u] ? (v - r * vpr) * 8 : 0;
+      off_c[u] = static_cast<int64_t>(r0 + r) * ldc + n0 + c;
+      off_s[u] = static_cast<int64_t>(r0 + r) * slot_ld + n0 + c;
+      off_m[u] = static_cast<int64_t>(r0 + r) * ldm + n0 + c;
+      own[u] = ld_cg16(C + off_c[u]);  // row 0 of the tile when not live: a valid address, value unused
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+      if (red.me <= 0) acc_bf16x8(acc[u], own[u]);
+    }
+    // one peer at a time, UN independent loads in flight; the local partial enters at position `me`
+    for (int q = 0; q < red.n; ++q) {
+      const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(red.slot[q]);
+      uint4 pv[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) pv[u] = ld_cg16(sp + off_s[u]);
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        acc_bf16x8(acc[u], pv[u]);
+        if (q + 1 == red.me) acc_bf16x8(acc[u], own[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      if (!live[u]) continue;
+      if (relu) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = fmaxf(acc[u][k], 0.f);
+      }
+      uint4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) po[k] = __floats2bfloat162_rn(acc[u][2 * k], acc[u][2 * k + 1]);
+      if (mask != nullptr) apply_relu_mask<__nv_bfloat16>(o, ld_cg16(mask + off_m[u]));
+      *reinterpret_cast<uint4*>(C + off_c[u]) = o;
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------
 // C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = block of bn_box columns)
 // ---------------------------------------------------------------------------------------
@@ -133,11 +229,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
                int b_resident, int relu, int* status, const PushTargets push,
-               const OutT* __restrict__ mask, int ldm) {
+               const OutT* __restrict__ mask_in, int ldm, const TileReduce red) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
 
+  const int relu_in = relu;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (K + BK - 1) / BK;
   const int n0 = blockIdx.y * bn_box;
@@ -163,6 +260,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&bars->tempty[b], 4);
     }
     bars->abort_flag = 0;
+    bars->wait_ok = 1;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -229,7 +327,6 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           break;
         }
         tc_fence_after();
-        PROF(t, 0);  // accumulator buffer free
         const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % stages;
@@ -253,12 +350,19 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           umma_commit(&bars->empty[s]);  // stage reusable once these MMAs retire
         }
         if (ok) umma_commit(&bars->tfull[buf]);
-        PROF(t, 1);  // all MMAs of the tile issued
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant owned by this warp
+    // with the in-kernel all-reduce the activation and the mask are applied after the sum
+    const bool fuse_reduce = red.n > 0;
+    const OutT* mask = fuse_reduce ? nullptr : mask_in;
+    if (fuse_reduce) relu = 0;
+    const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int prev_tile = -1;
+    bool red_ok = true;
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
@@ -270,7 +374,6 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      if (warp == 2 && lane == 0) PROF(t, 2);  // accumulator ready
       constexpr int ESZ = sizeof(OutT);
       constexpr int SEG_COLS = SEG_BYTES / ESZ;  // columns per staged segment
       constexpr int LANES_PER_ROW = SEG_BYTES / 16;
@@ -309,7 +412,6 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->tempty[buf]);
-          if (warp == 2 && lane == 0) PROF(t, 3);  // TMEM read + staged
         } else {
           __syncwarp();
         }
@@ -379,8 +481,35 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         __syncwarp();
       }
-      if (warp == 2 && lane == 0) PROF(t, 4);  // rows written
-
+      if constexpr (sizeof(OutT) == 2) {
+        if (fuse_reduce) {
+          // every epilogue warp has stored this tile locally and into the peers' slots: publish it,
+          // then finish the previous tile, whose partials from the peers had a whole tile's time to arrive
+          epi_bar_sync();
+          if (epi_tid == 0) {
+            __threadfence_system();
+            for (int p = 0; p < red.n; ++p)
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(red.remote_sig[p] + cta_id),
+                           "r"(red.base + static_cast<int>(t) + 1)
+                           : "memory");
+          }
+          if (prev_tile >= 0 &&
+              !reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, prev_tile * BM, min(BM, M - prev_tile * BM),
+                                n0, n_valid, red, push.ld, cta_id, red.base + static_cast<int>(t), relu_in,
+                                reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid, &bars->wait_ok)) {
+            red_ok = false;
+            *abort_flag = 1;
+            break;
+          }
+          prev_tile = tile;
+        }
+      }
+    }
+    if constexpr (sizeof(OutT) == 2) {
+      if (fuse_reduce && red_ok && prev_tile >= 0 && !*abort_flag)
+        reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, prev_tile * BM, min(BM, M - prev_tile * BM), n0,
+                         n_valid, red, push.ld, cta_id, red.base + static_cast<int>(t), relu_in,
+                         reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid, &bars->wait_ok);
     }
   }
 
@@ -607,7 +736,21 @@ static int num_sms() {
 const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                            int64_t ldc, int c_dtype, int64_t M, int64_t N, int64_t K, bool relu,
                            int* status, int max_stages, int ctas_limit, int nb_override,
-                           const PushTargets* push_in, const void* mask, int64_t ldm, cudaStream_t stream) {
+                           const PushTargets* push_in, const void* mask, int64_t ldm, cudaStream_t stream,
+                           const TileReduce* reduce_in) {
+  TileReduce red = {};
+  if (reduce_in != nullptr && reduce_in->n > 0) {
+    red = *reduce_in;
+    if (c_dtype != DT_BF16) return "gemm_nt: the in-kernel all-reduce needs a bf16 result";
+    if (push_in == nullptr || push_in->n != red.n || push_in->seg_rows != 0)
+      return "gemm_nt: the in-kernel all-reduce goes with the broadcast push to the same peers";
+    if (red.n > MAX_PEERS) return "gemm_nt: too many peers";
+    for (int q = 0; q < red.n; ++q)
+      if (red.slot[q] == nullptr || red.remote_sig[q] == nullptr || red.local_sig[q] == nullptr ||
+          reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
+        return "gemm_nt: bad in-kernel all-reduce description";
+    red.status = status;
+  }
   if (mask != nullptr && (ldm % 8 || reinterpret_cast<uintptr_t>(mask) % 16))
     return "gemm_nt: mask must be 16-byte aligned with a leading dimension multiple of 8";
   PushTargets push = {};
@@ -654,6 +797,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   const int tiles = static_cast<int>((M + BM - 1) / BM);
   const int n_blocks = static_cast<int>((N + bn_box - 1) / bn_box);
   const int ctas = std::min(tiles, ctas_limit > 0 ? ctas_limit : std::max(1, num_sms() / n_blocks));
+  if (red.n > 0 && ctas * n_blocks > GEMM_MAX_CTAS) return "gemm_nt: too many CTAs for the signal arrays";
   dim3 grid(ctas, static_cast<unsigned>(n_blocks));
   if (c_dtype == DT_BF16) {
     auto kern = gemm_nt_kernel<__nv_bfloat16>;
@@ -663,7 +807,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
                                                b_resident, relu ? 1 : 0, status, push,
                                                reinterpret_cast<const __nv_bfloat16*>(mask),
-                                               static_cast<int>(ldm));
+                                               static_cast<int>(ldm), red);
   } else if (c_dtype == DT_F32) {
     auto kern = gemm_nt_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -671,16 +815,12 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
                                                b_resident, relu ? 1 : 0, status, push,
-                                               reinterpret_cast<const float*>(mask), static_cast<int>(ldm));
+                                               reinterpret_cast<const float*>(mask), static_cast<int>(ldm), red);
   } else {
     return "gemm_nt: C must be bf16 or fp32";
   }
   return last_launch_error();
 }
-
-#ifdef PLX_GEMM_PROF
-void gemm_prof_dump(long long* host) { cudaMemcpyFromSymbol(host, g_gemm_prof, sizeof(long long) * 32 * 8); }
-#endif
 
 // Number of row-split CTAs gemm_tn uses for R reduction rows (scratch = parts * Mw * Nw floats).
 int gemm_tn_parts(int64_t R) {

@@ -3,9 +3,9 @@
 // The CUDA-core kernel (spmm.cu) spends about 12 instructions per 16 gathered bytes per lane on
 // widening bf16 and multiply-adding, and is bound by instruction issue.  Here the gathered rows
 // never enter the register file as data: a warp streams the nonzeros of its rows through a ring
-// in shared memory, 16 nonzeros per stage, filled asynchronously either by one bulk copy per
-// gathered row (cp.async.bulk, one lane issues a whole row, completion counted in bytes on an
-// mbarrier) or by 16-byte cp.async copies, and the weighted sums are formed by warp-level MMAs:
+// in shared memory, 16 nonzeros per stage, filled by asynchronous 16-byte copies (cp.async, one
+// commit group per stage; the warp stalls in cp.async.wait_group, it does not poll), and the
+// weighted sums are formed by warp-level MMAs:
 //
 //     C[16 features x 8] += A[16 features x 16 nonzeros] . B[16 nonzeros x 8]
 //
@@ -19,7 +19,9 @@
 // optional ReLU-derivative mask and the optional stores into the peers' receive slots).
 //
 // tcgen05 is not used: its accumulator is a 128-lane tile in tensor memory shared by a CTA, while
-// this product needs an independent accumulator per output row and 16 x 8 tiles.
+// this product needs an independent accumulator per output row and 16 x 8 tiles.  One bulk copy
+// (cp.async.bulk) per gathered row was measured too: the copy engine takes about 20 cycles per
+// copy and SM whatever the size, which is slower than the 16-byte copies for rows of 96-512 bytes.
 //
 // Reference call sites replaced: plexus/gcn_conv.py:98,188,265 (torch.sparse.mm -> cuSPARSE, fp32).
 
@@ -40,17 +42,18 @@ constexpr int KB = 16;  // nonzeros per stage = K of the MMA
 constexpr int KERNEL_ID_SPMM_MMA = 7;
 constexpr int MAX_STAGES = 8;
 
-template <int MB>
+// VEC: 16-byte pieces per feature row (D = 8 * VEC); MB: 16-feature blocks the MMAs cover.
+template <int VEC>
 struct Cfg {
+  static constexpr int MB = (VEC + 1) / 2;
   static constexpr int ROW_BYTES = MB * 32;                // staged row, features padded to 16
   static constexpr int PITCH = ROW_BYTES + 16;             // odd number of 16-byte units: no bank conflicts
   static constexpr int STAGE_BYTES = KB * PITCH;
   static constexpr int XP = MB * 16 + 8;                   // floats per slot of the exchange area
   static constexpr int XCH_BYTES = 4 * XP * 4;
   static constexpr int BT_BYTES = KB * 16;                 // weight tile: 8 bf16 per nonzero
-  static constexpr int BAR_BYTES = MAX_STAGES * 8;
   __host__ __device__ static constexpr int warp_bytes(int stages) {
-    return stages * STAGE_BYTES + XCH_BYTES + BT_BYTES + BAR_BYTES;
+    return stages * STAGE_BYTES + XCH_BYTES + BT_BYTES;
   }
 };
 
@@ -72,36 +75,22 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// One gathered row: global -> shared, completion in bytes on an mbarrier of this CTA (no multicast).
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-// The mbarrier receives one arrival from this thread when all its earlier cp.async have landed.
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < PLX_WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Wait until at most `n` of this thread's most recent commit groups are still in flight (n < 8).
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
   }
-  return false;
 }
 
 __device__ __forceinline__ uint4 pack_bf16x8(const float (&a)[8]) {
@@ -146,16 +135,107 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16* __restrict__ out, int64
       *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(push.base[q]) + orow * push.ld + c) = packed;
 }
 
-// MB: number of 16-feature blocks (D <= 16 * MB).  BULK: one bulk copy per gathered row instead of
-// 16-byte cp.async copies.
-template <int MB, bool BULK>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ unsigned long long spmm_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    acc[2 * k] += f.x;
+    acc[2 * k + 1] += f.y;
+  }
+}
+
+// In-kernel all-reduce: have all peers pushed every row of exchange tile `tile` (nrows rows)?
+__device__ __forceinline__ bool tile_arrived(const TileReduce& red, int tile, int nrows, int* seen_out) {
+  for (int q = 0; q < red.n; ++q) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + tile) : "memory");
+    if (seen < nrows) {
+      *seen_out = seen;
+      return false;
+    }
+  }
+  return true;
+}
+
+// In-kernel all-reduce, one exchange tile (output rows [r0, r0 + nrows)) whose partials have all
+// arrived, done by one warp: out = mask(sum over the group), partials added in group-rank order;
+// finally clear the tile's counters for the next op that uses this buffer.
+__device__ __forceinline__ void reduce_rows_tile(__nv_bfloat16* __restrict__ out, int64_t ldo, int r0, int nrows,
+                                                 int D, const __nv_bfloat16* __restrict__ mask, int64_t ldm,
+                                                 const TileReduce& red, int64_t slot_ld, int tile, int lane) {
+  __threadfence();
+  __syncwarp();
+  const int vec = D >> 3;
+  const int total = nrows * vec;
+  constexpr int UN = 4;
+  for (int v0 = lane; v0 < total; v0 += 32 * UN) {
+    int64_t off_o[UN], off_s[UN], off_m[UN];
+    bool live[UN];
+    uint4 own[UN];
+    float acc[UN][8];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int v = v0 + u * 32;
+      live[u] = v < total;
+      const int r = live[u] ? v / vec : 0, c = live[u] ? (v - r * vec) * 8 : 0;
+      off_o[u] = static_cast<int64_t>(r0 + r) * ldo + c;
+      off_s[u] = static_cast<int64_t>(r0 + r) * slot_ld + c;
+      off_m[u] = static_cast<int64_t>(r0 + r) * ldm + c;
+      own[u] = ld_cg16(out + off_o[u]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+      if (red.me <= 0) add_bf16x8(acc[u], own[u]);
+    }
+    for (int q = 0; q < red.n; ++q) {
+      const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(red.slot[q]);
+      uint4 pv[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) pv[u] = ld_cg16(sp + off_s[u]);
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        add_bf16x8(acc[u], pv[u]);
+        if (q + 1 == red.me) add_bf16x8(acc[u], own[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      if (!live[u]) continue;
+      if (mask != nullptr) mask_bf16x8(acc[u], ld_cg16(mask + off_m[u]));
+      *reinterpret_cast<uint4*>(out + off_o[u]) = pack_bf16x8(acc[u]);
+    }
+  }
+  __syncwarp();
+  if (lane == 0) {
+    for (int q = 0; q < red.n; ++q) red.local_sig[q][tile] = 0;
+    red.local_done[tile] = 0;
+  }
+}
+
+// VEC: 16-byte pieces per feature row (D = 8 * VEC), a compile-time constant so that the piece ->
+// (nonzero, column) mapping of the staging copies costs no division.
+template <int VEC>
+__global__ void __launch_bounds__(256, 2)
 spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, const float* __restrict__ val,
                 const __nv_bfloat16* __restrict__ H, int64_t ldh, __nv_bfloat16* __restrict__ out,
                 int64_t ldo, const __nv_bfloat16* __restrict__ mask, int64_t ldm, int D, int row_begin,
-                const int* __restrict__ block_start, int num_blocks, const PushTargets push, int stages,
-                int* status) {
-  using C = Cfg<MB>;
+                const int4* __restrict__ items, int num_items, const int* __restrict__ long_piece_start,
+                int* __restrict__ long_counter, float* __restrict__ scratch, const PushTargets push, int stages,
+                int* status, const TileReduce red, int out_rows) {
+  using C = Cfg<VEC>;
+  constexpr int MB = C::MB;
+  // with the in-kernel all-reduce the mask is applied after the sum, not to the pushed partials
+  const __nv_bfloat16* flush_mask = red.n > 0 ? nullptr : mask;
   extern __shared__ __align__(128) uint8_t spmm_mma_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -165,18 +245,12 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
   uint8_t* bt = reinterpret_cast<uint8_t*>(xch) + C::XCH_BYTES;
   const uint32_t stage0 = smem_u32(ws);
   const uint32_t bt_addr = smem_u32(bt);
-  const uint32_t bar0 = bt_addr + C::BT_BYTES;
 
   // staged rows a short stage leaves unwritten, and the padding columns, must hold finite values
   for (int i = lane; i < stages * C::STAGE_BYTES / 16; i += 32) reinterpret_cast<uint4*>(ws)[i] = make_uint4(0, 0, 0, 0);
-  if (lane < stages)
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + lane * 8), "r"(BULK ? 1 : 32));
-  fence_mbar_init();
-  fence_proxy_async();
   __syncwarp();
 
-  const int vec = D >> 3;                  // 16-byte pieces per feature row
-  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2;
+  constexpr int vec = VEC;
   const uint32_t ldh32 = static_cast<uint32_t>(ldh);
   // flush mapping: `vec` lanes write one row, 32 / vec rows at a time
   const int rows_per_iter = 32 / vec;      // >= 1 because D <= 256
@@ -185,15 +259,54 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
   // ldmatrix.x4.trans row addresses: see the four 8x8 blocks (k 0-7 / 8-15) x (feature 0-7 / 8-15)
   const uint32_t ldm_off = ((lane & 7) + ((lane & 16) ? 8 : 0)) * C::PITCH + ((lane & 8) ? 16 : 0);
 
-  int pos = 0;              // ring stage of the next stage to consume
-  uint32_t phase_bits = 0;  // bit s: parity the next wait on stage s expects
+  int pos = 0;  // ring stage of the next stage to consume
   bool ok = true;
+
+  // In-kernel all-reduce: exchange tiles this warp has to reduce (their last local row came from
+  // this warp) and whose partials from the peers have not all arrived yet.  A warp never waits for
+  // a peer while it still has work items: both ranks' warps finish their own rows unconditionally,
+  // so the final wait below cannot deadlock.  Lane j keeps pending tile j.
+  int pend_tile = 0, npend = 0;
+  auto poll_pending = [&](bool blocking) {
+    const unsigned long long t0 = blocking ? spmm_global_ns() : 0ull;
+    while (npend > 0 && ok) {
+      bool ready = false;
+      int seen = 0, t_rows = 0;
+      if (lane < npend) {
+        t_rows = min(red.tile_rows, out_rows - pend_tile * red.tile_rows);
+        ready = tile_arrived(red, pend_tile, t_rows, &seen);
+      }
+      const unsigned ready_mask = __ballot_sync(0xffffffffu, ready);
+      if (ready_mask == 0u) {
+        if (!blocking) return;
+        if (spmm_global_ns() - t0 > red.timeout_ns) {
+          if (lane == 0) report_status(red.status, ST_TIMEOUT, KERNEL_ID_SPMM_MMA, 20, t_rows, seen);
+          ok = false;
+          return;
+        }
+        __nanosleep(128);
+        continue;
+      }
+      const int j = __ffs(ready_mask) - 1;
+      const int T = __shfl_sync(0xffffffffu, pend_tile, j);
+      const int last = __shfl_sync(0xffffffffu, pend_tile, npend - 1);
+      if (lane == j) pend_tile = last;
+      --npend;
+      const int r0 = T * red.tile_rows;
+      reduce_rows_tile(out, ldo, r0, min(red.tile_rows, out_rows - r0), D, mask, ldm, red, push.ld, T, lane);
+    }
+  };
 
   const int warp_global = blockIdx.x * wpb + warp;
   const int warps_total = gridDim.x * wpb;
-  for (int b = warp_global; b < num_blocks && ok; b += warps_total) {
-    const int rb = __ldg(block_start + b), re = __ldg(block_start + b + 1);
-    const int nb = __ldg(rowptr + rb), ne = __ldg(rowptr + re);
+  for (int b = warp_global; b < num_items && ok; b += warps_total) {
+    // work item: a block of whole rows {rb, re, -, -}, or one piece of a long row
+    // {row, -(long id + 1), first nonzero, last nonzero + 1}; the pieces come first in the list and
+    // the index of a piece is also the index of its fp32 partial row in `scratch`
+    const int4 item = __ldg(items + b);
+    const bool piece = item.y < 0;
+    const int rb = item.x, re = piece ? item.x + 1 : item.y;
+    const int nb = piece ? item.z : __ldg(rowptr + rb), ne = piece ? item.w : __ldg(rowptr + re);
     const int nbatch = (ne - nb + KB - 1) / KB;
 
     float c[MB][4];
@@ -202,38 +315,30 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
 #pragma unroll
       for (int i = 0; i < 4; ++i) c[m][i] = 0.f;
 
-    // ---- issue stage `bi` of the block (nonzeros [i0, i0 + 16)) into ring stage `s`;
-    //      lanes 0..15 pass the column index of their nonzero
+    // ---- issue stage `bi` of the block (nonzeros [i0, i0 + 16)) into ring stage `s`: piece q of
+    //      the stage is 16 bytes number q % VEC of the row gathered for nonzero q / VEC; lanes 0..15
+    //      pass the column index of their nonzero.  One commit group per call, also when empty.
     auto issue = [&](int bi, int s, int my_col) {
       const uint32_t st_addr = stage0 + s * C::STAGE_BYTES;
-      const uint32_t bar = bar0 + s * 8;
-      const int i0 = nb + bi * KB;
-      const int cnt = min(KB, ne - i0);
-      if constexpr (BULK) {
-        if (lane == 0) mbar_expect_tx_addr(bar, static_cast<uint32_t>(cnt) * row_bytes);
-        __syncwarp();
-        if (lane < cnt)
-          bulk_copy_g2s(st_addr + lane * C::PITCH,
-                        H + static_cast<uint64_t>(static_cast<uint32_t>(my_col)) * ldh32, row_bytes, bar);
-      } else {
-        const int pieces = cnt * vec;
-        for (int q0 = 0; q0 < pieces; q0 += 32) {  // uniform trip count: every lane takes part in the shuffle
-          const int q = q0 + lane;
-          const int k = q / vec, v = q - k * vec;
-          const int ck = __shfl_sync(0xffffffffu, my_col, k & 15);
-          if (q < pieces)
-            cp_async16(st_addr + k * C::PITCH + v * 16,
-                       H + static_cast<uint64_t>(static_cast<uint32_t>(ck)) * ldh32 + v * 8);
-        }
-        cp_async_arrive_noinc(bar);
+      const int cnt = bi < nbatch ? min(KB, ne - (nb + bi * KB)) : 0;
+      constexpr int ITER = (KB * VEC + 31) / 32;
+#pragma unroll
+      for (int t = 0; t < ITER; ++t) {
+        const int q = t * 32 + lane;
+        const int k = q / VEC, v = q - k * VEC;
+        const int ck = __shfl_sync(0xffffffffu, my_col, k & 15);
+        if (k < cnt)
+          cp_async16(st_addr + k * C::PITCH + v * 16,
+                     H + static_cast<uint64_t>(static_cast<uint32_t>(ck)) * ldh32 + v * 8);
       }
+      cp_async_commit();
     };
 
     // ---- prologue: fill the ring
     const int pre = min(stages, nbatch);
     {
       int s = pos;
-      for (int bi = 0; bi < pre; ++bi) {
+      for (int bi = 0; bi < stages; ++bi) {  // always `stages` groups, the ones beyond the block empty
         const int i = nb + bi * KB + lane;
         const int my_col = (lane < KB && i < ne) ? __ldg(col + i) : 0;
         issue(bi, s, my_col);
@@ -256,10 +361,11 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
     int lo = nb;                    // rowptr[rf]
     int E0, E1, E2, E3;             // rowptr[rf + 1 .. rf + 4] (INT_MAX beyond the block)
     auto load_ends = [&]() {
-      E0 = rf + 1 <= re ? __ldg(rowptr + rf + 1) : INT_MAX;
-      E1 = rf + 2 <= re ? __ldg(rowptr + rf + 2) : INT_MAX;
-      E2 = rf + 3 <= re ? __ldg(rowptr + rf + 3) : INT_MAX;
-      E3 = rf + 4 <= re ? __ldg(rowptr + rf + 4) : INT_MAX;
+      // a piece is a single open row: nothing of it ends inside the piece
+      E0 = !piece && rf + 1 <= re ? __ldg(rowptr + rf + 1) : INT_MAX;
+      E1 = !piece && rf + 2 <= re ? __ldg(rowptr + rf + 2) : INT_MAX;
+      E2 = !piece && rf + 3 <= re ? __ldg(rowptr + rf + 3) : INT_MAX;
+      E3 = !piece && rf + 4 <= re ? __ldg(rowptr + rf + 4) : INT_MAX;
     };
     load_ends();
 
@@ -281,8 +387,8 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
           const float4 x1 = *reinterpret_cast<const float4*>(src + 4);
           float a[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           const int64_t orow = r - row_begin;
-          if (mask != nullptr)
-            mask_bf16x8(a, __ldg(reinterpret_cast<const uint4*>(mask + orow * ldm + f_v * 8)));
+          if (flush_mask != nullptr)
+            mask_bf16x8(a, __ldg(reinterpret_cast<const uint4*>(flush_mask + orow * ldm + f_v * 8)));
           store_vec(out, ldo, orow, f_v * 8, pack_bf16x8(a), push);
         }
       }
@@ -310,21 +416,9 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
              (static_cast<uint32_t>(__bfloat16_as_ushort(lw)) << 16);
       }
       const int s = pos;
-      if (!mbar_wait_addr(bar0 + s * 8, (phase_bits >> s) & 1u)) {
-        if (lane == 0) report_status(status, ST_TIMEOUT, KERNEL_ID_SPMM_MMA, s, bi, b);
-        ok = false;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        // giving up: let the other copies already issued land before the CTA exits (bounded)
-        int t = s;
-        for (int bj = bi + 1; bj < min(nbatch, bi + stages); ++bj) {
-          t = t + 1 == stages ? 0 : t + 1;
-          mbar_wait_addr(bar0 + t * 8, (phase_bits >> t) & 1u);
-        }
-        break;
-      }
-      phase_bits ^= 1u << s;
+      // stage bi is the oldest of the `stages` groups in flight
+      cp_async_wait_pending(stages - 1);
+      __syncwarp();
       pos = s + 1 == stages ? 0 : s + 1;
       const uint32_t a_base = stage0 + s * C::STAGE_BYTES + ldm_off;
 
@@ -356,38 +450,111 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
         load_ends();
       }
 
-      // the stage is free again: refill it with stage bi + stages
+      // the stage is free again: refill it with stage bi + stages (an empty group past the end)
       __syncwarp();
-      if (bi + stages < nbatch) {
-        fence_proxy_async();
-        issue(bi + stages, s, col_next);
-      }
+      issue(bi + stages, s, col_next);
       col_next = col_after;
       val_cur = val_next;
     }
-    if (!ok) break;
-    // ---- end of the block: write what is still open (and any trailing empty rows)
-    while (rf < re) {
-      flush(min(4, re - rf));
-      rf += 4;
+    // ---- publish finished output rows [orb, ore) for the in-kernel all-reduce: per exchange tile,
+    //      on every peer and locally; the warp whose rows complete a tile on this rank reduces it
+    auto publish = [&](int orb, int ore) {
+      for (int T = orb / red.tile_rows; T * red.tile_rows < ore && ok; ++T) {
+        const int t0 = T * red.tile_rows;
+        const int t_rows = min(red.tile_rows, out_rows - t0);
+        const int n_rows = min(ore, t0 + red.tile_rows) - max(orb, t0);
+        int mine = 0;
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();  // the rows (local and in the peers' slots) before the counters
+          for (int q = 0; q < red.n; ++q)
+            asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(red.remote_sig[q] + T), "r"(n_rows)
+                         : "memory");
+          mine = atomicAdd(red.local_done + T, n_rows) + n_rows == t_rows;
+        }
+        mine = __shfl_sync(0xffffffffu, mine, 0);
+        if (mine) {
+          if (npend == 32) poll_pending(true);  // list full: cannot happen with sane tile sizes
+          if (lane == npend) pend_tile = T;
+          ++npend;
+        }
+      }
+    };
+
+    if (!piece) {
+      // ---- end of the block: write what is still open (and any trailing empty rows)
+      while (rf < re) {
+        flush(min(4, re - rf));
+        rf += 4;
+      }
+      if (red.n > 0) publish(rb - row_begin, re - row_begin);
+    } else {
+      // ---- end of a piece: fp32 partial row to scratch; the warp that delivers the last piece of
+      //      the row sums all pieces in index order (the same order whoever comes last) and writes it
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        xch[tig * C::XP + m * 16 + gid] = c[m][0] + c[m][1];
+        xch[tig * C::XP + m * 16 + gid + 8] = c[m][2] + c[m][3];
+      }
+      __syncwarp();
+      if (lane < vec) {
+        const float* src = xch + (rb & 3) * C::XP + lane * 8;
+        float* dst = scratch + static_cast<int64_t>(b) * D + lane * 8;
+        *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+        *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+      }
+      __syncwarp();
+      const int L = -item.y - 1;
+      const int p0 = __ldg(long_piece_start + L), p1 = __ldg(long_piece_start + L + 1);
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();
+        last = atomicAdd(long_counter + L, 1) == p1 - p0 - 1;
+        __threadfence();
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        if (lane < vec) {
+          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int pp = p0; pp < p1; ++pp) {
+            const float* src = scratch + static_cast<int64_t>(pp) * D + lane * 8;
+            float4 x0, x1;
+            asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x0.x), "=f"(x0.y), "=f"(x0.z), "=f"(x0.w) : "l"(src));
+            asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x1.x), "=f"(x1.y), "=f"(x1.z), "=f"(x1.w) : "l"(src + 4));
+            a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w;
+            a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
+          }
+          const int64_t orow = rb - row_begin;
+          if (flush_mask != nullptr)
+            mask_bf16x8(a, __ldg(reinterpret_cast<const uint4*>(flush_mask + orow * ldm + lane * 8)));
+          store_vec(out, ldo, orow, lane * 8, pack_bf16x8(a), push);
+        }
+        if (lane == 0) long_counter[L] = 0;  // ready for the next launch on this matrix
+        if (red.n > 0) publish(rb - row_begin, rb - row_begin + 1);
+      }
     }
+    if (red.n > 0) poll_pending(false);
   }
+  if (red.n > 0 && ok) poll_pending(true);
 }
 
-template <int MB, bool BULK>
+template <int VEC>
 const char* launch_one(const int* rowptr, const int* col, const float* val, const __nv_bfloat16* H, int64_t ldh,
                        __nv_bfloat16* out, int64_t ldo, const __nv_bfloat16* mask, int64_t ldm, int D,
-                       int row_begin, const int* block_start, int num_blocks, const PushTargets& push,
-                       int* status, cudaStream_t stream) {
-  using C = Cfg<MB>;
+                       int row_begin, const int4* items, int num_items, const int* long_piece_start,
+                       int* long_counter, float* scratch, const PushTargets& push,
+                       int* status, const TileReduce& red, int out_rows, int stages_override,
+                       cudaStream_t stream) {
+  using C = Cfg<VEC>;
   int sms = 148, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // about 6 KB of gathered rows in flight per warp
-  int stages = 6144 / (KB * D * 2) + 1;
+  // about 8 KB of gathered rows in flight per warp
+  int stages = 8192 / (KB * D * 2) + 1;
   stages = std::max(3, std::min(MAX_STAGES, stages));
+  if (stages_override > 0) stages = std::max(2, std::min(MAX_STAGES, stages_override));
   const int limit = 232448;
-  // warps per SM bounded by shared memory and by registers (about 128 per thread at MB = 16)
+  // warps per SM: bounded by shared memory and by registers (128 per thread -> 16 warps)
   const int wb = C::warp_bytes(stages);
   int best_w = 1, best_ctas = 1, best_total = 0;
   for (int ctas = 1; ctas <= 4; ++ctas) {
@@ -401,40 +568,67 @@ const char* launch_one(const int* rowptr, const int* col, const float* val, cons
     }
   }
   const size_t smem = static_cast<size_t>(best_w) * wb;
-  auto kern = spmm_mma_kernel<MB, BULK>;
+  auto kern = spmm_mma_kernel<VEC>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  const int grid = std::max(1, std::min(sms * best_ctas, (num_blocks + best_w - 1) / best_w));
+  const int grid = std::max(1, std::min(sms * best_ctas, (num_items + best_w - 1) / best_w));
   kern<<<grid, best_w * 32, smem, stream>>>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin,
-                                            block_start, num_blocks, push, stages, status);
+                                            items, num_items, long_piece_start, long_counter, scratch, push,
+                                            stages, status, red, out_rows);
   return last_launch_error();
 }
 
-template <bool BULK>
-const char* dispatch_mb(int mb, const int* rowptr, const int* col, const float* val, const __nv_bfloat16* H,
-                        int64_t ldh, __nv_bfloat16* out, int64_t ldo, const __nv_bfloat16* mask, int64_t ldm,
-                        int D, int row_begin, const int* block_start, int num_blocks, const PushTargets& push,
-                        int* status, cudaStream_t stream) {
-#define PLX_MB(N)                                                                                            \
+const char* dispatch_vec(int vec, const int* rowptr, const int* col, const float* val, const __nv_bfloat16* H,
+                         int64_t ldh, __nv_bfloat16* out, int64_t ldo, const __nv_bfloat16* mask, int64_t ldm,
+                         int D, int row_begin, const int4* items, int num_items, const int* long_piece_start,
+                         int* long_counter, float* scratch, const PushTargets& push,
+                         int* status, const TileReduce& red, int out_rows, int stages, cudaStream_t stream) {
+#define PLX_VEC(N)                                                                                           \
   case N:                                                                                                    \
-    return launch_one<N, BULK>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, block_start,    \
-                               num_blocks, push, status, stream)
-  switch (mb) {
-    PLX_MB(1); PLX_MB(2); PLX_MB(3); PLX_MB(4); PLX_MB(5); PLX_MB(6); PLX_MB(7); PLX_MB(8);
-    PLX_MB(9); PLX_MB(10); PLX_MB(11); PLX_MB(12); PLX_MB(13); PLX_MB(14); PLX_MB(15); PLX_MB(16);
+    return launch_one<N>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D, row_begin, items, num_items,     \
+                         long_piece_start, long_counter, scratch, push, status, red, out_rows, stages, stream)
+  switch (vec) {
+    PLX_VEC(1); PLX_VEC(2); PLX_VEC(3); PLX_VEC(4); PLX_VEC(5); PLX_VEC(6); PLX_VEC(7); PLX_VEC(8);
+    PLX_VEC(9); PLX_VEC(10); PLX_VEC(11); PLX_VEC(12); PLX_VEC(13); PLX_VEC(14); PLX_VEC(15); PLX_VEC(16);
+    PLX_VEC(17); PLX_VEC(18); PLX_VEC(19); PLX_VEC(20); PLX_VEC(21); PLX_VEC(22); PLX_VEC(23); PLX_VEC(24);
+    PLX_VEC(25); PLX_VEC(26); PLX_VEC(27); PLX_VEC(28); PLX_VEC(29); PLX_VEC(30); PLX_VEC(31); PLX_VEC(32);
   }
-#undef PLX_MB
+#undef PLX_VEC
   return "spmm_mma: unsupported width";
 }
 
 }  // namespace
 
-// All rows of block_start[0] .. block_start[num_blocks] (absolute row numbers of the CSR arrays);
-// output row = row - row_begin.  bf16 features, D a multiple of 8; wider matrices are processed in
-// column chunks of 256.  staging: 0 = 16-byte cp.async copies, 1 = one bulk copy per gathered row.
+// Work items (see the kernel): the pieces of the long rows first, then blocks of whole rows; row
+// numbers are those of the CSR arrays, output row = row - row_begin.  scratch holds one fp32 row of D
+// columns per piece, long_counter one zero-initialised int per long row (the kernel leaves it zero).
+// bf16 features, D a multiple of 8; wider matrices are processed in column chunks of 256.
+// stages: depth of the shared-memory ring (0 = chosen from the row size).
 const char* launch_spmm_mma(const int* rowptr, const int* col, const float* val, const void* H, int64_t ldh,
                             void* out, int64_t ldo, const void* mask, int64_t ldm, int D, int row_begin,
-                            const int* block_start, int num_blocks, const PushTargets* push_in, int staging,
-                            int* status, cudaStream_t stream) {
+                            const int* items_in, int num_items, int num_pieces, const int* long_piece_start,
+                            int* long_counter, float* scratch, int64_t scratch_elems,
+                            const PushTargets* push_in, int stages,
+                            int* status, cudaStream_t stream, const TileReduce* reduce_in, int out_rows) {
+  const int4* items = reinterpret_cast<const int4*>(items_in);
+  if (reinterpret_cast<uintptr_t>(items_in) % 16) return "spmm_mma: the work items must be 16-byte aligned";
+  if (num_pieces > 0 && (long_piece_start == nullptr || long_counter == nullptr || scratch == nullptr ||
+                         reinterpret_cast<uintptr_t>(scratch) % 16 ||
+                         scratch_elems < static_cast<int64_t>(num_pieces) * D))
+    return "spmm_mma: long rows need the piece index, the counters and num_pieces * D scratch floats";
+  TileReduce red = {};
+  if (reduce_in != nullptr && reduce_in->n > 0) {
+    red = *reduce_in;
+    red.status = status;
+    if (push_in == nullptr || push_in->n != red.n || push_in->seg_rows != 0)
+      return "spmm_mma: the in-kernel all-reduce goes with the broadcast push to the same peers";
+    if (red.tile_rows <= 0 || red.local_done == nullptr || out_rows <= 0)
+      return "spmm_mma: bad in-kernel all-reduce description";
+    if (D > 256) return "spmm_mma: the in-kernel all-reduce handles at most 256 columns";
+    for (int q = 0; q < red.n; ++q)
+      if (red.slot[q] == nullptr || red.remote_sig[q] == nullptr || red.local_sig[q] == nullptr ||
+          reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
+        return "spmm_mma: bad in-kernel all-reduce description";
+  }
   PushTargets push = {};
   if (push_in != nullptr) {
     push = *push_in;
@@ -449,20 +643,18 @@ const char* launch_spmm_mma(const int* rowptr, const int* col, const float* val,
   if (reinterpret_cast<uintptr_t>(H) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
       reinterpret_cast<uintptr_t>(mask) % 16)
     return "spmm_mma: feature pointers must be 16-byte aligned";
-  if (D == 0 || num_blocks == 0) return nullptr;
+  if (D == 0 || num_items == 0) return nullptr;
+  if (num_pieces > 0 && D > 256) return "spmm_mma: long rows with more than 256 columns are not handled here";
   const __nv_bfloat16* Hb = static_cast<const __nv_bfloat16*>(H);
   __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* mb_ptr = static_cast<const __nv_bfloat16*>(mask);
   for (int c0 = 0; c0 < D; c0 += 256) {
     const int d = std::min(256, D - c0);
-    const int mb = (d + 15) / 16;
     PushTargets p = push;
     for (int q = 0; q < p.n; ++q) p.base[q] = static_cast<__nv_bfloat16*>(p.base[q]) + c0;
-    const char* e = staging == 1
-        ? dispatch_mb<true>(mb, rowptr, col, val, Hb + c0, ldh, ob + c0, ldo, mb_ptr ? mb_ptr + c0 : nullptr,
-                            ldm, d, row_begin, block_start, num_blocks, p, status, stream)
-        : dispatch_mb<false>(mb, rowptr, col, val, Hb + c0, ldh, ob + c0, ldo, mb_ptr ? mb_ptr + c0 : nullptr,
-                             ldm, d, row_begin, block_start, num_blocks, p, status, stream);
+    const char* e = dispatch_vec(d / 8, rowptr, col, val, Hb + c0, ldh, ob + c0, ldo, mb_ptr ? mb_ptr + c0 : nullptr,
+                                 ldm, d, row_begin, items, num_items, long_piece_start, long_counter, scratch, p,
+                                 status, red, out_rows, stages, stream);
     if (e) return e;
   }
   return nullptr;

@@ -66,13 +66,12 @@ def _csr_parts(A):
 
 # SpMM kernel variants:
 #   1 = CUDA-core kernel (packed fp32x2 multiply-adds; also the only one for fp32 features),
-#   2 = tensor-core kernel, gathered rows staged by 16-byte cp.async copies,
-#   3 = tensor-core kernel, one bulk copy (cp.async.bulk) per gathered row,
+#   2 = tensor-core kernel (gathered rows staged in shared memory by cp.async, warp MMAs),
 #   0 = the older warp-MMA accumulation inside the CUDA-core kernel's structure (kept for comparison).
-SPMM_VARIANT = int(os.environ.get("PLEXUS_SPMM_VARIANT", "3"))
-# rows longer than this stay with the CUDA-core kernel, which cuts them in pieces across warps; the
-# tensor-core kernel walks a row with one warp
-SPMM_MMA_MAX_ROW = int(os.environ.get("PLEXUS_SPMM_MMA_MAX_ROW", str(1 << 17)))
+SPMM_VARIANT = int(os.environ.get("PLEXUS_SPMM_VARIANT", "2"))
+SPMM_MMA_STAGES = int(os.environ.get("PLEXUS_SPMM_MMA_STAGES", "0"))  # 0: chosen from the row size
+# tensor-core kernel: rows longer than this are cut in pieces across warps; cost of a block of rows
+SPMM_MMA_LONG_ROW = int(os.environ.get("PLEXUS_SPMM_MMA_LONG_ROW", "4096"))
 SPMM_MMA_BLOCK_COST = int(os.environ.get("PLEXUS_SPMM_MMA_BLOCK_COST", "4096"))
 
 # per-row constant added to the nonzero count when balancing row blocks, and the cost of a block
@@ -150,10 +149,25 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
     return sch
 
 
-def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None):
-    """``block_start`` for the tensor-core kernel: consecutive rows of about ``SPMM_MMA_BLOCK_COST``
-    nonzeros (+ a per-row constant) each, every row included; ``None`` if a row is longer than
-    ``SPMM_MMA_MAX_ROW`` (the caller then uses the CUDA-core kernel)."""
+class SpmmMmaSchedule:
+    """Work items of the tensor-core SpMM for one matrix (or row range); see ``spmm_mma_schedule``."""
+
+    __slots__ = ("items", "num_pieces", "long_piece_start", "long_counter")
+
+
+def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmMmaSchedule:
+    """Work items of the tensor-core kernel for rows ``[r0, r1)``, built once per matrix on the device.
+
+    * Rows longer than ``SPMM_MMA_LONG_ROW`` nonzeros are cut in equal pieces (multiples of 16
+      nonzeros); a warp accumulates one piece into an fp32 partial row and the warp that delivers
+      the last piece of a row sums the pieces in index order.
+    * The other rows form blocks of consecutive rows of about ``SPMM_MMA_BLOCK_COST`` nonzeros
+      (+ a per-row constant) each; a block never contains a long row, so its nonzeros are one
+      contiguous range of the CSR arrays.
+
+    ``items`` is int32 ``[n, 4]``: the pieces first (``row, -(long id + 1), first nnz, last nnz + 1``),
+    then the blocks (``first row, last row + 1, 0, 0``).
+    """
     cache = None
     if owner is not None:
         cache = getattr(owner, "_plx_spmm_mma_schedules", None)
@@ -163,29 +177,60 @@ def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None):
                 owner._plx_spmm_mma_schedules = cache
             except Exception:
                 cache = None
-    key = (r0, r1, SPMM_MMA_BLOCK_COST)
+    key = (r0, r1, SPMM_MMA_BLOCK_COST, SPMM_MMA_LONG_ROW)
     if cache is not None and key in cache:
         return cache[key]
     dev = crow.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    sch = SpmmMmaSchedule()
     rows = r1 - r0
-    if rows <= 0:
-        res = torch.empty(0, dtype=torch.int32, device=dev)
+    beg = crow[r0:r1].to(torch.int64)
+    deg = crow[r0 + 1 : r1 + 1].to(torch.int64) - beg
+    is_long = deg > SPMM_MMA_LONG_ROW
+    # ---- pieces of the long rows
+    lidx = torch.nonzero(is_long).flatten()
+    if lidx.numel():
+        ldeg, lbeg = deg[lidx], beg[lidx]
+        want = (ldeg + SPMM_MMA_LONG_ROW - 1) // SPMM_MMA_LONG_ROW
+        plen = ((ldeg + want - 1) // want + 15) // 16 * 16
+        npieces = (ldeg + plen - 1) // plen
+        pstart = torch.zeros(lidx.numel() + 1, dtype=torch.int64, device=dev)
+        pstart[1:] = torch.cumsum(npieces, 0)
+        owner_of = torch.repeat_interleave(torch.arange(lidx.numel(), device=dev), npieces)
+        k = torch.arange(int(pstart[-1]), device=dev) - pstart[:-1][owner_of]
+        pb = lbeg[owner_of] + k * plen[owner_of]
+        pe = torch.minimum(pb + plen[owner_of], (lbeg + ldeg)[owner_of])
+        pieces = torch.stack([lidx[owner_of] + r0, -(owner_of + 1), pb, pe], dim=1)
+        sch.long_piece_start = pstart.to(torch.int32)
+        sch.long_counter = torch.zeros(lidx.numel(), **i32)
     else:
-        deg = (crow[r0 + 1 : r1 + 1] - crow[r0:r1]).to(torch.int64)
-        if int(deg.max()) > SPMM_MMA_MAX_ROW:
-            res = None
-        else:
-            wcum = torch.cumsum(deg + SPMM_ROW_COST, 0)
-            total = int(wcum[-1])
-            nb = max(1, min(rows, total // SPMM_MMA_BLOCK_COST))
-            targets = (torch.arange(1, nb, device=dev, dtype=torch.float64) * (total / nb)).to(torch.int64)
-            inner = torch.searchsorted(wcum, targets, right=True)
-            res = (torch.unique_consecutive(torch.cat([
-                torch.zeros(1, dtype=torch.int64, device=dev), inner,
-                torch.full((1,), rows, dtype=torch.int64, device=dev)])) + r0).to(torch.int32)
+        pieces = torch.empty((0, 4), dtype=torch.int64, device=dev)
+        sch.long_piece_start = torch.empty(0, **i32)
+        sch.long_counter = torch.empty(0, **i32)
+    sch.num_pieces = int(pieces.shape[0])
+    # ---- blocks of the other rows: a new block where the accumulated cost crosses a multiple of the
+    #      block cost, and after every long row
+    sidx = torch.nonzero(~is_long).flatten()
+    if sidx.numel():
+        cost = deg[sidx] + SPMM_ROW_COST
+        wcum = torch.cumsum(cost, 0)
+        blk = (wcum - cost) // SPMM_MMA_BLOCK_COST
+        run = torch.cumsum(is_long.to(torch.int64), 0)[sidx]
+        keyv = run * (int(blk[-1]) + 2) + blk
+        first = torch.ones(sidx.numel(), dtype=torch.bool, device=dev)
+        first[1:] = keyv[1:] != keyv[:-1]
+        starts = torch.nonzero(first).flatten()
+        ends = torch.cat([starts[1:], torch.full((1,), sidx.numel(), dtype=torch.int64, device=dev)])
+        rb = sidx[starts] + r0
+        re = sidx[ends - 1] + 1 + r0
+        zeros = torch.zeros_like(rb)
+        blocks = torch.stack([rb, re, zeros, zeros], dim=1)
+    else:
+        blocks = torch.empty((0, 4), dtype=torch.int64, device=dev)
+    sch.items = torch.cat([pieces, blocks]).to(torch.int32).contiguous()
     if cache is not None:
-        cache[key] = res
-    return res
+        cache[key] = sch
+    return sch
 
 
 DEBUG = os.environ.get("PLEXUS_DEBUG", "0") not in ("", "0")
@@ -202,12 +247,24 @@ def validate_csr(A) -> None:
     check_status(col.device)
 
 
+def spmm_supports_tile_reduce(A, H, row_range=None) -> bool:
+    """Whether :func:`spmm` can finish an all-reduce inside the kernel for these operands (the
+    tensor-core kernel must be the one that runs, and one launch must cover all columns)."""
+    if SPMM_VARIANT != 2 or H.dtype != torch.bfloat16 or H.shape[1] % 8 or H.shape[1] > 256:
+        return False
+    r0, r1 = row_range if row_range is not None else (0, A.shape[0])
+    return r1 > r0
+
+
 def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_dtype=None, out=None,
-         push_ptrs=(), push_ld=0, variant=None, push_seg=(0, 0)):
+         push_ptrs=(), push_ld=0, variant=None, push_seg=(0, 0), tile_reduce=None):
     """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
     ``push_seg = (rows per owner, this rank's position)``: reduce-scatter push (each row goes only
     to the rank that owns it) instead of the broadcast push.
-    ``variant``: see ``SPMM_VARIANT`` (default: the tensor-core kernel for bf16 features)."""
+    ``variant``: see ``SPMM_VARIANT`` (default: the tensor-core kernel for bf16 features).
+    ``tile_reduce = (slots, remote_sig, local_sig, me, timeout_ms, tile_rows, local_done_ptr)``:
+    finish the all-reduce over the push peers inside the kernel (the mask is applied after the
+    sum); only with the tensor-core kernel, see :func:`spmm_supports_tile_reduce`."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -228,16 +285,23 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
     variant = SPMM_VARIANT if variant is None else int(variant)
-    if variant in (2, 3) and H.dtype == torch.bfloat16 and H.shape[1] % 8 == 0 and r1 > r0:
-        blocks = spmm_mma_schedule(crow, r0, r1, owner=A)
-        if blocks is not None:
-            C.spmm_mma(crow, col, val, H, out, relu_mask, r0, blocks, list(push_ptrs), int(push_ld),
-                       1 if variant == 3 else 0, int(push_seg[0]), int(push_seg[1]), status_buffer(H.device))
+    if variant == 2 and H.dtype == torch.bfloat16 and H.shape[1] % 8 == 0 and r1 > r0:
+        sch = spmm_mma_schedule(crow, r0, r1, owner=A)
+        if sch.num_pieces == 0 or H.shape[1] <= 256:
+            tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0.0, 0, 0)
+            scratch = (_scratch_floats(sch.num_pieces * H.shape[1], H.device) if sch.num_pieces
+                       else _EMPTY_F32(H.device))
+            C.spmm_mma(crow, col, val, H, out, relu_mask, r0, sch.items, sch.num_pieces, sch.long_piece_start,
+                       sch.long_counter, scratch, list(push_ptrs), int(push_ld),
+                       SPMM_MMA_STAGES, int(push_seg[0]), int(push_seg[1]), status_buffer(H.device),
+                       list(tr[0]), list(tr[1]), list(tr[2]), int(tr[3]), float(tr[4]), int(tr[5]), int(tr[6]))
             _count(-(-H.shape[1] // 256))
             if out_dtype is not None and out_dtype != out.dtype:
                 out = out.to(out_dtype)
             return out
-    if variant in (2, 3):
+    if tile_reduce is not None:
+        raise RuntimeError("spmm: the in-kernel all-reduce needs the tensor-core kernel")
+    if variant == 2:
         variant = 1
     sch = spmm_schedule(crow, r0, r1, owner=A)
     npieces = sch.piece_beg.numel()
@@ -265,11 +329,13 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
 
 
 def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant: int = 0,
-         push_ptrs=(), push_ld=0, relu_mask=None, push_seg=(0, 0), out=None):
+         push_ptrs=(), push_ld=0, relu_mask=None, push_seg=(0, 0), out=None, tile_reduce=None):
     """``relu_mask`` (shape of the result): zero the result where the mask is not positive.
     ``push_ptrs`` / ``push_seg``: fused-collective epilogue, see :func:`spmm`.
     ``out``: optional destination of ``op(a) @ op(b)`` for the non-transposed-``a`` forms (rows
-    contiguous, e.g. a row block of a larger matrix)."""
+    contiguous, e.g. a row block of a larger matrix).
+    ``tile_reduce = (slots, remote_sig, local_sig, base, me, timeout_ms)``: finish the all-reduce
+    over the push peers inside the kernel (ReLU / mask applied after the sum)."""
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas, nb = GEMM_VARIANTS[variant]
@@ -308,8 +374,10 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         raise ValueError("gemm: out has the wrong shape or layout")
     if relu_mask is not None and relu_mask.dtype != out.dtype:
         relu_mask = relu_mask.to(out.dtype)
+    tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0, 0.0)
     C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask,
-              int(push_seg[0]), int(push_seg[1]))
+              int(push_seg[0]), int(push_seg[1]), list(tr[0]), list(tr[1]), list(tr[2]), int(tr[3]), int(tr[4]),
+              float(tr[5]))
     _count(1)
     return out
 

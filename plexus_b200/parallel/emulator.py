@@ -73,6 +73,9 @@ class _Kernels:
     def symm_close(self, addr: int) -> None:
         self._segments.pop(addr).close()
 
+    def symm_clear(self, addr: int, nbytes: int) -> None:
+        ctypes.memset(addr, 0, int(nbytes))
+
     def symm_free(self, addr: int) -> None:
         shm = self._segments.pop(addr)
         shm.close()
@@ -202,31 +205,93 @@ class _Ops:
                 _view(a, (r1 - r0) * push_ld, out.dtype).view(r1 - r0, push_ld)[:, :cols].copy_(out[r0:r1])
                 out[r0:r1] = float("nan")  # the kernel never writes these rows locally
 
+    def spmm_supports_tile_reduce(self, A, H, row_range=None) -> bool:
+        return True
+
     def spmm(self, A, H, relu_mask=None, row_range=None, out_dtype=None, out=None, push_ptrs=(), push_ld=0,
-             variant=None, push_seg=(0, 0)):
+             variant=None, push_seg=(0, 0), tile_reduce=None):
         from ..ops import reference
 
-        res = reference.spmm(A, H, relu_mask=relu_mask, row_range=row_range, out_dtype=out_dtype).contiguous()
+        fused = tile_reduce is not None and len(tile_reduce[0]) > 0
+        res = reference.spmm(A, H, relu_mask=None if fused else relu_mask, row_range=row_range,
+                             out_dtype=out_dtype).contiguous()
         if out is not None:
             out.copy_(res)
             res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
+        if fused:
+            self._tile_reduce_rows(res, tile_reduce, push_ld, relu_mask)
         self._count(1)
         return res
 
+    def _tile_reduce_rows(self, res, tile_reduce, slot_ld, mask):
+        """The SpMM's in-kernel all-reduce: per exchange tile, add the rows pushed to the peers'
+        counters, wait (bounded) for the peers' counts, sum in group-rank order, clear the counters."""
+        slots, remote_sig, local_sig, me, timeout_ms, tile_rows, _local_done = tile_reduce
+        rows, cols = res.shape
+        acc_dtype = torch.float64 if res.dtype == torch.float64 else torch.float32
+        tiles = [(t0, min(tile_rows, rows - t0)) for t0 in range(0, rows, tile_rows)]
+        for T, (t0, n) in enumerate(tiles):
+            for a in remote_sig:
+                c = ctypes.c_int32.from_address(a + 4 * T)
+                c.value = c.value + n  # the only writer of this counter during the op
+        deadline = time.time() + timeout_ms / 1e3
+        for T, (t0, n) in enumerate(tiles):
+            for q, a in enumerate(local_sig):
+                c = ctypes.c_int32.from_address(a + 4 * T)
+                while c.value < n:
+                    if time.time() > deadline:
+                        st = self.status_buffer()
+                        if int(st[0]) == 0:
+                            st[:5] = torch.tensor([1, 7, 20 + q, n, c.value], dtype=torch.int32)
+                        return
+                    time.sleep(0.0002)
+            seg = res[t0 : t0 + n]
+            others = [_view(a, rows * slot_ld, res.dtype).view(rows, slot_ld)[t0 : t0 + n, :cols] for a in slots]
+            _Kernels._finish(seg, _Kernels._ordered_sum(seg, others, me, acc_dtype), False,
+                             None if mask is None else mask[t0 : t0 + n])
+            for a in local_sig:
+                ctypes.c_int32.from_address(a + 4 * T).value = 0
+
     def gemm(self, a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant=0, push_ptrs=(),
-             push_ld=0, relu_mask=None, push_seg=(0, 0), out=None):
+             push_ld=0, relu_mask=None, push_seg=(0, 0), out=None, tile_reduce=None):
         from ..ops import reference
 
-        res = reference.gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu, out_dtype=out_dtype).contiguous()
-        if relu_mask is not None:
+        fused = tile_reduce is not None and len(tile_reduce[0]) > 0
+        # with the in-kernel all-reduce the activation and the mask come after the sum
+        res = reference.gemm(a, b, trans_a=trans_a, trans_b=trans_b, relu=relu and not fused,
+                             out_dtype=out_dtype).contiguous()
+        if relu_mask is not None and not fused:
             res = reference.relu_backward(res, relu_mask)
         if out is not None:
             out.copy_(res)
             res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
+        if fused:
+            self._tile_reduce(res, tile_reduce, push_ld, relu, relu_mask, signal_index=0)
         self._count(1)
         return res
+
+    def _tile_reduce(self, res, tile_reduce, slot_ld, relu, mask, signal_index):
+        """The in-kernel all-reduce with the whole matrix as one tile: publish one signal per peer
+        (value ``base + 1``), wait for the peers' signals (bounded), sum in group-rank order."""
+        slots, remote_sig, local_sig, base, me, timeout_ms = tile_reduce[:6]
+        for a in remote_sig:
+            ctypes.c_int32.from_address(a + 4 * signal_index).value = int(base) + 1
+        deadline = time.time() + timeout_ms / 1e3
+        for q, a in enumerate(local_sig):
+            flag = ctypes.c_int32.from_address(a + 4 * signal_index)
+            while flag.value - (int(base) + 1) < 0:
+                if time.time() > deadline:
+                    st = self.status_buffer()
+                    if int(st[0]) == 0:
+                        st[:5] = torch.tensor([1, 6, 20 + q, int(base) + 1, flag.value], dtype=torch.int32)
+                    return
+                time.sleep(0.0002)
+        rows, cols = res.shape
+        acc_dtype = torch.float64 if res.dtype == torch.float64 else torch.float32
+        others = [_view(a, rows * slot_ld, res.dtype).view(rows, slot_ld)[:, :cols] for a in slots]
+        _Kernels._finish(res, _Kernels._ordered_sum(res, others, me, acc_dtype), relu, mask)
 
     def relu_backward(self, grad, out):
         from ..ops import reference

@@ -63,6 +63,8 @@ TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 # receive slots (2 buffers x p slots per axis) stay bounded however large the activations are
 # (a 55M x 86 bf16 matrix is 9.5 GB; unblocked its slots alone would take 38 GB per axis).
 MAX_MESSAGE_BYTES = int(os.environ.get("PLEXUS_MAX_MESSAGE_BYTES", str(2 << 30)))
+# finish one-shot all-reduces inside the compute kernel (tile by tile, no separate reduce launch)
+IN_KERNEL_REDUCE = os.environ.get("PLEXUS_IN_KERNEL_REDUCE", "1") != "0"
 ROW_BLOCK_MULTIPLE = 128  # row blocks start on a GEMM tile boundary
 
 
@@ -78,7 +80,7 @@ def _row_blocks(rows: int, row_bytes: int):
 
 
 # how often each form carried a matrix collective (for tests and the metrics sink)
-op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0}
+op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0, "in_kernel": 0}
 
 
 def _skip() -> bool:
@@ -161,11 +163,16 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     blocks = _row_blocks(rows, D * H.element_size())
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
+    in_kernel = IN_KERNEL_REDUCE and opc.spmm_supports_tile_reduce(A, H)
     if len(blocks) == 1:
         ax.ensure(rows * D * H.element_size())
         epoch, buf = ax.next_op()
-        out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
-        _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
+        if in_kernel:
+            out = opc.spmm(A, H, relu_mask=relu_mask, push_ptrs=ax.push_targets(buf), push_ld=D,
+                           tile_reduce=ax.tile_reduce_spmm(buf, rows))
+        else:
+            out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
+            _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
     else:
         # one op per row block: the receive slots stay bounded
         op_counts["row_blocked"] += 1
@@ -173,9 +180,16 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
         ax.ensure(max(r1 - r0 for r0, r1 in blocks) * D * H.element_size())
         for r0, r1 in blocks:
             epoch, buf = ax.next_op()
-            opc.spmm(A, H, row_range=(r0, r1), out=out[r0:r1], push_ptrs=ax.push_targets(buf), push_ld=D)
-            _reduce(ax, out[r0:r1], buf, epoch, False, None if relu_mask is None else relu_mask[r0:r1], KID_SPMM)
+            mask_blk = None if relu_mask is None else relu_mask[r0:r1]
+            if in_kernel and opc.spmm_supports_tile_reduce(A, H, (r0, r1)):
+                opc.spmm(A, H, relu_mask=mask_blk, row_range=(r0, r1), out=out[r0:r1],
+                         push_ptrs=ax.push_targets(buf), push_ld=D, tile_reduce=ax.tile_reduce_spmm(buf, r1 - r0))
+            else:
+                opc.spmm(A, H, row_range=(r0, r1), out=out[r0:r1], push_ptrs=ax.push_targets(buf), push_ld=D)
+                _reduce(ax, out[r0:r1], buf, epoch, False, mask_blk, KID_SPMM)
     op_counts["one_shot"] += 1
+    if in_kernel:
+        op_counts["in_kernel"] += 1
     return out
 
 
@@ -232,21 +246,32 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
         dist.all_reduce(out, group=group)
         return torch.relu_(out) if relu else out
     blocks = _row_blocks(rows, N * a.element_size())
+    in_kernel = IN_KERNEL_REDUCE and (emulator.active() or (a.dtype == torch.bfloat16 and N % 8 == 0))
     if len(blocks) == 1:
         ax.ensure(rows * N * a.element_size())
         epoch, buf = ax.next_op()
-        out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
-        _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
+        if in_kernel:
+            out = opc.gemm(a, W, trans_b=trans_b, relu=relu, push_ptrs=ax.push_targets(buf), push_ld=N,
+                           tile_reduce=ax.tile_reduce_gemm(epoch, buf))
+        else:
+            out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
+            _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
     else:
         op_counts["row_blocked"] += 1
         out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
         ax.ensure(max(r1 - r0 for r0, r1 in blocks) * N * a.element_size())
         for r0, r1 in blocks:
             epoch, buf = ax.next_op()
-            opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
-                     out=out[r0:r1])
-            _reduce(ax, out[r0:r1], buf, epoch, relu, None, KID_GEMM)
+            if in_kernel:
+                opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=relu, push_ptrs=ax.push_targets(buf), push_ld=N,
+                         out=out[r0:r1], tile_reduce=ax.tile_reduce_gemm(epoch, buf))
+            else:
+                opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
+                         out=out[r0:r1])
+                _reduce(ax, out[r0:r1], buf, epoch, relu, None, KID_GEMM)
     op_counts["one_shot"] += 1
+    if in_kernel:
+        op_counts["in_kernel"] += 1
     return out
 
 

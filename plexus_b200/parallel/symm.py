@@ -4,7 +4,12 @@ A workspace is one ``cudaMalloc`` per rank whose CUDA-IPC handle is exchanged ov
 process group, so every rank holds a device pointer into every peer's buffer and kernels can
 store into / load from peer memory directly over NVLink.  Layout of each rank's buffer::
 
-    [ flags: int32[2][8] (1 KiB reserved) | buffer 0: p slots | buffer 1: p slots ]
+    [ flags: int32[2][8] (1 KiB) | signals: int32[2][8][SIG_INTS] | buffer 0: p slots | buffer 1: p slots ]
+
+The signals serve the kernels that finish an all-reduce themselves: per (buffer, source rank) the
+first ``GEMM_SIG_INTS`` entries are written by the source's GEMM CTAs (one entry per CTA, counting
+the tiles it has pushed), the next ``TILE_SIG_INTS`` count, per fixed block of output rows, how
+many rows of that block the source's SpMM has pushed.
 
 Slot ``s`` of a buffer receives data from group rank ``s``.  The op counter ("epoch") of an axis
 selects buffer ``epoch % 2``; see ``csrc/kernels/comm_fused.cu`` for the flag protocol and why
@@ -35,8 +40,13 @@ def _device_sync() -> None:
     if not emulator.active():
         torch.cuda.synchronize()
 
-FLAG_BYTES = 1024
 MAX_GROUP = 8
+OP_FLAG_BYTES = 1024
+GEMM_SIG_INTS = 256          # >= the largest grid of the tcgen05 GEMM
+TILE_SIG_INTS = 65536        # row blocks of one SpMM output
+SIG_INTS = GEMM_SIG_INTS + TILE_SIG_INTS
+FLAG_BYTES = OP_FLAG_BYTES + 2 * MAX_GROUP * SIG_INTS * 4
+EPOCH_LIMIT = 100000         # signal values are epoch << 14 + count: stay far below 2^31
 DEFAULT_TIMEOUT_MS = 5000.0
 
 
@@ -64,6 +74,7 @@ class AxisComm:
         self.local_ptr = 0
         self.ptrs: List[int] = []
         self.timeout_ms = DEFAULT_TIMEOUT_MS
+        self._local_done = None  # per-tile row counters of this rank's own SpMM (device-local)
 
     # -- allocation ---------------------------------------------------------------------
     def ensure(self, slot_bytes: int) -> None:
@@ -116,8 +127,49 @@ class AxisComm:
         return self.ptrs[owner] + (buf * MAX_GROUP + src) * 4
 
     def next_op(self):
+        if self.epoch >= EPOCH_LIMIT:
+            self._restart_epochs()
         self.epoch += 1
         return self.epoch, self.epoch % 2
+
+    def _restart_epochs(self) -> None:
+        """Start counting ops from zero again (collective: every rank of the axis reaches the limit
+        at the same op).  Nobody may still be waiting on an old value when the flags are cleared."""
+        _device_sync()
+        dist.barrier(group=self.group)
+        _C().symm_clear(self.local_ptr, FLAG_BYTES)
+        _device_sync()
+        dist.barrier(group=self.group)
+        self.epoch = 0
+
+    def sig_base(self, epoch: int) -> int:
+        return epoch << 14
+
+    def gemm_sig(self, owner: int, buf: int, src: int) -> int:
+        """Address of the per-CTA signal array that rank ``src`` writes inside ``owner``'s workspace."""
+        return self.ptrs[owner] + OP_FLAG_BYTES + ((buf * MAX_GROUP + src) * SIG_INTS) * 4
+
+    def tile_sig(self, owner: int, buf: int, src: int) -> int:
+        """Address of the per-row-block counters that rank ``src`` adds to inside ``owner``'s workspace."""
+        return self.gemm_sig(owner, buf, src) + GEMM_SIG_INTS * 4
+
+    def tile_reduce_gemm(self, epoch: int, buf: int):
+        """Argument tuple of the GEMM's in-kernel all-reduce for op ``epoch`` (see ``ops.cuda.gemm``)."""
+        return (self.recv_slots(buf), [self.gemm_sig(q, buf, self.rank) for q in self.peers],
+                [self.gemm_sig(self.rank, buf, q) for q in self.peers], self.sig_base(epoch), self.rank,
+                self.timeout_ms)
+
+    def tile_reduce_spmm(self, buf: int, out_rows: int):
+        """Argument tuple of the SpMM's in-kernel all-reduce (see ``ops.cuda.spmm``): exchange tiles of
+        at least 512 output rows, at most ``TILE_SIG_INTS`` of them."""
+        tile_rows = max(512, -(-out_rows // TILE_SIG_INTS))
+        tile_rows = -(-tile_rows // 128) * 128
+        if self._local_done is None:
+            dev = "cpu" if emulator.active() else torch.device("cuda", torch.cuda.current_device())
+            self._local_done = torch.zeros(TILE_SIG_INTS, dtype=torch.int32, device=dev)
+        return (self.recv_slots(buf), [self.tile_sig(q, buf, self.rank) for q in self.peers],
+                [self.tile_sig(self.rank, buf, q) for q in self.peers], self.rank, self.timeout_ms, tile_rows,
+                self._local_done.data_ptr())
 
     def push_targets(self, buf: int) -> List[int]:
         """This rank's slot in every peer's buffer."""

@@ -153,6 +153,134 @@ def test_two_shot_all_reduce(world):
     run_gpus(_two_shot_ops, world)
 
 
+def _sparse_shard(dense, dev):
+    from plexus_b200.data import graph_ops
+
+    rows, cols = dense.shape
+    sp = dense.to_sparse_coo().coalesce()
+    crow, col, val = graph_ops.coo_to_csr(sp.indices()[0].to(dev), sp.indices()[1].to(dev), sp.values().to(dev),
+                                          rows, cols)
+    return graph_ops.csr_tensor(crow, col, val, (rows, cols))
+
+
+def _in_kernel_ops(rank, world, long_row):
+    """All-reduces finished inside the compute kernels (one-shot form): the GEMM exchanges 128-row
+    tiles CTA by CTA, the SpMM exchanges fixed blocks of rows tracked by counters.  Results are checked
+    against fp32 sums and must be bitwise equal on every rank of the group."""
+    import plexus_b200 as plx
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.parallel import fused
+
+    fused.ONE_SHOT_MAX_RANKS = 8
+    fused.SMALL_MESSAGE_BYTES = 0
+    opc.SPMM_MMA_LONG_ROW = long_row
+    grid = plx.init(world, 1, 1, comm="fused")
+    g = grid.group("x")
+    ax = fused.symm.axis_for(g)
+    ax.timeout_ms = 2000.0
+    dev = torch.device("cuda", rank)
+
+    def close(got, want, tag):
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-3, (tag, err)
+        every = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(every, got.contiguous(), group=g)
+        assert all(torch.equal(every[0], e) for e in every), (tag, "replicas differ")
+
+    before = dict(fused.op_counts)
+    # rows: fewer than one tile, not a multiple of the tile, more tiles than CTAs (several per CTA)
+    for it, (rows, cols, D) in enumerate([(100, 300, 64), (3001, 2000, 128), (40000, 5000, 256), (20011, 3000, 48)]):
+        gen = torch.Generator().manual_seed(200 + it)
+        K = 64
+        Xs = [torch.randn(rows, K, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        Ws = [(torch.randn(K, D, generator=gen) / 8).to(torch.bfloat16) for _ in range(world)]
+        wantg = sum(Xs[r].float() @ Ws[r].float() for r in range(world))
+        for rep in range(2):  # twice: both buffers of the axis, and the second use of every signal
+            close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].to(dev), g), wantg, ("gemm", it, rep))
+        close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].to(dev), g, relu=True), torch.relu(wantg),
+              ("gemm relu", it))
+        close(fused.gemm_all_reduce(Xs[rank].to(dev), Ws[rank].t().contiguous().to(dev), g, trans_b=True),
+              wantg, ("gemm nt", it))
+        # sparse product; every rank has other rows that are long or empty
+        dens = 0.004 if rows > 10000 else 0.03
+        dense = [(torch.rand(rows, cols, generator=gen) < dens).float() * torch.randn(rows, cols, generator=gen)
+                 for _ in range(world)]
+        for r in range(world):
+            dense[r][(17 * (r + 1)) % rows] = torch.randn(cols, generator=gen)       # a full row
+            dense[r][(5 + r) % rows::97] = 0                                           # empty rows
+        Hs = [torch.randn(cols, D, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        mask = torch.randn(rows, D, generator=gen).to(torch.bfloat16)
+        want = sum(dense[r] @ Hs[r].float() for r in range(world))
+        A, H = _sparse_shard(dense[rank], dev), Hs[rank].to(dev)
+        for rep in range(2):
+            close(fused.spmm_all_reduce(A, H, g), want, ("spmm", it, rep))
+        close(fused.spmm_all_reduce(A, H, g, relu_mask=mask.to(dev)), want * (mask.float() > 0), ("spmm mask", it))
+    torch.cuda.synchronize()
+    opc.check_status()
+    assert fused.op_counts["in_kernel"] - before["in_kernel"] == 4 * 7, fused.op_counts
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("world,long_row", [(2, 4096), (2, 64), (4, 256)])
+def test_in_kernel_all_reduce(world, long_row):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_in_kernel_ops, world, long_row, timeout=300)
+
+
+def _other_forms(rank, world):
+    """Forms that so far only ran on the emulated peer memory: the reduce-scatter fused into the SpMM,
+    all-reduces carried in row blocks under a small message cap, and the all-gather in pieces."""
+    import plexus_b200 as plx
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.parallel import fused
+
+    grid = plx.init(world, 1, 1, comm="fused")
+    g = grid.group("x")
+    dev = torch.device("cuda", rank)
+    gen = torch.Generator().manual_seed(7)
+    rows, cols, D = 1024 * world, 900, 64
+    dense = [(torch.rand(rows, cols, generator=gen) < 0.03).float() * torch.randn(rows, cols, generator=gen)
+             for _ in range(world)]
+    Hs = [torch.randn(cols, D, generator=gen).to(torch.bfloat16) for _ in range(world)]
+    want = sum(dense[r] @ Hs[r].float() for r in range(world))
+    A, H = _sparse_shard(dense[rank], dev), Hs[rank].to(dev)
+    seg = fused.spmm_reduce_scatter(A, H, g)
+    assert seg is not None and seg.shape == (rows // world, D)
+    mine = want[rank * rows // world : (rank + 1) * rows // world]
+    assert (seg.float().cpu() - mine).abs().max() <= 2e-2 * want.abs().max() + 1e-3
+    # row blocks: a cap of 64 KB per op
+    old = fused.MAX_MESSAGE_BYTES
+    fused.MAX_MESSAGE_BYTES = 1 << 16
+    try:
+        before = fused.op_counts["row_blocked"]
+        out = fused.spmm_all_reduce(A, H, g)
+        assert (out.float().cpu() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-3
+        X = torch.randn(rows, 64, generator=gen).to(torch.bfloat16)
+        W = (torch.randn(64, D, generator=gen) / 8).to(torch.bfloat16)
+        og = fused.gemm_all_reduce(X.to(dev), W.to(dev), g, relu=True)
+        wg = torch.relu(world * (X.float() @ W.float()))
+        assert (og.float().cpu() - wg).abs().max() <= 2e-2 * wg.abs().max() + 1e-3
+        assert fused.op_counts["row_blocked"] == before + 2
+        # all-gather in pieces of at most the cap
+        t = torch.arange(40000, dtype=torch.float32) + 1e6 * rank
+        ga = fused.all_gather(t.to(dev), g)
+        assert torch.equal(ga.cpu(), torch.cat([torch.arange(40000, dtype=torch.float32) + 1e6 * r
+                                                for r in range(world)]))
+    finally:
+        fused.MAX_MESSAGE_BYTES = old
+    torch.cuda.synchronize()
+    opc.check_status()
+    plx.shutdown()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_reduce_scatter_row_blocks_and_gather_pieces(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_other_forms, world)
+
+
 def _model(rank, world, grid, layers, force_two_shot=False):
     import plexus_b200 as plx
     from plexus_b200.models.cross_entropy import parallel_cross_entropy
