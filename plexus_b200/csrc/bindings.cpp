@@ -97,13 +97,14 @@ const int* int_ptr(const Tensor& t) {
   return t.data_ptr<int>();
 }
 
-// schedule tensors: block_start, piece_beg, piece_end, long_rows, long_piece_start (int32, device)
-void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
-              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& block_start,
-              const Tensor& piece_beg, const Tensor& piece_end, const Tensor& long_rows,
-              const Tensor& long_piece_start, const Tensor& scratch,
-              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t variant,
-              int64_t push_seg_rows, int64_t push_me) {
+// Both SpMM kernels take the same arguments; `tensor_core` selects spmm_mma.cu (bf16 only).
+void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H,
+                Tensor& out, const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& items,
+                int64_t num_pieces, const Tensor& long_piece_start, Tensor& long_counter, const Tensor& scratch,
+                const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t stages, int64_t push_seg_rows,
+                int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots,
+                const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
+                int64_t red_me, double red_timeout_ms, int64_t red_tile_rows, int64_t red_local_done) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -111,6 +112,7 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
   TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && val.is_contiguous());
   TORCH_CHECK(H.dim() == 2 && out.dim() == 2 && H.stride(1) == 1 && out.stride(1) == 1);
   TORCH_CHECK(out.scalar_type() == H.scalar_type(), "spmm: out dtype must match H");
+  TORCH_CHECK(!tensor_core || H.scalar_type() == at::kBFloat16, "spmm: the tensor-core kernel takes bf16 features");
   const int64_t D = H.size(1);
   TORCH_CHECK(out.size(1) == D, "spmm: bad output shape");
   const void* mptr = nullptr;
@@ -121,61 +123,7 @@ void spmm_csr(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
     mptr = mask->data_ptr();
     ldm = mask->stride(0);
   }
-  plx::SpmmSchedule s;
-  s.block_start = int_ptr(block_start);
-  s.num_blocks = block_start.numel() > 0 ? static_cast<int>(block_start.numel()) - 1 : 0;
-  s.piece_beg = int_ptr(piece_beg);
-  s.piece_end = int_ptr(piece_end);
-  s.num_pieces = static_cast<int>(piece_beg.numel());
-  TORCH_CHECK(piece_end.numel() == piece_beg.numel());
-  s.long_rows = int_ptr(long_rows);
-  s.long_piece_start = int_ptr(long_piece_start);
-  s.num_long = static_cast<int>(long_rows.numel());
-  TORCH_CHECK(s.num_long == 0 || long_piece_start.numel() == long_rows.numel() + 1);
-  float* scr = nullptr;
-  int64_t scr_n = 0;
-  if (scratch.defined() && scratch.numel() > 0) {
-    TORCH_CHECK(scratch.is_cuda() && scratch.scalar_type() == at::kFloat && scratch.is_contiguous());
-    scr = scratch.data_ptr<float>();
-    scr_n = scratch.numel();
-  }
-  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
-  TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
-              "spmm: row segments do not cover the output");
-  c10::cuda::CUDAGuard guard(H.device());
-  check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(),
-                             val.data_ptr<float>(), H.data_ptr(), H.stride(0), out.data_ptr(),
-                             out.stride(0), mptr, ldm, static_cast<int>(D), static_cast<int>(row_begin),
-                             s, scr, scr_n, push.n ? &push : nullptr, static_cast<int>(variant), stream()));
-}
-
-// Tensor-core SpMM (bf16): the work items cover every row of [row_begin, row_begin + out.size(0)).
-void spmm_mma(const Tensor& rowptr, const Tensor& col, const Tensor& val, const Tensor& H, Tensor& out,
-              const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& items, int64_t num_pieces,
-              const Tensor& long_piece_start, Tensor& long_counter, const Tensor& scratch,
-              const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t stages, int64_t push_seg_rows,
-              int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots,
-              const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
-              int64_t red_me, double red_timeout_ms, int64_t red_tile_rows, int64_t red_local_done) {
-  TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
-  TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
-              "spmm: int32 CSR indices required");
-  TORCH_CHECK(val.scalar_type() == at::kFloat, "spmm: fp32 CSR values required");
-  TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && val.is_contiguous());
-  TORCH_CHECK(H.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
-              "spmm_mma: bf16 features required");
-  TORCH_CHECK(H.dim() == 2 && out.dim() == 2 && H.stride(1) == 1 && out.stride(1) == 1);
-  const int64_t D = H.size(1);
-  TORCH_CHECK(out.size(1) == D, "spmm: bad output shape");
-  const void* mptr = nullptr;
-  int64_t ldm = 0;
-  if (mask.has_value() && mask->defined()) {
-    TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == H.scalar_type() && mask->size(1) == D &&
-                mask->size(0) == out.size(0) && mask->stride(1) == 1, "spmm: bad mask");
-    mptr = mask->data_ptr();
-    ldm = mask->stride(0);
-  }
-  TORCH_CHECK(items.numel() % 4 == 0, "spmm_mma: work items are 4 ints each");
+  TORCH_CHECK(items.numel() % 4 == 0, "spmm: work items are 4 ints each");
   const int num_items = static_cast<int>(items.numel() / 4);
   float* scr = nullptr;
   int64_t scr_n = 0;
@@ -194,13 +142,23 @@ void spmm_mma(const Tensor& rowptr, const Tensor& col, const Tensor& val, const 
               "spmm: row segments do not cover the output");
   plx::TileReduce red = make_tile_reduce(red_slots, red_remote_sig, red_local_sig, 0, red_me, red_timeout_ms,
                                          red_tile_rows, red_local_done);
+  red.status = status_ptr(status);
   c10::cuda::CUDAGuard guard(H.device());
-  check(plx::launch_spmm_mma(rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(), H.data_ptr(),
-                             H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm, static_cast<int>(D),
-                             static_cast<int>(row_begin), int_ptr(items), num_items, static_cast<int>(num_pieces),
-                             int_ptr(long_piece_start), counters, scr, scr_n, push.n ? &push : nullptr,
-                             static_cast<int>(stages), status_ptr(status), stream(), red.n ? &red : nullptr,
-                             static_cast<int>(out.size(0))));
+  if (tensor_core) {
+    check(plx::launch_spmm_mma(rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(), H.data_ptr(),
+                               H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm, static_cast<int>(D),
+                               static_cast<int>(row_begin), int_ptr(items), num_items,
+                               static_cast<int>(num_pieces), int_ptr(long_piece_start), counters, scr, scr_n,
+                               push.n ? &push : nullptr, static_cast<int>(stages), status_ptr(status), stream(),
+                               red.n ? &red : nullptr, static_cast<int>(out.size(0))));
+  } else {
+    check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(),
+                               H.data_ptr(), H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm,
+                               static_cast<int>(D), static_cast<int>(row_begin), int_ptr(items), num_items,
+                               static_cast<int>(num_pieces), int_ptr(long_piece_start), counters, scr, scr_n,
+                               push.n ? &push : nullptr, stream(), red.n ? &red : nullptr,
+                               static_cast<int>(out.size(0))));
+  }
 }
 
 int64_t spmm_scratch_per_piece(const Tensor& H) {
@@ -570,9 +528,7 @@ void csr_validate(const Tensor& rowptr, const Tensor& col, int64_t nrows, int64_
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("spmm_csr", &spmm_csr, "CSR SpMM, bf16/fp32 features, fp32 accumulate");
-  m.def("spmm_mma", &spmm_mma, "CSR SpMM on the tensor cores (bf16 features, fp32 accumulate)");
-  m.def("spmm_piece_size", &plx::spmm_piece_size);
+  m.def("spmm_items", &spmm_items, "CSR SpMM (CUDA-core or tensor-core kernel), fp32 accumulate");
   m.def("spmm_scratch_per_piece", &spmm_scratch_per_piece);
   m.def("gemm_nt", &gemm_nt, "C = A . B^T on tcgen05 (bf16 in, fp32 accumulate)");
   m.def("gemm_tn_parts", &gemm_tn_parts, "number of row splits gemm_tn uses");

@@ -49,32 +49,18 @@ struct TileReduce {
 };
 
 // ---- spmm.cu
-// Per-matrix work schedule (device arrays, built once per shard; see ops/cuda.py):
-//   block_start[num_blocks+1] : consecutive-row blocks of about equal cost
-//   long rows (more than spmm_piece_size() nonzeros) are cut in pieces [piece_beg, piece_end) of
-//   the nonzero range; long_piece_start[num_long+1] indexes the pieces of each long row.
-struct SpmmSchedule {
-  const int* block_start;
-  int num_blocks;
-  const int* piece_beg;
-  const int* piece_end;
-  int num_pieces;
-  const int* long_rows;
-  const int* long_piece_start;
-  int num_long;
-};
-int spmm_piece_size();
+// CUDA-core SpMM (bf16 or fp32 features), one launch.  Work items, 4 ints each: the pieces of the
+// long rows first ({row, -(long id + 1), first nonzero, last nonzero + 1}; a piece's index is also
+// the index of its fp32 partial row in `scratch`, spmm_scratch_per_piece() floats each), then
+// blocks of whole rows ({first row, last row + 1, 0, 0}).  long_piece_start[num_long + 1] indexes
+// the pieces of each long row; long_counter[num_long] must be zero and is left zero.
 int64_t spmm_scratch_per_piece(int dtype, int D);
-// scratch: fp32, num_pieces * spmm_scratch_per_piece(dtype, D) elements (unused without long rows)
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
-                            int64_t ldm, int D, int row_begin, const SpmmSchedule& sched,
+                            int64_t ldm, int D, int row_begin, const int* items, int num_items,
+                            int num_pieces, const int* long_piece_start, int* long_counter,
                             float* scratch, int64_t scratch_elems, const PushTargets* push,
-                            int variant, cudaStream_t stream);
-// variant: how a row's nonzeros are accumulated.  FMA: packed fp32x2 multiply-adds on CUDA cores
-// (the fastest measured, used by default from Python).  TENSOR: gathered rows are staged in shared
-// memory and summed by warp-level MMAs (bf16 features up to 256 columns; other cases use FMA).
-enum : int { SPMM_VARIANT_TENSOR = 0, SPMM_VARIANT_FMA = 1 };
+                            cudaStream_t stream, const TileReduce* reduce = nullptr, int out_rows = 0);
 
 // ---- spmm_mma.cu
 // Tensor-core SpMM for bf16 features (any D that is a multiple of 8), one launch for rows of any

@@ -49,8 +49,10 @@ struct alignas(8) GemmBarriers {
   uint64_t tempty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int wait_ok;
-  int pad;
+  int seen;        // epilogue: number of this CTA's tiles every peer has published (broadcast slot)
+  int sig_idle;    // the signalling warp is waiting at its barrier
+  int sig_count;   // tiles stored so far, handed to the signalling warp (-1: leave)
+  int do_sig;      // epilogue broadcast slot: hand over at this tile
 };
 
 // Epilogue staging: every epilogue warp owns 32 rows; a segment of SEG_BYTES per row goes
@@ -127,6 +129,9 @@ __device__ __forceinline__ unsigned long long gemm_global_ns() {
   return t;
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// hand-over from the four epilogue warps (arrive, not blocking) to the signalling warp (sync)
+__device__ __forceinline__ void sig_bar_arrive() { asm volatile("bar.arrive 2, 160;" ::: "memory"); }
+__device__ __forceinline__ void sig_bar_sync() { asm volatile("bar.sync 2, 160;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg16(const void* p) {
   uint4 v;
   asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -142,34 +147,23 @@ __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
   }
 }
 
-// The four epilogue warps (128 threads, `tid` 0..127) finish rows [r0, r0 + nrows) x columns
-// [n0, n0 + ncols): wait until every peer published tile number `expect` of this CTA, then
-// C = act(sum over the group of the partials), summed in group-rank order.  Returns false after a
-// timeout (recorded in the status words).
-__device__ __forceinline__ bool reduce_tile_bf16(__nv_bfloat16* __restrict__ C, int ldc, int r0, int nrows, int n0,
-                                                 int ncols, const TileReduce& red, int64_t slot_ld, int cta,
-                                                 int expect, int relu, const __nv_bfloat16* __restrict__ mask,
-                                                 int ldm, int tid, volatile int* wait_ok) {
-  if (tid == 0) {
-    int good = 1;
-    const unsigned long long t0 = gemm_global_ns();
-    for (int q = 0; q < red.n && good; ++q) {
-      int seen;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
-      while (seen - expect < 0) {
-        if (gemm_global_ns() - t0 > red.timeout_ns) {
-          report_status(red.status, ST_TIMEOUT, KERNEL_ID_GEMM, 20 + q, expect, seen);
-          good = 0;
-          break;
-        }
-        __nanosleep(32);
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
-      }
-    }
-    *wait_ok = good;
+// Peers' progress: the smallest number of tiles of CTA `cta` that every peer has published.
+__device__ __forceinline__ int peers_published(const TileReduce& red, int cta) {
+  int m = 0x7fffffff;
+  for (int q = 0; q < red.n; ++q) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
+    m = min(m, seen - red.base);
   }
-  epi_bar_sync();
-  if (!*wait_ok) return false;
+  return m;
+}
+
+// The four epilogue warps (128 threads, `tid` 0..127) finish rows [r0, r0 + nrows) x columns
+// [n0, n0 + ncols) of a tile whose partials have arrived from every peer:
+// C = act(sum over the group of the partials), summed in group-rank order.
+__device__ __forceinline__ void reduce_tile_bf16(__nv_bfloat16* __restrict__ C, int ldc, int r0, int nrows, int n0,
+                                                 int ncols, const TileReduce& red, int64_t slot_ld, int relu,
+                                                 const __nv_bfloat16* __restrict__ mask, int ldm, int tid) {
   const int vpr = ncols >> 3;
   const int total = nrows * vpr;
   constexpr int UN = 4;
@@ -218,14 +212,13 @@ __device__ __forceinline__ bool reduce_tile_bf16(__nv_bfloat16* __restrict__ C, 
       *reinterpret_cast<uint4*>(C + off_c[u]) = o;
     }
   }
-  return true;
 }
 
 // ---------------------------------------------------------------------------------------
 // C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = block of bn_box columns)
 // ---------------------------------------------------------------------------------------
 template <typename OutT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + 32, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
                int b_resident, int relu, int* status, const PushTargets push,
@@ -260,7 +253,10 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&bars->tempty[b], 4);
     }
     bars->abort_flag = 0;
-    bars->wait_ok = 1;
+    bars->seen = 0;
+    bars->sig_idle = 1;
+    bars->sig_count = 0;
+    bars->do_sig = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -352,7 +348,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (ok) umma_commit(&bars->tfull[buf]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant owned by this warp
     // with the in-kernel all-reduce the activation and the mask are applied after the sum
@@ -361,8 +357,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (fuse_reduce) relu = 0;
     const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
     const int epi_tid = (warp - 2) * 32 + lane;
-    int prev_tile = -1;
-    bool red_ok = true;
+    int reduced = 0;  // tiles of this CTA already summed over the group
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
@@ -483,33 +478,106 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if constexpr (sizeof(OutT) == 2) {
         if (fuse_reduce) {
-          // every epilogue warp has stored this tile locally and into the peers' slots: publish it,
-          // then finish the previous tile, whose partials from the peers had a whole tile's time to arrive
+          // The tile is stored, locally and in the peers' slots.  If the signalling warp is free, hand
+          // it the tile count: it publishes the CTA's progress on the peers (one system-scope fence
+          // covers every tile stored so far) without holding the epilogue up.  Then finish whatever
+          // tiles have arrived from the peers in the meantime.
           epi_bar_sync();
           if (epi_tid == 0) {
-            __threadfence_system();
-            for (int p = 0; p < red.n; ++p)
-              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(red.remote_sig[p] + cta_id),
-                           "r"(red.base + static_cast<int>(t) + 1)
-                           : "memory");
+            const int idle = *reinterpret_cast<volatile int*>(&bars->sig_idle);
+            bars->do_sig = idle;
+            if (idle) {
+              bars->sig_count = static_cast<int>(t) + 1;
+              bars->sig_idle = 0;
+            }
+            bars->seen = peers_published(red, cta_id);
           }
-          if (prev_tile >= 0 &&
-              !reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, prev_tile * BM, min(BM, M - prev_tile * BM),
-                                n0, n_valid, red, push.ld, cta_id, red.base + static_cast<int>(t), relu_in,
-                                reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid, &bars->wait_ok)) {
-            red_ok = false;
-            *abort_flag = 1;
-            break;
+          epi_bar_sync();
+          if (bars->do_sig) sig_bar_arrive();
+          const int upto = min(bars->seen, static_cast<int>(t) + 1);
+          for (; reduced < upto; ++reduced) {
+            const int rt = blockIdx.x + reduced * gridDim.x;
+            reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, rt * BM, min(BM, M - rt * BM), n0, n_valid,
+                             red, push.ld, relu_in, reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid);
           }
-          prev_tile = tile;
         }
       }
     }
     if constexpr (sizeof(OutT) == 2) {
-      if (fuse_reduce && red_ok && prev_tile >= 0 && !*abort_flag)
-        reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, prev_tile * BM, min(BM, M - prev_tile * BM), n0,
-                         n_valid, red, push.ld, cta_id, red.base + static_cast<int>(t), relu_in,
-                         reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid, &bars->wait_ok);
+      if (fuse_reduce) {
+        // all tiles computed (or given up): the last hand-over carries the final count, or -1
+        const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                             static_cast<int>(gridDim.x);
+        const bool complete = !*abort_flag && static_cast<int>(t) == my_tiles;
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          // if the last hand-over already carried the final count, the signalling warp leaves by itself
+          const int final_sent = bars->sig_count == my_tiles;
+          bars->do_sig = !final_sent;
+          if (!final_sent) {
+            const unsigned long long t0 = gemm_global_ns();
+            while (*reinterpret_cast<volatile int*>(&bars->sig_idle) == 0 && gemm_global_ns() - t0 < 8 * red.timeout_ns)
+              __nanosleep(100);
+            bars->sig_count = complete ? my_tiles : -1;
+            bars->sig_idle = 0;
+          }
+        }
+        epi_bar_sync();
+        if (bars->do_sig) sig_bar_arrive();
+        // wait (bounded) for the peers' remaining tiles and finish them
+        const unsigned long long t0 = gemm_global_ns();
+        while (complete && reduced < my_tiles) {
+          epi_bar_sync();
+          if (epi_tid == 0) {
+            int m = peers_published(red, cta_id);
+            if (m <= reduced && gemm_global_ns() - t0 > red.timeout_ns) {
+              report_status(red.status, ST_TIMEOUT, KERNEL_ID_GEMM, 20, reduced, m);
+              m = -1;
+            }
+            bars->seen = m;
+          }
+          epi_bar_sync();
+          const int got = bars->seen;
+          if (got < 0) {
+            *abort_flag = 1;
+            break;
+          }
+          if (got <= reduced) __nanosleep(200);
+          for (const int upto = min(got, my_tiles); reduced < upto; ++reduced) {
+            const int rt = blockIdx.x + reduced * gridDim.x;
+            reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, rt * BM, min(BM, M - rt * BM), n0, n_valid,
+                             red, push.ld, relu_in, reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid);
+          }
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------- signalling warp (in-kernel all-reduce only)
+    // Woken through a named barrier by the epilogue warps after they stored a tile; the barrier makes
+    // their stores (local and remote) precede the fence below.  The fence waits for the NVLink
+    // stores to drain, tens of microseconds under load: here that is off the epilogue's critical
+    // path, and one fence covers every tile stored so far.
+    if (red.n > 0) {
+      const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+      const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                           static_cast<int>(gridDim.x);
+      while (true) {
+        sig_bar_sync();
+        const int cnt = *reinterpret_cast<volatile int*>(&bars->sig_count);
+        if (cnt < 0) break;
+        if (lane == 0) {
+          __threadfence_system();
+          for (int p = 0; p < red.n; ++p)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(red.remote_sig[p] + cta_id), "r"(red.base + cnt)
+                         : "memory");
+        }
+        __syncwarp();
+        if (cnt >= my_tiles) break;  // sig_idle stays 0: nobody hands over again
+        if (lane == 0) {
+          __threadfence_block();
+          *reinterpret_cast<volatile int*>(&bars->sig_idle) = 1;
+        }
+      }
     }
   }
 
@@ -802,7 +870,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   if (c_dtype == DT_BF16) {
     auto kern = gemm_nt_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
+    kern<<<grid, red.n > 0 ? GEMM_THREADS + 32 : GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),
                                                static_cast<int>(N), static_cast<int>(K), bn_box, stages,
                                                b_resident, relu ? 1 : 0, status, push,

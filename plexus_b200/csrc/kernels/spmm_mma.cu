@@ -33,6 +33,7 @@
 
 #include "../include/plexus_kernels.h"
 #include "../include/ptx_sm100.cuh"
+#include "../include/spmm_tile_reduce.cuh"
 
 namespace plx {
 
@@ -135,93 +136,6 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16* __restrict__ out, int64
       *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(push.base[q]) + orow * push.ld + c) = packed;
 }
 
-__device__ __forceinline__ unsigned long long spmm_global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint4 ld_cg16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 f = __bfloat1622float2(p[k]);
-    acc[2 * k] += f.x;
-    acc[2 * k + 1] += f.y;
-  }
-}
-
-// In-kernel all-reduce: have all peers pushed every row of exchange tile `tile` (nrows rows)?
-__device__ __forceinline__ bool tile_arrived(const TileReduce& red, int tile, int nrows, int* seen_out) {
-  for (int q = 0; q < red.n; ++q) {
-    int seen;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + tile) : "memory");
-    if (seen < nrows) {
-      *seen_out = seen;
-      return false;
-    }
-  }
-  return true;
-}
-
-// In-kernel all-reduce, one exchange tile (output rows [r0, r0 + nrows)) whose partials have all
-// arrived, done by one warp: out = mask(sum over the group), partials added in group-rank order;
-// finally clear the tile's counters for the next op that uses this buffer.
-__device__ __forceinline__ void reduce_rows_tile(__nv_bfloat16* __restrict__ out, int64_t ldo, int r0, int nrows,
-                                                 int D, const __nv_bfloat16* __restrict__ mask, int64_t ldm,
-                                                 const TileReduce& red, int64_t slot_ld, int tile, int lane) {
-  __threadfence();
-  __syncwarp();
-  const int vec = D >> 3;
-  const int total = nrows * vec;
-  constexpr int UN = 4;
-  for (int v0 = lane; v0 < total; v0 += 32 * UN) {
-    int64_t off_o[UN], off_s[UN], off_m[UN];
-    bool live[UN];
-    uint4 own[UN];
-    float acc[UN][8];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int v = v0 + u * 32;
-      live[u] = v < total;
-      const int r = live[u] ? v / vec : 0, c = live[u] ? (v - r * vec) * 8 : 0;
-      off_o[u] = static_cast<int64_t>(r0 + r) * ldo + c;
-      off_s[u] = static_cast<int64_t>(r0 + r) * slot_ld + c;
-      off_m[u] = static_cast<int64_t>(r0 + r) * ldm + c;
-      own[u] = ld_cg16(out + off_o[u]);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
-      if (red.me <= 0) add_bf16x8(acc[u], own[u]);
-    }
-    for (int q = 0; q < red.n; ++q) {
-      const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(red.slot[q]);
-      uint4 pv[UN];
-#pragma unroll
-      for (int u = 0; u < UN; ++u) pv[u] = ld_cg16(sp + off_s[u]);
-#pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        add_bf16x8(acc[u], pv[u]);
-        if (q + 1 == red.me) add_bf16x8(acc[u], own[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      if (!live[u]) continue;
-      if (mask != nullptr) mask_bf16x8(acc[u], ld_cg16(mask + off_m[u]));
-      *reinterpret_cast<uint4*>(out + off_o[u]) = pack_bf16x8(acc[u]);
-    }
-  }
-  __syncwarp();
-  if (lane == 0) {
-    for (int q = 0; q < red.n; ++q) red.local_sig[q][tile] = 0;
-    red.local_done[tile] = 0;
-  }
-}
-
 // VEC: 16-byte pieces per feature row (D = 8 * VEC), a compile-time constant so that the piece ->
 // (nonzero, column) mapping of the staging copies costs no division.
 template <int VEC>
@@ -262,40 +176,8 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
   int pos = 0;  // ring stage of the next stage to consume
   bool ok = true;
 
-  // In-kernel all-reduce: exchange tiles this warp has to reduce (their last local row came from
-  // this warp) and whose partials from the peers have not all arrived yet.  A warp never waits for
-  // a peer while it still has work items: both ranks' warps finish their own rows unconditionally,
-  // so the final wait below cannot deadlock.  Lane j keeps pending tile j.
-  int pend_tile = 0, npend = 0;
-  auto poll_pending = [&](bool blocking) {
-    const unsigned long long t0 = blocking ? spmm_global_ns() : 0ull;
-    while (npend > 0 && ok) {
-      bool ready = false;
-      int seen = 0, t_rows = 0;
-      if (lane < npend) {
-        t_rows = min(red.tile_rows, out_rows - pend_tile * red.tile_rows);
-        ready = tile_arrived(red, pend_tile, t_rows, &seen);
-      }
-      const unsigned ready_mask = __ballot_sync(0xffffffffu, ready);
-      if (ready_mask == 0u) {
-        if (!blocking) return;
-        if (spmm_global_ns() - t0 > red.timeout_ns) {
-          if (lane == 0) report_status(red.status, ST_TIMEOUT, KERNEL_ID_SPMM_MMA, 20, t_rows, seen);
-          ok = false;
-          return;
-        }
-        __nanosleep(128);
-        continue;
-      }
-      const int j = __ffs(ready_mask) - 1;
-      const int T = __shfl_sync(0xffffffffu, pend_tile, j);
-      const int last = __shfl_sync(0xffffffffu, pend_tile, npend - 1);
-      if (lane == j) pend_tile = last;
-      --npend;
-      const int r0 = T * red.tile_rows;
-      reduce_rows_tile(out, ldo, r0, min(red.tile_rows, out_rows - r0), D, mask, ldm, red, push.ld, T, lane);
-    }
-  };
+  // in-kernel all-reduce (red.n > 0): see spmm_tile_reduce.cuh
+  tile_reduce::Reducer reducer(red, out, ldo, mask, ldm, push.ld, D, out_rows, lane, KERNEL_ID_SPMM_MMA);
 
   const int warp_global = blockIdx.x * wpb + warp;
   const int warps_total = gridDim.x * wpb;
@@ -456,38 +338,13 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
       col_next = col_after;
       val_cur = val_next;
     }
-    // ---- publish finished output rows [orb, ore) for the in-kernel all-reduce: per exchange tile,
-    //      on every peer and locally; the warp whose rows complete a tile on this rank reduces it
-    auto publish = [&](int orb, int ore) {
-      for (int T = orb / red.tile_rows; T * red.tile_rows < ore && ok; ++T) {
-        const int t0 = T * red.tile_rows;
-        const int t_rows = min(red.tile_rows, out_rows - t0);
-        const int n_rows = min(ore, t0 + red.tile_rows) - max(orb, t0);
-        int mine = 0;
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_system();  // the rows (local and in the peers' slots) before the counters
-          for (int q = 0; q < red.n; ++q)
-            asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(red.remote_sig[q] + T), "r"(n_rows)
-                         : "memory");
-          mine = atomicAdd(red.local_done + T, n_rows) + n_rows == t_rows;
-        }
-        mine = __shfl_sync(0xffffffffu, mine, 0);
-        if (mine) {
-          if (npend == 32) poll_pending(true);  // list full: cannot happen with sane tile sizes
-          if (lane == npend) pend_tile = T;
-          ++npend;
-        }
-      }
-    };
-
     if (!piece) {
       // ---- end of the block: write what is still open (and any trailing empty rows)
       while (rf < re) {
         flush(min(4, re - rf));
         rf += 4;
       }
-      if (red.n > 0) publish(rb - row_begin, re - row_begin);
+      if (red.n > 0) reducer.publish(rb - row_begin, re - row_begin);
     } else {
       // ---- end of a piece: fp32 partial row to scratch; the warp that delivers the last piece of
       //      the row sums all pieces in index order (the same order whoever comes last) and writes it
@@ -510,10 +367,10 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
       if (lane == 0) {
         __threadfence();
         last = atomicAdd(long_counter + L, 1) == p1 - p0 - 1;
-        __threadfence();
       }
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last) {
+        __threadfence();
         if (lane < vec) {
           float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           for (int pp = p0; pp < p1; ++pp) {
@@ -530,12 +387,15 @@ spmm_mma_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, con
           store_vec(out, ldo, orow, lane * 8, pack_bf16x8(a), push);
         }
         if (lane == 0) long_counter[L] = 0;  // ready for the next launch on this matrix
-        if (red.n > 0) publish(rb - row_begin, rb - row_begin + 1);
+        if (red.n > 0) reducer.publish(rb - row_begin, rb - row_begin + 1);
       }
     }
-    if (red.n > 0) poll_pending(false);
+    if (red.n > 0) {
+      reducer.poll(false);
+      ok = ok && reducer.ok;
+    }
   }
-  if (red.n > 0 && ok) poll_pending(true);
+  if (red.n > 0 && ok) reducer.finish();
 }
 
 template <int VEC>

@@ -66,30 +66,39 @@ def _csr_parts(A):
 
 # SpMM kernel variants:
 #   1 = CUDA-core kernel (packed fp32x2 multiply-adds; also the only one for fp32 features),
-#   2 = tensor-core kernel (gathered rows staged in shared memory by cp.async, warp MMAs),
-#   0 = the older warp-MMA accumulation inside the CUDA-core kernel's structure (kept for comparison).
-SPMM_VARIANT = int(os.environ.get("PLEXUS_SPMM_VARIANT", "2"))
+#   2 = tensor-core kernel (gathered rows staged in shared memory by cp.async, warp MMAs; bf16 only).
+# Measured on B200 the CUDA-core kernel is the faster one at every width of the GCN configurations
+# (e.g. 1.07 ms against 1.33 ms on a 1.2M x 1.2M shard with 31M nonzeros at 128 columns), so it is
+# the default; the tensor-core kernel stays selectable.
+SPMM_VARIANT = int(os.environ.get("PLEXUS_SPMM_VARIANT", "1"))
 SPMM_MMA_STAGES = int(os.environ.get("PLEXUS_SPMM_MMA_STAGES", "0"))  # 0: chosen from the row size
-# tensor-core kernel: rows longer than this are cut in pieces across warps; cost of a block of rows
-SPMM_MMA_LONG_ROW = int(os.environ.get("PLEXUS_SPMM_MMA_LONG_ROW", "4096"))
-SPMM_MMA_BLOCK_COST = int(os.environ.get("PLEXUS_SPMM_MMA_BLOCK_COST", "4096"))
-
-# per-row constant added to the nonzero count when balancing row blocks, and the cost of a block
+# per-row constant added to the nonzero count when balancing row blocks
 SPMM_ROW_COST = 8
-SPMM_BLOCK_COST = 1024
+# (rows longer than this are cut in pieces across warps, cost of a block of rows) per variant
+SPMM_LONG_ROW = {1: int(os.environ.get("PLEXUS_SPMM_LONG_ROW", "1024")),
+                 2: int(os.environ.get("PLEXUS_SPMM_MMA_LONG_ROW", "4096"))}
+SPMM_BLOCK_COST = {1: int(os.environ.get("PLEXUS_SPMM_BLOCK_COST", "1024")),
+                   2: int(os.environ.get("PLEXUS_SPMM_MMA_BLOCK_COST", "4096"))}
 
 
 class SpmmSchedule:
-    """Device-side work schedule of one CSR matrix (or row range), built once and cached."""
+    """Work items of an SpMM kernel for one matrix (or row range); see ``spmm_schedule``."""
 
-    __slots__ = ("block_start", "piece_beg", "piece_end", "long_rows", "long_piece_start", "launches")
+    __slots__ = ("items", "num_pieces", "long_piece_start", "long_counter")
 
 
-def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSchedule:
-    """Row blocks of about equal cost plus the pieces of rows longer than the kernel's piece size.
+def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None, variant: int = 1) -> SpmmSchedule:
+    """Work items of an SpMM kernel for rows ``[r0, r1)``, built once per matrix on the device.
 
-    The result is cached on ``owner`` (the sparse tensor object), so it lives exactly as long
-    as the matrix it describes.
+    * Rows longer than ``SPMM_LONG_ROW[variant]`` nonzeros are cut in equal pieces (multiples of 16
+      nonzeros); a warp accumulates one piece into an fp32 partial row and the warp that delivers
+      the last piece of a row sums the pieces in index order.
+    * The other rows form blocks of consecutive rows of about ``SPMM_BLOCK_COST[variant]`` nonzeros
+      (+ a per-row constant) each; a block never contains a long row, so its nonzeros are one
+      contiguous range of the CSR arrays.
+
+    ``items`` is int32 ``[n, 4]``: the pieces first (``row, -(long id + 1), first nnz, last nnz + 1``),
+    then the blocks (``first row, last row + 1, 0, 0``).
     """
     cache = None
     if owner is not None:
@@ -100,98 +109,22 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmSched
                 owner._plx_spmm_schedules = cache
             except Exception:
                 cache = None
-    key = (r0, r1)
+    long_row, block_cost = SPMM_LONG_ROW[variant], SPMM_BLOCK_COST[variant]
+    key = (r0, r1, block_cost, long_row)
     if cache is not None and key in cache:
         return cache[key]
-    _schedules = cache if cache is not None else {}
-    piece = _ext.load().spmm_piece_size()
     dev = crow.device
     i32 = dict(dtype=torch.int32, device=dev)
     sch = SpmmSchedule()
     rows = r1 - r0
-    if rows <= 0:
-        empty = torch.empty(0, **i32)
-        sch.block_start = sch.piece_beg = sch.piece_end = sch.long_rows = sch.long_piece_start = empty
-        sch.launches = 0
-        _schedules[key] = sch
-        return sch
     beg = crow[r0:r1].to(torch.int64)
     deg = crow[r0 + 1 : r1 + 1].to(torch.int64) - beg
-    is_long = deg > piece
-    cost = torch.where(is_long, torch.zeros_like(deg), deg) + SPMM_ROW_COST
-    wcum = torch.cumsum(cost, 0)
-    total = int(wcum[-1])
-    nb = max(1, min(rows, total // SPMM_BLOCK_COST))
-    targets = (torch.arange(1, nb, device=dev, dtype=torch.float64) * (total / nb)).to(torch.int64)
-    inner = torch.searchsorted(wcum, targets, right=True)
-    sch.block_start = (torch.cat([
-        torch.zeros(1, dtype=torch.int64, device=dev), inner,
-        torch.full((1,), rows, dtype=torch.int64, device=dev)]) + r0).to(torch.int32)
-    idx = torch.nonzero(is_long).flatten()
-    if idx.numel():
-        ldeg, lbeg = deg[idx], beg[idx]
-        npieces = (ldeg + piece - 1) // piece
-        pstart = torch.zeros(idx.numel() + 1, dtype=torch.int64, device=dev)
-        pstart[1:] = torch.cumsum(npieces, 0)
-        owner = torch.repeat_interleave(torch.arange(idx.numel(), device=dev), npieces)
-        k = torch.arange(int(pstart[-1]), device=dev) - pstart[:-1][owner]
-        pb = lbeg[owner] + k * piece
-        pe = torch.minimum(pb + piece, (lbeg + ldeg)[owner])
-        sch.piece_beg, sch.piece_end = pb.to(torch.int32), pe.to(torch.int32)
-        sch.long_rows = (idx + r0).to(torch.int32)
-        sch.long_piece_start = pstart.to(torch.int32)
-        sch.launches = 3
-    else:
-        empty = torch.empty(0, **i32)
-        sch.piece_beg = sch.piece_end = sch.long_rows = sch.long_piece_start = empty
-        sch.launches = 1
-    _schedules[key] = sch
-    return sch
-
-
-class SpmmMmaSchedule:
-    """Work items of the tensor-core SpMM for one matrix (or row range); see ``spmm_mma_schedule``."""
-
-    __slots__ = ("items", "num_pieces", "long_piece_start", "long_counter")
-
-
-def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmMmaSchedule:
-    """Work items of the tensor-core kernel for rows ``[r0, r1)``, built once per matrix on the device.
-
-    * Rows longer than ``SPMM_MMA_LONG_ROW`` nonzeros are cut in equal pieces (multiples of 16
-      nonzeros); a warp accumulates one piece into an fp32 partial row and the warp that delivers
-      the last piece of a row sums the pieces in index order.
-    * The other rows form blocks of consecutive rows of about ``SPMM_MMA_BLOCK_COST`` nonzeros
-      (+ a per-row constant) each; a block never contains a long row, so its nonzeros are one
-      contiguous range of the CSR arrays.
-
-    ``items`` is int32 ``[n, 4]``: the pieces first (``row, -(long id + 1), first nnz, last nnz + 1``),
-    then the blocks (``first row, last row + 1, 0, 0``).
-    """
-    cache = None
-    if owner is not None:
-        cache = getattr(owner, "_plx_spmm_mma_schedules", None)
-        if cache is None:
-            cache = {}
-            try:
-                owner._plx_spmm_mma_schedules = cache
-            except Exception:
-                cache = None
-    key = (r0, r1, SPMM_MMA_BLOCK_COST, SPMM_MMA_LONG_ROW)
-    if cache is not None and key in cache:
-        return cache[key]
-    dev = crow.device
-    i32 = dict(dtype=torch.int32, device=dev)
-    sch = SpmmMmaSchedule()
-    rows = r1 - r0
-    beg = crow[r0:r1].to(torch.int64)
-    deg = crow[r0 + 1 : r1 + 1].to(torch.int64) - beg
-    is_long = deg > SPMM_MMA_LONG_ROW
+    is_long = deg > long_row
     # ---- pieces of the long rows
     lidx = torch.nonzero(is_long).flatten()
     if lidx.numel():
         ldeg, lbeg = deg[lidx], beg[lidx]
-        want = (ldeg + SPMM_MMA_LONG_ROW - 1) // SPMM_MMA_LONG_ROW
+        want = (ldeg + long_row - 1) // long_row
         plen = ((ldeg + want - 1) // want + 15) // 16 * 16
         npieces = (ldeg + plen - 1) // plen
         pstart = torch.zeros(lidx.numel() + 1, dtype=torch.int64, device=dev)
@@ -214,7 +147,7 @@ def spmm_mma_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None) -> SpmmM
     if sidx.numel():
         cost = deg[sidx] + SPMM_ROW_COST
         wcum = torch.cumsum(cost, 0)
-        blk = (wcum - cost) // SPMM_MMA_BLOCK_COST
+        blk = (wcum - cost) // block_cost
         run = torch.cumsum(is_long.to(torch.int64), 0)[sidx]
         keyv = run * (int(blk[-1]) + 2) + blk
         first = torch.ones(sidx.numel(), dtype=torch.bool, device=dev)
@@ -248,9 +181,10 @@ def validate_csr(A) -> None:
 
 
 def spmm_supports_tile_reduce(A, H, row_range=None) -> bool:
-    """Whether :func:`spmm` can finish an all-reduce inside the kernel for these operands (the
-    tensor-core kernel must be the one that runs, and one launch must cover all columns)."""
-    if SPMM_VARIANT != 2 or H.dtype != torch.bfloat16 or H.shape[1] % 8 or H.shape[1] > 256:
+    """Whether :func:`spmm` can finish an all-reduce inside the kernel for these operands."""
+    if H.dtype != torch.bfloat16 or H.shape[1] % 8:
+        return False
+    if SPMM_VARIANT == 2 and H.shape[1] > 256:
         return False
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
     return r1 > r0
@@ -261,10 +195,10 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     """``push_ptrs``: this rank's receive slots in the peers' workspaces (fused collective).
     ``push_seg = (rows per owner, this rank's position)``: reduce-scatter push (each row goes only
     to the rank that owns it) instead of the broadcast push.
-    ``variant``: see ``SPMM_VARIANT`` (default: the tensor-core kernel for bf16 features).
+    ``variant``: see ``SPMM_VARIANT``.
     ``tile_reduce = (slots, remote_sig, local_sig, me, timeout_ms, tile_rows, local_done_ptr)``:
     finish the all-reduce over the push peers inside the kernel (the mask is applied after the
-    sum); only with the tensor-core kernel, see :func:`spmm_supports_tile_reduce`."""
+    sum); see :func:`spmm_supports_tile_reduce`."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -285,31 +219,24 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
     variant = SPMM_VARIANT if variant is None else int(variant)
-    if variant == 2 and H.dtype == torch.bfloat16 and H.shape[1] % 8 == 0 and r1 > r0:
-        sch = spmm_mma_schedule(crow, r0, r1, owner=A)
-        if sch.num_pieces == 0 or H.shape[1] <= 256:
-            tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0.0, 0, 0)
-            scratch = (_scratch_floats(sch.num_pieces * H.shape[1], H.device) if sch.num_pieces
-                       else _EMPTY_F32(H.device))
-            C.spmm_mma(crow, col, val, H, out, relu_mask, r0, sch.items, sch.num_pieces, sch.long_piece_start,
-                       sch.long_counter, scratch, list(push_ptrs), int(push_ld),
-                       SPMM_MMA_STAGES, int(push_seg[0]), int(push_seg[1]), status_buffer(H.device),
-                       list(tr[0]), list(tr[1]), list(tr[2]), int(tr[3]), float(tr[4]), int(tr[5]), int(tr[6]))
-            _count(-(-H.shape[1] // 256))
-            if out_dtype is not None and out_dtype != out.dtype:
-                out = out.to(out_dtype)
-            return out
-    if tile_reduce is not None:
-        raise RuntimeError("spmm: the in-kernel all-reduce needs the tensor-core kernel")
-    if variant == 2:
+    if variant not in (1, 2):
+        raise ValueError("spmm: variant must be 1 (CUDA cores) or 2 (tensor cores)")
+    if variant == 2 and not (H.dtype == torch.bfloat16 and H.shape[1] % 8 == 0):
         variant = 1
-    sch = spmm_schedule(crow, r0, r1, owner=A)
-    npieces = sch.piece_beg.numel()
-    scratch = _scratch_floats(npieces * C.spmm_scratch_per_piece(H), H.device) if npieces else _EMPTY_F32(H.device)
-    C.spmm_csr(crow, col, val, H, out, relu_mask, r0, sch.block_start, sch.piece_beg, sch.piece_end,
-               sch.long_rows, sch.long_piece_start, scratch, list(push_ptrs), int(push_ld),
-               variant, int(push_seg[0]), int(push_seg[1]))
-    _count(sch.launches)
+    if r1 == r0 or H.shape[1] == 0:
+        return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
+    sch = spmm_schedule(crow, r0, r1, owner=A, variant=variant)
+    if variant == 2 and sch.num_pieces and H.shape[1] > 256:
+        variant = 1  # the tensor-core kernel sums pieces of at most 256 columns
+        sch = spmm_schedule(crow, r0, r1, owner=A, variant=variant)
+    per_piece = H.shape[1] if variant == 2 else C.spmm_scratch_per_piece(H)
+    scratch = _scratch_floats(sch.num_pieces * per_piece, H.device) if sch.num_pieces else _EMPTY_F32(H.device)
+    tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0.0, 0, 0)
+    C.spmm_items(variant == 2, crow, col, val, H, out, relu_mask, r0, sch.items, sch.num_pieces,
+                 sch.long_piece_start, sch.long_counter, scratch, list(push_ptrs), int(push_ld), SPMM_MMA_STAGES,
+                 int(push_seg[0]), int(push_seg[1]), status_buffer(H.device), list(tr[0]), list(tr[1]),
+                 list(tr[2]), int(tr[3]), float(tr[4]), int(tr[5]), int(tr[6]))
+    _count(-(-H.shape[1] // 256) if variant == 2 else 1)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
     return out

@@ -173,7 +173,7 @@ def _in_kernel_ops(rank, world, long_row):
 
     fused.ONE_SHOT_MAX_RANKS = 8
     fused.SMALL_MESSAGE_BYTES = 0
-    opc.SPMM_MMA_LONG_ROW = long_row
+    opc.SPMM_LONG_ROW[1] = opc.SPMM_LONG_ROW[2] = long_row
     grid = plx.init(world, 1, 1, comm="fused")
     g = grid.group("x")
     ax = fused.symm.axis_for(g)
