@@ -44,23 +44,13 @@ plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t
   return p;
 }
 
-// In-kernel all-reduce description from Python lists of raw addresses (empty lists: off).
-plx::TileReduce make_tile_reduce(const std::vector<int64_t>& slots, const std::vector<int64_t>& remote_sig,
-                                 const std::vector<int64_t>& local_sig, int64_t base, int64_t me,
-                                 double timeout_ms, int64_t tile_rows = 0, int64_t local_done = 0) {
+// In-kernel all-reduce description: this rank's sentinel-kept receive slots (empty list: off).
+plx::TileReduce make_tile_reduce(const std::vector<int64_t>& slots, int64_t me, double timeout_ms) {
   plx::TileReduce r = {};
-  TORCH_CHECK(slots.size() == remote_sig.size() && slots.size() == local_sig.size() &&
-              slots.size() <= static_cast<size_t>(plx::MAX_PEERS), "bad in-kernel all-reduce description");
+  TORCH_CHECK(slots.size() <= static_cast<size_t>(plx::MAX_PEERS), "bad in-kernel all-reduce description");
   r.n = static_cast<int>(slots.size());
-  for (int i = 0; i < r.n; ++i) {
-    r.slot[i] = reinterpret_cast<const void*>(slots[i]);
-    r.remote_sig[i] = reinterpret_cast<int*>(remote_sig[i]);
-    r.local_sig[i] = reinterpret_cast<int*>(local_sig[i]);
-  }
-  r.base = static_cast<int>(base);
+  for (int i = 0; i < r.n; ++i) r.slot[i] = reinterpret_cast<void*>(slots[i]);
   r.me = static_cast<int>(me);
-  r.tile_rows = static_cast<int>(tile_rows);
-  r.local_done = reinterpret_cast<int*>(local_done);
   r.timeout_ns = static_cast<unsigned long long>(timeout_ms * 1e6);
   return r;
 }
@@ -102,9 +92,8 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
                 Tensor& out, const c10::optional<Tensor>& mask, int64_t row_begin, const Tensor& items,
                 int64_t num_pieces, const Tensor& long_piece_start, Tensor& long_counter, const Tensor& scratch,
                 const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t stages, int64_t push_seg_rows,
-                int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots,
-                const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
-                int64_t red_me, double red_timeout_ms, int64_t red_tile_rows, int64_t red_local_done) {
+                int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots, int64_t red_me,
+                double red_timeout_ms) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -140,8 +129,7 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
   plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
   TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
               "spmm: row segments do not cover the output");
-  plx::TileReduce red = make_tile_reduce(red_slots, red_remote_sig, red_local_sig, 0, red_me, red_timeout_ms,
-                                         red_tile_rows, red_local_done);
+  plx::TileReduce red = make_tile_reduce(red_slots, red_me, red_timeout_ms);
   red.status = status_ptr(status);
   c10::cuda::CUDAGuard guard(H.device());
   if (tensor_core) {
@@ -168,13 +156,12 @@ int64_t spmm_scratch_per_piece(const Tensor& H) {
 void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tensor& status,
              int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
              const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask,
-             int64_t push_seg_rows, int64_t push_me, const std::vector<int64_t>& red_slots,
-             const std::vector<int64_t>& red_remote_sig, const std::vector<int64_t>& red_local_sig,
-             int64_t red_base, int64_t red_me, double red_timeout_ms) {
+             int64_t push_seg_rows, int64_t push_me, const std::vector<int64_t>& red_slots, int64_t red_me,
+             double red_timeout_ms) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
-  plx::TileReduce red = make_tile_reduce(red_slots, red_remote_sig, red_local_sig, red_base, red_me, red_timeout_ms);
+  plx::TileReduce red = make_tile_reduce(red_slots, red_me, red_timeout_ms);
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
@@ -398,6 +385,24 @@ void gather_segments(const std::vector<int64_t>& src_ptrs, const std::vector<int
                                     stream()));
 }
 
+void reduce_sentinel(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t slot_ld, bool relu,
+                     const c10::optional<Tensor>& mask, double timeout_ms, int64_t kernel_id, const Tensor& status,
+                     int64_t me, int64_t max_blocks) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->scalar_type() == at::kBFloat16 && mask->sizes() == out.sizes() && mask->stride(1) == 1);
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  check(plx::launch_reduce_sentinel_bf16(out.data_ptr(), out.stride(0), make_slots(slot_ptrs, me), slot_ld,
+                                         out.size(0), static_cast<int>(out.size(1)), relu, mptr, ldm, timeout_ms,
+                                         static_cast<int>(kernel_id), status_ptr(status),
+                                         static_cast<int>(max_blocks), stream()));
+}
+
 void reduce_slots_f32(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t op,
                       const std::vector<int64_t>& remote_flags, const std::vector<int64_t>& local_flags,
                       int64_t epoch, double timeout_ms, int64_t kernel_id, const Tensor& status, int64_t me) {
@@ -441,8 +446,8 @@ int64_t symm_open(const std::string& handle) {
 
 void symm_close(int64_t ptr) { check(plx::symm_close(reinterpret_cast<void*>(ptr))); }
 void symm_free(int64_t ptr) { check(plx::symm_free(reinterpret_cast<void*>(ptr))); }
-void symm_clear(int64_t ptr, int64_t bytes) {
-  check(plx::symm_clear(reinterpret_cast<void*>(ptr), static_cast<size_t>(bytes)));
+void symm_fill(int64_t ptr, int64_t byte, int64_t bytes) {
+  check(plx::symm_fill(reinterpret_cast<void*>(ptr), static_cast<int>(byte), static_cast<size_t>(bytes)));
 }
 
 // ---- start-up kernels ---------------------------------------------------------------------
@@ -548,6 +553,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("csr_validate", &csr_validate);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_slots_f32", &reduce_slots_f32);
+  m.def("reduce_sentinel", &reduce_sentinel);
   m.def("reduce_segment", &reduce_segment);
   m.def("gather_segments", &gather_segments);
   m.def("push_copy", &push_copy);
@@ -556,5 +562,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_open", &symm_open);
   m.def("symm_close", &symm_close);
   m.def("symm_free", &symm_free);
-  m.def("symm_clear", &symm_clear);
+  m.def("symm_fill", &symm_fill);
 }

@@ -27,23 +27,19 @@ struct PushTargets {
 };
 
 // In-kernel all-reduce of a fused "compute + push" kernel (one-shot form): besides pushing its
-// partial result tiles into the peers' receive slots (PushTargets), the kernel reduces them itself.
-// Unit of exchange: a "tile" (GEMM: the 128-row tiles a CTA processes, in order; SpMM: fixed blocks
-// of consecutive output rows).  After storing a tile locally and into the peers' slots, the kernel
-// publishes it on every peer (release, system scope); it then waits (bounded) until the peers
-// published theirs, adds the received partials to its own in group-rank order, applies ReLU / the
-// mask and writes the final rows - no second launch.  Both ranks of a pair run the same grid, so
-// CTA c of one rank exchanges with CTA c of the other (GEMM) or tiles are tracked by row counters
-// (SpMM).  n == 0 switches it off.
+// partial result rows into the peers' receive slots (PushTargets), the kernel sums the partials it
+// receives itself - no second launch, no flags, no system-scope fences.  The receive slots used for
+// this hold a SENTINEL (every byte 0xFF, a bf16 NaN that no conversion from fp32 produces) wherever
+// nothing has arrived yet: a warp that has stored rows locally and into the peers' slots later
+// re-reads its own rows and the peers' partials of the same rows, treats a 16-byte vector as
+// arrived once none of its eight elements is the sentinel, adds the partials in group-rank order,
+// applies ReLU / the mask, writes the final rows and puts the sentinel back into the slot for the
+// next use of the buffer.  Waiting for a vector is bounded; a timeout is recorded in the status
+// words.  n == 0 switches it off.
 struct TileReduce {
-  int n;                               // peers
-  const void* slot[MAX_PEERS];         // this rank's receive slot of every peer (same layout as the push)
-  int* remote_sig[MAX_PEERS];          // this rank's signal array inside peer q's workspace (written here)
-  int* local_sig[MAX_PEERS];           // peer q's signal array inside this rank's workspace (polled here)
-  int base;                            // GEMM: tile k of a CTA publishes base + k + 1
-  int me;                              // position in the group (summation order)
-  int tile_rows;                       // SpMM: rows per exchange tile
-  int* local_done;                     // SpMM: rows of each tile this rank has finished (device-local)
+  int n;                        // peers
+  void* slot[MAX_PEERS];        // this rank's sentinel-kept receive slot of every peer (layout of the push)
+  int me;                       // position in the group (summation order)
   unsigned long long timeout_ns;
   int* status;
 };
@@ -83,8 +79,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
                            int* status, int max_stages, int ctas_limit, int nb_override,
                            const PushTargets* push, const void* mask, int64_t ldm, cudaStream_t stream,
                            const TileReduce* reduce = nullptr);
-// Largest number of CTAs launch_gemm_nt uses (size of the per-CTA signal arrays of TileReduce).
-constexpr int GEMM_MAX_CTAS = 256;
+
 // mask (same dtype and shape as C, may be null): C = result where mask > 0, else 0.
 // out[Mw,Nw] fp32 = A[R,Mw]^T . B[R,Nw]; scratch >= gemm_tn_parts(R)*Mw*Nw floats.
 int gemm_tn_parts(int64_t R);
@@ -157,6 +152,10 @@ struct PeerSync {
 const char* launch_reduce_slots_bf16(void* out, int64_t ldo, const SlotList& slots, int64_t lds,
                                      int64_t rows, int cols, bool relu, const void* mask, int64_t ldm,
                                      const PeerSync& sync, cudaStream_t stream);
+// Flag-free variant: the slots are sentinel-kept (see TileReduce); slots.me = position in the group.
+const char* launch_reduce_sentinel_bf16(void* out, int64_t ldo, const SlotList& slots, int64_t lds, int64_t rows,
+                                        int cols, bool relu, const void* mask, int64_t ldm, double timeout_ms,
+                                        int kernel_id, int* status, int max_blocks, cudaStream_t stream);
 const char* launch_reduce_slots_f32(float* out, const SlotList& slots, int64_t n, int op,
                                     const PeerSync& sync, cudaStream_t stream);
 const char* launch_push_copy(const void* src, const SlotList& dst, int64_t bytes, cudaStream_t stream);
@@ -181,7 +180,7 @@ const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 const char* symm_open(const unsigned char* handle64, void** ptr);
 const char* symm_close(void* ptr);
 const char* symm_free(void* ptr);
-const char* symm_clear(void* ptr, size_t bytes);  // zero the first `bytes` of a local workspace
+const char* symm_fill(void* ptr, int byte, size_t bytes);  // memset on a local workspace
 
 // ---- graph_prep.cu (start-up kernels)
 const char* launch_rmat_edges(int64_t num_nodes, int64_t first_edge, int64_t n, uint64_t seed, double a,

@@ -136,6 +136,93 @@ reduce_slots_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const Slo
   }
 }
 
+// Flag-free receive side of the one-shot all-reduce.  The peers' partials arrive in sentinel-kept
+// slots (every byte 0xFF where nothing has arrived; see TileReduce in plexus_kernels.h): a vector is
+// used once none of its eight bf16 elements is the sentinel, so the producers need neither flags
+// nor fences and this kernel may start while the peers are still sending.  The local partial is
+// already complete (the compute kernel that wrote it precedes this launch in stream order).
+//   out[r, c] = act( sum over the group, in group-rank order ), then the slots get the sentinel back.
+__device__ __forceinline__ bool has_sentinel(const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  bool s = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s = s || (w[i] & 0xffffu) == 0xffffu || (w[i] >> 16) == 0xffffu;
+  return s;
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+reduce_sentinel_bf16_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const SlotList slots, int64_t lds,
+                            int64_t rows, int cols, int relu, const __nv_bfloat16* __restrict__ mask, int64_t ldm,
+                            unsigned long long timeout_ns, int kernel_id, int* status) {
+  const int my_pos = slots.me;
+  const int vec_per_row = cols / 8;
+  const int64_t total = rows * vec_per_row;
+  const uint4 fill = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const uint4 own = *reinterpret_cast<const uint4*>(out + r * ldo + c);
+    uint4 pv[MAX_PEERS];
+    unsigned long long t0 = 0;
+    while (true) {
+      bool ready = true;
+#pragma unroll
+      for (int q = 0; q < MAX_PEERS; ++q)
+        if (q < slots.n) {
+          pv[q] = ld_cg_u4(static_cast<const __nv_bfloat16*>(slots.ptr[q]) + r * lds + c);
+          ready = ready && !has_sentinel(pv[q]);
+        }
+      if (ready) break;
+      if (t0 == 0) t0 = global_ns();
+      if (global_ns() - t0 > timeout_ns) {
+        report_status(status, ST_TIMEOUT, kernel_id, 40, static_cast<int>(r), c);
+        return;
+      }
+      __nanosleep(256);
+    }
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    if (my_pos <= 0) add_bf16x8(acc, own);
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q) {
+      if (q < slots.n) {
+        add_bf16x8(acc, pv[q]);
+        if (q + 1 == my_pos) add_bf16x8(acc, own);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(slots.ptr[q]) + r * lds + c) = fill;
+      }
+    }
+    if (relu) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = fmaxf(acc[k], 0.f);
+    }
+    if (mask != nullptr) {
+      const uint4 mv = *reinterpret_cast<const uint4*>(mask + r * ldm + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&mv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        if (!(f.x > 0.f)) acc[2 * k] = 0.f;
+        if (!(f.y > 0.f)) acc[2 * k + 1] = 0.f;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) po[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
+  }
+}
+
 // Two-shot all-reduce, middle step: reduce this rank's row segment and broadcast the result.
 //   out rows [row0, row0 + rows) += sum_q slot_q[0 .. rows)  (fp32), then ReLU / mask, then the
 //   reduced rows are written to `out` and to slot row (r - row0) of every destination in `bcast`.
@@ -277,6 +364,21 @@ const char* launch_reduce_slots_bf16(void* out, int64_t ldo, const SlotList& slo
   return last_launch_error();
 }
 
+const char* launch_reduce_sentinel_bf16(void* out, int64_t ldo, const SlotList& slots, int64_t lds, int64_t rows,
+                                        int cols, bool relu, const void* mask, int64_t ldm, double timeout_ms,
+                                        int kernel_id, int* status, int max_blocks, cudaStream_t stream) {
+  if (cols % 8 || ldo % 8 || lds % 8 || (mask && ldm % 8)) return "reduce_sentinel: widths must be multiples of 8";
+  if (slots.n < 1 || slots.n > MAX_PEERS) return "reduce_sentinel: bad number of peers";
+  if (rows <= 0) return nullptr;
+  int grid = copy_grid(rows * (cols / 8));
+  if (max_blocks > 0) grid = std::min(grid, max_blocks);
+  reduce_sentinel_bf16_kernel<<<grid, 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(out), ldo, slots, lds, rows, cols, relu ? 1 : 0,
+      static_cast<const __nv_bfloat16*>(mask), ldm, static_cast<unsigned long long>(timeout_ms * 1e6), kernel_id,
+      status);
+  return last_launch_error();
+}
+
 const char* launch_reduce_segment_bf16(void* out, int64_t ldo, int64_t row0, const SlotList& slots,
                                        int64_t lds, int64_t rows, int cols, bool relu, const void* mask,
                                        int64_t ldm, const SlotList& bcast, const PeerSync& sync,
@@ -381,8 +483,8 @@ const char* symm_close(void* ptr) {
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
-const char* symm_clear(void* ptr, size_t bytes) {
-  cudaError_t e = cudaMemset(ptr, 0, bytes);
+const char* symm_fill(void* ptr, int byte, size_t bytes) {
+  cudaError_t e = cudaMemset(ptr, byte, bytes);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

@@ -30,6 +30,7 @@
 
 #include "../include/plexus_kernels.h"
 #include "../include/ptx_sm100.cuh"
+#include "../include/sentinel_reduce.cuh"
 
 namespace plx {
 
@@ -49,10 +50,8 @@ struct alignas(8) GemmBarriers {
   uint64_t tempty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int seen;        // epilogue: number of this CTA's tiles every peer has published (broadcast slot)
-  int sig_idle;    // the signalling warp is waiting at its barrier
-  int sig_count;   // tiles stored so far, handed to the signalling warp (-1: leave)
-  int do_sig;      // epilogue broadcast slot: hand over at this tile
+  int stored[4];  // in-kernel all-reduce: tiles each epilogue warp has stored (read by its reducer warp)
+  int pad[2];
 };
 
 // Epilogue staging: every epilogue warp owns 32 rows; a segment of SEG_BYTES per row goes
@@ -122,103 +121,13 @@ __device__ __forceinline__ void apply_relu_mask<float>(uint4& v, const uint4& m)
     if (!(mf[i] > 0.f)) vw[i] = 0u;
 }
 
-// ----- in-kernel all-reduce of finished tiles (see TileReduce)
-__device__ __forceinline__ unsigned long long gemm_global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// hand-over from the four epilogue warps (arrive, not blocking) to the signalling warp (sync)
-__device__ __forceinline__ void sig_bar_arrive() { asm volatile("bar.arrive 2, 160;" ::: "memory"); }
-__device__ __forceinline__ void sig_bar_sync() { asm volatile("bar.sync 2, 160;" ::: "memory"); }
-__device__ __forceinline__ uint4 ld_cg16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 f = __bfloat1622float2(p[k]);
-    acc[2 * k] += f.x;
-    acc[2 * k + 1] += f.y;
-  }
-}
-
-// Peers' progress: the smallest number of tiles of CTA `cta` that every peer has published.
-__device__ __forceinline__ int peers_published(const TileReduce& red, int cta) {
-  int m = 0x7fffffff;
-  for (int q = 0; q < red.n; ++q) {
-    int seen;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(red.local_sig[q] + cta) : "memory");
-    m = min(m, seen - red.base);
-  }
-  return m;
-}
-
-// The four epilogue warps (128 threads, `tid` 0..127) finish rows [r0, r0 + nrows) x columns
-// [n0, n0 + ncols) of a tile whose partials have arrived from every peer:
-// C = act(sum over the group of the partials), summed in group-rank order.
-__device__ __forceinline__ void reduce_tile_bf16(__nv_bfloat16* __restrict__ C, int ldc, int r0, int nrows, int n0,
-                                                 int ncols, const TileReduce& red, int64_t slot_ld, int relu,
-                                                 const __nv_bfloat16* __restrict__ mask, int ldm, int tid) {
-  const int vpr = ncols >> 3;
-  const int total = nrows * vpr;
-  constexpr int UN = 4;
-  for (int v0 = tid; v0 < total; v0 += 128 * UN) {
-    int64_t off_c[UN], off_s[UN], off_m[UN];
-    bool live[UN];
-    uint4 own[UN];
-    float acc[UN][8];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int v = v0 + u * 128;
-      live[u] = v < total;
-      const int r = live[u] ? v / vpr : 0, c = live[u] ? (v - r * vpr) * 8 : 0;
-      off_c[u] = static_cast<int64_t>(r0 + r) * ldc + n0 + c;
-      off_s[u] = static_cast<int64_t>(r0 + r) * slot_ld + n0 + c;
-      off_m[u] = static_cast<int64_t>(r0 + r) * ldm + n0 + c;
-      own[u] = ld_cg16(C + off_c[u]);  // row 0 of the tile when not live: a valid address, value unused
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
-      if (red.me <= 0) acc_bf16x8(acc[u], own[u]);
-    }
-    // one peer at a time, UN independent loads in flight; the local partial enters at position `me`
-    for (int q = 0; q < red.n; ++q) {
-      const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(red.slot[q]);
-      uint4 pv[UN];
-#pragma unroll
-      for (int u = 0; u < UN; ++u) pv[u] = ld_cg16(sp + off_s[u]);
-#pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        acc_bf16x8(acc[u], pv[u]);
-        if (q + 1 == red.me) acc_bf16x8(acc[u], own[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      if (!live[u]) continue;
-      if (relu) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc[u][k] = fmaxf(acc[u][k], 0.f);
-      }
-      uint4 o;
-      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) po[k] = __floats2bfloat162_rn(acc[u][2 * k], acc[u][2 * k + 1]);
-      if (mask != nullptr) apply_relu_mask<__nv_bfloat16>(o, ld_cg16(mask + off_m[u]));
-      *reinterpret_cast<uint4*>(C + off_c[u]) = o;
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------------
 // C[M,N] = A[M,K] . B[N,K]^T   (persistent over 128-row tiles; blockIdx.y = block of bn_box columns)
 // ---------------------------------------------------------------------------------------
-template <typename OutT>
-__global__ void __launch_bounds__(GEMM_THREADS + 32, 1)
+// FUSED: with the in-kernel all-reduce (bf16 result, four more warps); a separate instantiation so
+// that the plain kernel keeps its register budget.
+template <typename OutT, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? GEMM_THREADS + 128 : GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT* __restrict__ C, int ldc, int M, int N, int K, int bn_box, int stages,
                int b_resident, int relu, int* status, const PushTargets push,
@@ -253,10 +162,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&bars->tempty[b], 4);
     }
     bars->abort_flag = 0;
-    bars->seen = 0;
-    bars->sig_idle = 1;
-    bars->sig_count = 0;
-    bars->do_sig = 0;
+    bars->stored[0] = bars->stored[1] = bars->stored[2] = bars->stored[3] = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -352,12 +258,9 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant owned by this warp
     // with the in-kernel all-reduce the activation and the mask are applied after the sum
-    const bool fuse_reduce = red.n > 0;
+    constexpr bool fuse_reduce = FUSED;
     const OutT* mask = fuse_reduce ? nullptr : mask_in;
     if (fuse_reduce) relu = 0;
-    const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
-    const int epi_tid = (warp - 2) * 32 + lane;
-    int reduced = 0;  // tiles of this CTA already summed over the group
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
@@ -476,106 +379,54 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         __syncwarp();
       }
-      if constexpr (sizeof(OutT) == 2) {
-        if (fuse_reduce) {
-          // The tile is stored, locally and in the peers' slots.  If the signalling warp is free, hand
-          // it the tile count: it publishes the CTA's progress on the peers (one system-scope fence
-          // covers every tile stored so far) without holding the epilogue up.  Then finish whatever
-          // tiles have arrived from the peers in the meantime.
-          epi_bar_sync();
-          if (epi_tid == 0) {
-            const int idle = *reinterpret_cast<volatile int*>(&bars->sig_idle);
-            bars->do_sig = idle;
-            if (idle) {
-              bars->sig_count = static_cast<int>(t) + 1;
-              bars->sig_idle = 0;
-            }
-            bars->seen = peers_published(red, cta_id);
-          }
-          epi_bar_sync();
-          if (bars->do_sig) sig_bar_arrive();
-          const int upto = min(bars->seen, static_cast<int>(t) + 1);
-          for (; reduced < upto; ++reduced) {
-            const int rt = blockIdx.x + reduced * gridDim.x;
-            reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, rt * BM, min(BM, M - rt * BM), n0, n_valid,
-                             red, push.ld, relu_in, reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid);
-          }
-        }
-      }
-    }
-    if constexpr (sizeof(OutT) == 2) {
-      if (fuse_reduce) {
-        // all tiles computed (or given up): the last hand-over carries the final count, or -1
-        const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                             static_cast<int>(gridDim.x);
-        const bool complete = !*abort_flag && static_cast<int>(t) == my_tiles;
-        epi_bar_sync();
-        if (epi_tid == 0) {
-          // if the last hand-over already carried the final count, the signalling warp leaves by itself
-          const int final_sent = bars->sig_count == my_tiles;
-          bars->do_sig = !final_sent;
-          if (!final_sent) {
-            const unsigned long long t0 = gemm_global_ns();
-            while (*reinterpret_cast<volatile int*>(&bars->sig_idle) == 0 && gemm_global_ns() - t0 < 8 * red.timeout_ns)
-              __nanosleep(100);
-            bars->sig_count = complete ? my_tiles : -1;
-            bars->sig_idle = 0;
-          }
-        }
-        epi_bar_sync();
-        if (bars->do_sig) sig_bar_arrive();
-        // wait (bounded) for the peers' remaining tiles and finish them
-        const unsigned long long t0 = gemm_global_ns();
-        while (complete && reduced < my_tiles) {
-          epi_bar_sync();
-          if (epi_tid == 0) {
-            int m = peers_published(red, cta_id);
-            if (m <= reduced && gemm_global_ns() - t0 > red.timeout_ns) {
-              report_status(red.status, ST_TIMEOUT, KERNEL_ID_GEMM, 20, reduced, m);
-              m = -1;
-            }
-            bars->seen = m;
-          }
-          epi_bar_sync();
-          const int got = bars->seen;
-          if (got < 0) {
-            *abort_flag = 1;
-            break;
-          }
-          if (got <= reduced) __nanosleep(200);
-          for (const int upto = min(got, my_tiles); reduced < upto; ++reduced) {
-            const int rt = blockIdx.x + reduced * gridDim.x;
-            reduce_tile_bf16(reinterpret_cast<__nv_bfloat16*>(C), ldc, rt * BM, min(BM, M - rt * BM), n0, n_valid,
-                             red, push.ld, relu_in, reinterpret_cast<const __nv_bfloat16*>(mask_in), ldm, epi_tid);
-          }
-        }
-      }
-    }
-  } else if (warp == 6) {
-    // ---------------------------------------------------- signalling warp (in-kernel all-reduce only)
-    // Woken through a named barrier by the epilogue warps after they stored a tile; the barrier makes
-    // their stores (local and remote) precede the fence below.  The fence waits for the NVLink
-    // stores to drain, tens of microseconds under load: here that is off the epilogue's critical
-    // path, and one fence covers every tile stored so far.
-    if (red.n > 0) {
-      const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
-      const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                           static_cast<int>(gridDim.x);
-      while (true) {
-        sig_bar_sync();
-        const int cnt = *reinterpret_cast<volatile int*>(&bars->sig_count);
-        if (cnt < 0) break;
-        if (lane == 0) {
-          __threadfence_system();
-          for (int p = 0; p < red.n; ++p)
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(red.remote_sig[p] + cta_id), "r"(red.base + cnt)
+      if constexpr (FUSED) {
+        {
+          // this warp's 32 rows of the tile are stored, locally and in the peers' slots: tell the
+          // reducer warp of this row quadrant
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(&bars->stored[q])),
+                         "r"(static_cast<int>(t) + 1)
                          : "memory");
         }
-        __syncwarp();
-        if (cnt >= my_tiles) break;  // sig_idle stays 0: nobody hands over again
-        if (lane == 0) {
-          __threadfence_block();
-          *reinterpret_cast<volatile int*>(&bars->sig_idle) = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------ reducer warps (in-kernel all-reduce only)
+    // Warp 6 + q finishes the rows of quadrant q: as soon as epilogue warp q has stored a tile it
+    // re-reads those rows together with the peers' partials of the same rows (valid once they no
+    // longer hold the sentinel), sums in group-rank order, applies ReLU / the mask and writes the
+    // final rows.  Waiting for the peers happens here, off the path of the MMAs and the pushes.
+    if constexpr (FUSED) {
+      const int q = warp - 6;
+      const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                           static_cast<int>(gridDim.x);
+      const int relu_after = relu;
+      for (int k = 0; k < my_tiles && red.n > 0; ++k) {
+        const unsigned long long t0 = sentinel::global_ns();
+        bool have = false;
+        while (!have && !*abort_flag) {
+          int v;
+          asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(&bars->stored[q])) : "memory");
+          have = v > k;
+          if (!have) {
+            if (sentinel::global_ns() - t0 > 4 * red.timeout_ns) break;  // the producers report their own timeouts
+            __nanosleep(64);
+          }
+        }
+        have = __all_sync(0xffffffffu, have);
+        if (!have) break;
+        const int r0 = (static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x)) * BM + q * 32;
+        const int nrows = min(32, M - r0);
+        if (nrows <= 0) continue;
+        const int done = sentinel::reduce_rows<8>(
+            reinterpret_cast<__nv_bfloat16*>(C) + static_cast<int64_t>(r0) * ldc + n0, ldc,
+            static_cast<int64_t>(r0) * push.ld + n0, push.ld, nrows, n_valid, 0, red, relu_after,
+            mask_in ? reinterpret_cast<const __nv_bfloat16*>(mask_in) + static_cast<int64_t>(r0) * ldm + n0 : nullptr,
+            ldm, lane, true, KERNEL_ID_GEMM);
+        if (done < 0) {
+          *abort_flag = 1;
+          break;
         }
       }
     }
@@ -814,8 +665,7 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
       return "gemm_nt: the in-kernel all-reduce goes with the broadcast push to the same peers";
     if (red.n > MAX_PEERS) return "gemm_nt: too many peers";
     for (int q = 0; q < red.n; ++q)
-      if (red.slot[q] == nullptr || red.remote_sig[q] == nullptr || red.local_sig[q] == nullptr ||
-          reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
+      if (red.slot[q] == nullptr || reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
         return "gemm_nt: bad in-kernel all-reduce description";
     red.status = status;
   }
@@ -865,19 +715,29 @@ const char* launch_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ld
   const int tiles = static_cast<int>((M + BM - 1) / BM);
   const int n_blocks = static_cast<int>((N + bn_box - 1) / bn_box);
   const int ctas = std::min(tiles, ctas_limit > 0 ? ctas_limit : std::max(1, num_sms() / n_blocks));
-  if (red.n > 0 && ctas * n_blocks > GEMM_MAX_CTAS) return "gemm_nt: too many CTAs for the signal arrays";
   dim3 grid(ctas, static_cast<unsigned>(n_blocks));
   if (c_dtype == DT_BF16) {
-    auto kern = gemm_nt_kernel<__nv_bfloat16>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<grid, red.n > 0 ? GEMM_THREADS + 32 : GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
-                                               static_cast<int>(ldc), static_cast<int>(M),
-                                               static_cast<int>(N), static_cast<int>(K), bn_box, stages,
-                                               b_resident, relu ? 1 : 0, status, push,
-                                               reinterpret_cast<const __nv_bfloat16*>(mask),
-                                               static_cast<int>(ldm), red);
+    if (red.n > 0) {
+      auto kern = gemm_nt_kernel<__nv_bfloat16, true>;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, GEMM_THREADS + 128, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
+                                                       static_cast<int>(ldc), static_cast<int>(M),
+                                                       static_cast<int>(N), static_cast<int>(K), bn_box, stages,
+                                                       b_resident, relu ? 1 : 0, status, push,
+                                                       reinterpret_cast<const __nv_bfloat16*>(mask),
+                                                       static_cast<int>(ldm), red);
+    } else {
+      auto kern = gemm_nt_kernel<__nv_bfloat16, false>;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C),
+                                                 static_cast<int>(ldc), static_cast<int>(M),
+                                                 static_cast<int>(N), static_cast<int>(K), bn_box, stages,
+                                                 b_resident, relu ? 1 : 0, status, push,
+                                                 reinterpret_cast<const __nv_bfloat16*>(mask),
+                                                 static_cast<int>(ldm), red);
+    }
   } else if (c_dtype == DT_F32) {
-    auto kern = gemm_nt_kernel<float>;
+    auto kern = gemm_nt_kernel<float, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, reinterpret_cast<float*>(C),
                                                static_cast<int>(ldc), static_cast<int>(M),

@@ -422,11 +422,9 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
     if (dtype != DT_BF16) return "spmm: the in-kernel all-reduce needs bf16 features";
     if (push_in == nullptr || push_in->n != red.n || push_in->seg_rows != 0)
       return "spmm: the in-kernel all-reduce goes with the broadcast push to the same peers";
-    if (red.tile_rows <= 0 || red.local_done == nullptr || out_rows <= 0 || D % 8)
-      return "spmm: bad in-kernel all-reduce description";
+    if (D % 8) return "spmm: bad in-kernel all-reduce description";
     for (int q = 0; q < red.n; ++q)
-      if (red.slot[q] == nullptr || red.remote_sig[q] == nullptr || red.local_sig[q] == nullptr ||
-          reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
+      if (red.slot[q] == nullptr || reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
         return "spmm: bad in-kernel all-reduce description";
   }
   if ((ldh * esz) % 16 || (ldo * esz) % 16 || (D * esz) % 16 || (mask && (ldm * esz) % 16))

@@ -481,12 +481,9 @@ const char* launch_spmm_mma(const int* rowptr, const int* col, const float* val,
     red.status = status;
     if (push_in == nullptr || push_in->n != red.n || push_in->seg_rows != 0)
       return "spmm_mma: the in-kernel all-reduce goes with the broadcast push to the same peers";
-    if (red.tile_rows <= 0 || red.local_done == nullptr || out_rows <= 0)
-      return "spmm_mma: bad in-kernel all-reduce description";
     if (D > 256) return "spmm_mma: the in-kernel all-reduce handles at most 256 columns";
     for (int q = 0; q < red.n; ++q)
-      if (red.slot[q] == nullptr || red.remote_sig[q] == nullptr || red.local_sig[q] == nullptr ||
-          reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
+      if (red.slot[q] == nullptr || reinterpret_cast<uintptr_t>(red.slot[q]) % 16)
         return "spmm_mma: bad in-kernel all-reduce description";
   }
   PushTargets push = {};

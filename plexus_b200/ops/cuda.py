@@ -196,9 +196,9 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     ``push_seg = (rows per owner, this rank's position)``: reduce-scatter push (each row goes only
     to the rank that owns it) instead of the broadcast push.
     ``variant``: see ``SPMM_VARIANT``.
-    ``tile_reduce = (slots, remote_sig, local_sig, me, timeout_ms, tile_rows, local_done_ptr)``:
-    finish the all-reduce over the push peers inside the kernel (the mask is applied after the
-    sum); see :func:`spmm_supports_tile_reduce`."""
+    ``tile_reduce = (sentinel slots, me, timeout_ms)`` (``AxisComm.tile_reduce``): finish the
+    all-reduce over the push peers inside the kernel (the mask is applied after the sum); the push
+    must then go to the peers' sentinel slots.  See :func:`spmm_supports_tile_reduce`."""
     C = _ext.load()
     crow, col, val = _csr_parts(A)
     r0, r1 = row_range if row_range is not None else (0, A.shape[0])
@@ -231,11 +231,11 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
         sch = spmm_schedule(crow, r0, r1, owner=A, variant=variant)
     per_piece = H.shape[1] if variant == 2 else C.spmm_scratch_per_piece(H)
     scratch = _scratch_floats(sch.num_pieces * per_piece, H.device) if sch.num_pieces else _EMPTY_F32(H.device)
-    tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0.0, 0, 0)
+    tr = tile_reduce if tile_reduce is not None else ([], 0, 0.0)
     C.spmm_items(variant == 2, crow, col, val, H, out, relu_mask, r0, sch.items, sch.num_pieces,
                  sch.long_piece_start, sch.long_counter, scratch, list(push_ptrs), int(push_ld), SPMM_MMA_STAGES,
-                 int(push_seg[0]), int(push_seg[1]), status_buffer(H.device), list(tr[0]), list(tr[1]),
-                 list(tr[2]), int(tr[3]), float(tr[4]), int(tr[5]), int(tr[6]))
+                 int(push_seg[0]), int(push_seg[1]), status_buffer(H.device), list(tr[0]), int(tr[1]),
+                 float(tr[2]))
     _count(-(-H.shape[1] // 256) if variant == 2 else 1)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
@@ -261,8 +261,8 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
     ``push_ptrs`` / ``push_seg``: fused-collective epilogue, see :func:`spmm`.
     ``out``: optional destination of ``op(a) @ op(b)`` for the non-transposed-``a`` forms (rows
     contiguous, e.g. a row block of a larger matrix).
-    ``tile_reduce = (slots, remote_sig, local_sig, base, me, timeout_ms)``: finish the all-reduce
-    over the push peers inside the kernel (ReLU / mask applied after the sum)."""
+    ``tile_reduce = (sentinel slots, me, timeout_ms)`` (``AxisComm.tile_reduce``): finish the
+    all-reduce over the push peers inside the kernel (ReLU / mask applied after the sum)."""
     C = _ext.load()
     st = status_buffer(a.device)
     max_stages, ctas, nb = GEMM_VARIANTS[variant]
@@ -301,10 +301,9 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         raise ValueError("gemm: out has the wrong shape or layout")
     if relu_mask is not None and relu_mask.dtype != out.dtype:
         relu_mask = relu_mask.to(out.dtype)
-    tr = tile_reduce if tile_reduce is not None else ([], [], [], 0, 0, 0.0)
+    tr = tile_reduce if tile_reduce is not None else ([], 0, 0.0)
     C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask,
-              int(push_seg[0]), int(push_seg[1]), list(tr[0]), list(tr[1]), list(tr[2]), int(tr[3]), int(tr[4]),
-              float(tr[5]))
+              int(push_seg[0]), int(push_seg[1]), list(tr[0]), int(tr[1]), float(tr[2]))
     _count(1)
     return out
 

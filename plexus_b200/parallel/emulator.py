@@ -73,8 +73,8 @@ class _Kernels:
     def symm_close(self, addr: int) -> None:
         self._segments.pop(addr).close()
 
-    def symm_clear(self, addr: int, nbytes: int) -> None:
-        ctypes.memset(addr, 0, int(nbytes))
+    def symm_fill(self, addr: int, byte: int, nbytes: int) -> None:
+        ctypes.memset(addr, int(byte), int(nbytes))
 
     def symm_free(self, addr: int) -> None:
         shm = self._segments.pop(addr)
@@ -129,6 +129,27 @@ class _Kernels:
         if mask is not None:
             acc = acc * (mask > 0)
         out.copy_(acc.to(out.dtype))
+
+    def reduce_sentinel(self, out, slot_ptrs, slot_ld, relu, mask, timeout_ms, kid, status, me=-1, max_blocks=0):
+        """Flag-free receive side: the slots hold 0xFF bytes where nothing has arrived; wait (bounded)
+        until no element is the sentinel, sum in group-rank order, put the sentinel back."""
+        rows, cols = out.shape
+        esz = out.element_size()
+        acc_dtype = torch.float64 if out.dtype == torch.float64 else torch.float32
+        deadline = time.time() + timeout_ms / 1e3
+        views = []
+        for q, a in enumerate(slot_ptrs):
+            raw = _view(a, rows * slot_ld * esz, torch.uint8).view(rows, slot_ld, esz)[:, :cols]
+            while bool((raw == 0xFF).all(dim=2).any()):
+                if time.time() > deadline:
+                    if int(status[0]) == 0:
+                        status[:5] = torch.tensor([1, kid, 40 + q, 0, 0], dtype=torch.int32)
+                    return
+                time.sleep(0.0002)
+            views.append(_view(a, rows * slot_ld, out.dtype).view(rows, slot_ld)[:, :cols])
+        self._finish(out, self._ordered_sum(out, views, me, acc_dtype), relu, mask)
+        for a in slot_ptrs:
+            _view(a, rows * slot_ld * esz, torch.uint8).view(rows, slot_ld * esz)[:, : cols * esz].fill_(0xFF)
 
     def reduce_slots_f32(self, out, slot_ptrs, op, remote, local, epoch, timeout_ms, kid, status, me=-1):
         if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
@@ -220,38 +241,33 @@ class _Ops:
             res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
         if fused:
-            self._tile_reduce_rows(res, tile_reduce, push_ld, relu_mask)
+            self._sentinel_reduce(res, tile_reduce, push_ld, False, relu_mask)
         self._count(1)
         return res
 
-    def _tile_reduce_rows(self, res, tile_reduce, slot_ld, mask):
-        """The SpMM's in-kernel all-reduce: per exchange tile, add the rows pushed to the peers'
-        counters, wait (bounded) for the peers' counts, sum in group-rank order, clear the counters."""
-        slots, remote_sig, local_sig, me, timeout_ms, tile_rows, _local_done = tile_reduce
+    def _sentinel_reduce(self, res, tile_reduce, slot_ld, relu, mask):
+        """The in-kernel all-reduce: the peers' partials sit in sentinel-kept slots (every byte 0xFF
+        where nothing has arrived).  Wait (bounded) until no element of a slot is the sentinel, sum
+        in group-rank order, apply ReLU / the mask, and put the sentinel back."""
+        slots, me, timeout_ms = tile_reduce
         rows, cols = res.shape
+        esz = res.element_size()
         acc_dtype = torch.float64 if res.dtype == torch.float64 else torch.float32
-        tiles = [(t0, min(tile_rows, rows - t0)) for t0 in range(0, rows, tile_rows)]
-        for T, (t0, n) in enumerate(tiles):
-            for a in remote_sig:
-                c = ctypes.c_int32.from_address(a + 4 * T)
-                c.value = c.value + n  # the only writer of this counter during the op
         deadline = time.time() + timeout_ms / 1e3
-        for T, (t0, n) in enumerate(tiles):
-            for q, a in enumerate(local_sig):
-                c = ctypes.c_int32.from_address(a + 4 * T)
-                while c.value < n:
-                    if time.time() > deadline:
-                        st = self.status_buffer()
-                        if int(st[0]) == 0:
-                            st[:5] = torch.tensor([1, 7, 20 + q, n, c.value], dtype=torch.int32)
-                        return
-                    time.sleep(0.0002)
-            seg = res[t0 : t0 + n]
-            others = [_view(a, rows * slot_ld, res.dtype).view(rows, slot_ld)[t0 : t0 + n, :cols] for a in slots]
-            _Kernels._finish(seg, _Kernels._ordered_sum(seg, others, me, acc_dtype), False,
-                             None if mask is None else mask[t0 : t0 + n])
-            for a in local_sig:
-                ctypes.c_int32.from_address(a + 4 * T).value = 0
+        views = []
+        for q, a in enumerate(slots):
+            raw = _view(a, rows * slot_ld * esz, torch.uint8).view(rows, slot_ld, esz)[:, :cols]
+            while bool((raw == 0xFF).all(dim=2).any()):
+                if time.time() > deadline:
+                    st = self.status_buffer()
+                    if int(st[0]) == 0:
+                        st[:5] = torch.tensor([1, 6, 30 + q, 0, 0], dtype=torch.int32)
+                    return
+                time.sleep(0.0002)
+            views.append(_view(a, rows * slot_ld, res.dtype).view(rows, slot_ld)[:, :cols])
+        _Kernels._finish(res, _Kernels._ordered_sum(res, views, me, acc_dtype), relu, mask)
+        for a in slots:
+            _view(a, rows * slot_ld * esz, torch.uint8).view(rows, slot_ld * esz)[:, : cols * esz].fill_(0xFF)
 
     def gemm(self, a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant=0, push_ptrs=(),
              push_ld=0, relu_mask=None, push_seg=(0, 0), out=None, tile_reduce=None):
@@ -268,30 +284,9 @@ class _Ops:
             res = out
         self._push(res, list(push_ptrs), push_ld, push_seg)
         if fused:
-            self._tile_reduce(res, tile_reduce, push_ld, relu, relu_mask, signal_index=0)
+            self._sentinel_reduce(res, tile_reduce, push_ld, relu, relu_mask)
         self._count(1)
         return res
-
-    def _tile_reduce(self, res, tile_reduce, slot_ld, relu, mask, signal_index):
-        """The in-kernel all-reduce with the whole matrix as one tile: publish one signal per peer
-        (value ``base + 1``), wait for the peers' signals (bounded), sum in group-rank order."""
-        slots, remote_sig, local_sig, base, me, timeout_ms = tile_reduce[:6]
-        for a in remote_sig:
-            ctypes.c_int32.from_address(a + 4 * signal_index).value = int(base) + 1
-        deadline = time.time() + timeout_ms / 1e3
-        for q, a in enumerate(local_sig):
-            flag = ctypes.c_int32.from_address(a + 4 * signal_index)
-            while flag.value - (int(base) + 1) < 0:
-                if time.time() > deadline:
-                    st = self.status_buffer()
-                    if int(st[0]) == 0:
-                        st[:5] = torch.tensor([1, 6, 20 + q, int(base) + 1, flag.value], dtype=torch.int32)
-                    return
-                time.sleep(0.0002)
-        rows, cols = res.shape
-        acc_dtype = torch.float64 if res.dtype == torch.float64 else torch.float32
-        others = [_view(a, rows * slot_ld, res.dtype).view(rows, slot_ld)[:, :cols] for a in slots]
-        _Kernels._finish(res, _Kernels._ordered_sum(res, others, me, acc_dtype), relu, mask)
 
     def relu_backward(self, grad, out):
         from ..ops import reference

@@ -63,8 +63,21 @@ TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"
 # receive slots (2 buffers x p slots per axis) stay bounded however large the activations are
 # (a 55M x 86 bf16 matrix is 9.5 GB; unblocked its slots alone would take 38 GB per axis).
 MAX_MESSAGE_BYTES = int(os.environ.get("PLEXUS_MAX_MESSAGE_BYTES", str(2 << 30)))
-# finish one-shot all-reduces inside the compute kernel (tile by tile, no separate reduce launch)
-IN_KERNEL_REDUCE = os.environ.get("PLEXUS_IN_KERNEL_REDUCE", "1") != "0"
+# Three receive sides exist for the one-shot all-reduce of a matrix (SpMM / GEMM epilogue pushes):
+#   flagged (default): one reduce launch after the compute kernel, released by the peers' flags;
+#   pipelined (PLEXUS_PIPELINE=1): no flags - the partials are pushed into sentinel-kept slots and
+#       a reduce kernel recognises arrived data by itself; the matrix is cut in row chunks and the
+#       reduce of chunk i runs on a side stream while chunk i + 1 is computed and pushed;
+#   in-kernel (PLEXUS_IN_KERNEL_REDUCE=1): the compute kernel itself sums the sentinel-kept slots.
+# Measured on 2 B200 (1M x 256 bf16, ms, SpMM+AR / GEMM+AR): flagged 1.81 / 1.10, pipelined
+# 2.17 / 1.22, in-kernel 2.97 / 3.02 - the reduce is a pure streaming pass that needs a full grid of
+# threads to run at HBM speed; inside the compute kernels it is starved of threads, and on a side
+# stream its polling CTAs take SM slots from the compute kernel.  The flagged form stays the default.
+PIPELINE = os.environ.get("PLEXUS_PIPELINE", "0") != "0"
+PIPELINE_CHUNKS = int(os.environ.get("PLEXUS_PIPELINE_CHUNKS", "4"))
+PIPELINE_MIN_BYTES = int(os.environ.get("PLEXUS_PIPELINE_MIN_BYTES", str(16 << 20)))
+REDUCE_MAX_BLOCKS = int(os.environ.get("PLEXUS_REDUCE_MAX_BLOCKS", str(148 * 4)))
+IN_KERNEL_REDUCE = os.environ.get("PLEXUS_IN_KERNEL_REDUCE", "0") != "0"
 ROW_BLOCK_MULTIPLE = 128  # row blocks start on a GEMM tile boundary
 
 
@@ -80,7 +93,8 @@ def _row_blocks(rows: int, row_bytes: int):
 
 
 # how often each form carried a matrix collective (for tests and the metrics sink)
-op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0, "in_kernel": 0}
+op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0, "in_kernel": 0,
+             "pipelined": 0}
 
 
 def _skip() -> bool:
@@ -135,6 +149,48 @@ def _two_shot_finish(ax, out, seg, ranges, epoch, buf, relu, mask, kid):
     opc._count(2)
 
 
+def _pipeline_chunks(rows: int, row_bytes: int):
+    """Row ranges of the pipelined one-shot form (multiples of 128 rows)."""
+    if PIPELINE_CHUNKS <= 1 or rows * row_bytes < PIPELINE_MIN_BYTES:
+        return [(0, rows)]
+    step = -(-(-(-rows // PIPELINE_CHUNKS)) // 128) * 128
+    return [(r, min(rows, r + step)) for r in range(0, rows, step)]
+
+
+class _SideStream:
+    """The axis' side stream for the overlapped reduces (a no-op on the host emulation)."""
+
+    def __init__(self, ax):
+        self.on = not emulator.active()
+        if self.on:
+            if getattr(ax, "_side_stream", None) is None:
+                ax._side_stream = torch.cuda.Stream()
+            self.side = ax._side_stream
+            self.main = torch.cuda.current_stream()
+
+    def run(self, fn):
+        """``fn`` after everything issued so far on the main stream, on the side stream."""
+        if not self.on:
+            return fn()
+        self.side.wait_stream(self.main)
+        with torch.cuda.stream(self.side):
+            return fn()
+
+    def join(self):
+        if self.on:
+            self.main.wait_stream(self.side)
+
+
+def _reduce_sentinel(ax, out, slots, slot_ld, relu, mask, kid):
+    _Backend.load().reduce_sentinel(out, slots, slot_ld, bool(relu), mask, ax.timeout_ms, kid,
+                                    opc.status_buffer(out.device), ax.rank, REDUCE_MAX_BLOCKS)
+    opc._count(1)
+
+
+def _sentinel_ok(dtype, cols: int) -> bool:
+    return emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+
+
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
     remote, local = ax.sync(buf)
     _Backend.load().reduce_slots(out, ax.recv_slots(buf), out.stride(0), bool(relu), mask, remote, local,
@@ -164,12 +220,29 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     if relu_mask is not None and relu_mask.dtype != H.dtype:
         relu_mask = relu_mask.to(H.dtype)
     in_kernel = IN_KERNEL_REDUCE and opc.spmm_supports_tile_reduce(A, H)
+    if PIPELINE and not in_kernel and len(blocks) == 1 and _sentinel_ok(H.dtype, D):
+        esz = H.element_size()
+        ax.ensure(sentinel_bytes=rows * D * esz)
+        _epoch, buf = ax.next_op()
+        out = torch.empty((rows, D), dtype=H.dtype, device=H.device)
+        targets, slots = ax.spush_targets(buf), ax.tile_reduce(buf)[0]
+        side = _SideStream(ax)
+        for r0, r1 in _pipeline_chunks(rows, D * esz):
+            off = r0 * D * esz
+            opc.spmm(A, H, row_range=(r0, r1), out=out[r0:r1], push_ptrs=[t + off for t in targets], push_ld=D)
+            side.run(lambda: _reduce_sentinel(ax, out[r0:r1], [p + off for p in slots], D, False,
+                                              None if relu_mask is None else relu_mask[r0:r1], KID_SPMM))
+        side.join()
+        op_counts["one_shot"] += 1
+        op_counts["pipelined"] += 1
+        return out
     if len(blocks) == 1:
-        ax.ensure(rows * D * H.element_size())
+        nbytes = rows * D * H.element_size()
+        ax.ensure(sentinel_bytes=nbytes) if in_kernel else ax.ensure(nbytes)
         epoch, buf = ax.next_op()
         if in_kernel:
-            out = opc.spmm(A, H, relu_mask=relu_mask, push_ptrs=ax.push_targets(buf), push_ld=D,
-                           tile_reduce=ax.tile_reduce_spmm(buf, rows))
+            out = opc.spmm(A, H, relu_mask=relu_mask, push_ptrs=ax.spush_targets(buf), push_ld=D,
+                           tile_reduce=ax.tile_reduce(buf))
         else:
             out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D)
             _reduce(ax, out, buf, epoch, False, relu_mask, KID_SPMM)
@@ -177,13 +250,14 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
         # one op per row block: the receive slots stay bounded
         op_counts["row_blocked"] += 1
         out = torch.empty((rows, D), dtype=H.dtype, device=H.device)
-        ax.ensure(max(r1 - r0 for r0, r1 in blocks) * D * H.element_size())
+        nbytes = max(r1 - r0 for r0, r1 in blocks) * D * H.element_size()
+        ax.ensure(sentinel_bytes=nbytes) if in_kernel else ax.ensure(nbytes)
         for r0, r1 in blocks:
             epoch, buf = ax.next_op()
             mask_blk = None if relu_mask is None else relu_mask[r0:r1]
-            if in_kernel and opc.spmm_supports_tile_reduce(A, H, (r0, r1)):
+            if in_kernel:
                 opc.spmm(A, H, relu_mask=mask_blk, row_range=(r0, r1), out=out[r0:r1],
-                         push_ptrs=ax.push_targets(buf), push_ld=D, tile_reduce=ax.tile_reduce_spmm(buf, r1 - r0))
+                         push_ptrs=ax.spush_targets(buf), push_ld=D, tile_reduce=ax.tile_reduce(buf))
             else:
                 opc.spmm(A, H, row_range=(r0, r1), out=out[r0:r1], push_ptrs=ax.push_targets(buf), push_ld=D)
                 _reduce(ax, out[r0:r1], buf, epoch, False, mask_blk, KID_SPMM)
@@ -247,24 +321,42 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
         return torch.relu_(out) if relu else out
     blocks = _row_blocks(rows, N * a.element_size())
     in_kernel = IN_KERNEL_REDUCE and (emulator.active() or (a.dtype == torch.bfloat16 and N % 8 == 0))
+    if PIPELINE and not in_kernel and len(blocks) == 1 and _sentinel_ok(a.dtype, N):
+        esz = a.element_size()
+        ax.ensure(sentinel_bytes=rows * N * esz)
+        _epoch, buf = ax.next_op()
+        out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+        targets, slots = ax.spush_targets(buf), ax.tile_reduce(buf)[0]
+        side = _SideStream(ax)
+        for r0, r1 in _pipeline_chunks(rows, N * esz):
+            off = r0 * N * esz
+            opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False, push_ptrs=[t + off for t in targets], push_ld=N,
+                     out=out[r0:r1])
+            side.run(lambda: _reduce_sentinel(ax, out[r0:r1], [p + off for p in slots], N, relu, None, KID_GEMM))
+        side.join()
+        op_counts["one_shot"] += 1
+        op_counts["pipelined"] += 1
+        return out
     if len(blocks) == 1:
-        ax.ensure(rows * N * a.element_size())
+        nbytes = rows * N * a.element_size()
+        ax.ensure(sentinel_bytes=nbytes) if in_kernel else ax.ensure(nbytes)
         epoch, buf = ax.next_op()
         if in_kernel:
-            out = opc.gemm(a, W, trans_b=trans_b, relu=relu, push_ptrs=ax.push_targets(buf), push_ld=N,
-                           tile_reduce=ax.tile_reduce_gemm(epoch, buf))
+            out = opc.gemm(a, W, trans_b=trans_b, relu=relu, push_ptrs=ax.spush_targets(buf), push_ld=N,
+                           tile_reduce=ax.tile_reduce(buf))
         else:
             out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N)
             _reduce(ax, out, buf, epoch, relu, None, KID_GEMM)
     else:
         op_counts["row_blocked"] += 1
         out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
-        ax.ensure(max(r1 - r0 for r0, r1 in blocks) * N * a.element_size())
+        nbytes = max(r1 - r0 for r0, r1 in blocks) * N * a.element_size()
+        ax.ensure(sentinel_bytes=nbytes) if in_kernel else ax.ensure(nbytes)
         for r0, r1 in blocks:
             epoch, buf = ax.next_op()
             if in_kernel:
-                opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=relu, push_ptrs=ax.push_targets(buf), push_ld=N,
-                         out=out[r0:r1], tile_reduce=ax.tile_reduce_gemm(epoch, buf))
+                opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=relu, push_ptrs=ax.spush_targets(buf), push_ld=N,
+                         out=out[r0:r1], tile_reduce=ax.tile_reduce(buf))
             else:
                 opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
                          out=out[r0:r1])

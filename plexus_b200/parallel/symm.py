@@ -4,17 +4,16 @@ A workspace is one ``cudaMalloc`` per rank whose CUDA-IPC handle is exchanged ov
 process group, so every rank holds a device pointer into every peer's buffer and kernels can
 store into / load from peer memory directly over NVLink.  Layout of each rank's buffer::
 
-    [ flags: int32[2][8] (1 KiB) | signals: int32[2][8][SIG_INTS] | buffer 0: p slots | buffer 1: p slots ]
-
-The signals serve the kernels that finish an all-reduce themselves: per (buffer, source rank) the
-first ``GEMM_SIG_INTS`` entries are written by the source's GEMM CTAs (one entry per CTA, counting
-the tiles it has pushed), the next ``TILE_SIG_INTS`` count, per fixed block of output rows, how
-many rows of that block the source's SpMM has pushed.
+    [ flags: int32[2][8] (1 KiB) | buffer 0: p slots | buffer 1: p slots | sentinel buffer 0 | sentinel buffer 1 ]
 
 Slot ``s`` of a buffer receives data from group rank ``s``.  The op counter ("epoch") of an axis
 selects buffer ``epoch % 2``; see ``csrc/kernels/comm_fused.cu`` for the flag protocol and why
-double buffering is enough.  Workspaces grow on demand (a collective operation: every rank of
-the axis asks for the same size at the same point of the program).
+double buffering is enough.  The *sentinel* buffers serve the all-reduces that the compute kernels
+finish themselves: they hold 0xFF bytes wherever nothing has arrived, the receiving kernel
+recognises arrived bf16 data by itself and puts the sentinel back after use, so these ops need
+neither flags nor fences (``csrc/include/sentinel_reduce.cuh``).  Workspaces grow on demand (a
+collective operation: every rank of the axis asks for the same size at the same point of the
+program).
 """
 
 from __future__ import annotations
@@ -41,12 +40,7 @@ def _device_sync() -> None:
         torch.cuda.synchronize()
 
 MAX_GROUP = 8
-OP_FLAG_BYTES = 1024
-GEMM_SIG_INTS = 256          # >= the largest grid of the tcgen05 GEMM
-TILE_SIG_INTS = 65536        # row blocks of one SpMM output
-SIG_INTS = GEMM_SIG_INTS + TILE_SIG_INTS
-FLAG_BYTES = OP_FLAG_BYTES + 2 * MAX_GROUP * SIG_INTS * 4
-EPOCH_LIMIT = 100000         # signal values are epoch << 14 + count: stay far below 2^31
+FLAG_BYTES = 1024
 DEFAULT_TIMEOUT_MS = 5000.0
 
 
@@ -71,17 +65,20 @@ class AxisComm:
         self.same_host = bool((allh == allh[0]).all())
         self.epoch = 0
         self.slot_bytes = 0
+        self.sslot_bytes = 0  # slot size of the sentinel buffers
         self.local_ptr = 0
         self.ptrs: List[int] = []
         self.timeout_ms = DEFAULT_TIMEOUT_MS
-        self._local_done = None  # per-tile row counters of this rank's own SpMM (device-local)
 
     # -- allocation ---------------------------------------------------------------------
-    def ensure(self, slot_bytes: int) -> None:
+    def ensure(self, slot_bytes: int = 0, sentinel_bytes: int = 0) -> None:
+        """Make the flagged slots at least ``slot_bytes`` and the sentinel slots at least
+        ``sentinel_bytes`` large (collective over the axis when something has to grow)."""
         if not self.same_host:
             raise RuntimeError("peer-memory workspace requested for an axis that spans hosts")
-        slot_bytes = (int(slot_bytes) + 1023) // 1024 * 1024
-        if slot_bytes <= self.slot_bytes:
+        slot_bytes = max(self.slot_bytes, (int(slot_bytes) + 1023) // 1024 * 1024)
+        sentinel_bytes = max(self.sslot_bytes, (int(sentinel_bytes) + 1023) // 1024 * 1024)
+        if slot_bytes == self.slot_bytes and sentinel_bytes == self.sslot_bytes and self.ptrs:
             return
         C = _C()
         dev = (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(self.group) == "nccl"
@@ -90,8 +87,11 @@ class AxisComm:
         _device_sync()
         dist.barrier(group=self.group)
         self.release()
-        total = FLAG_BYTES + 2 * self.p * slot_bytes
+        plain = 2 * self.p * slot_bytes
+        total = FLAG_BYTES + plain + 2 * self.p * sentinel_bytes
         ptr, handle = C.symm_alloc(total)
+        if sentinel_bytes:
+            C.symm_fill(ptr + FLAG_BYTES + plain, 0xFF, 2 * self.p * sentinel_bytes)
         mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
         allh = torch.empty(self.p * 64, dtype=torch.uint8, device=dev)
         dist.all_gather_into_tensor(allh, mine, group=self.group)
@@ -99,7 +99,7 @@ class AxisComm:
         self.ptrs = []
         for q in range(self.p):
             self.ptrs.append(ptr if q == self.rank else C.symm_open(bytes(allh[q].tolist())))
-        self.local_ptr, self.slot_bytes = ptr, slot_bytes
+        self.local_ptr, self.slot_bytes, self.sslot_bytes = ptr, slot_bytes, sentinel_bytes
         _device_sync()
         dist.barrier(group=self.group)
 
@@ -116,7 +116,7 @@ class AxisComm:
         except Exception:
             pass
         C.symm_free(self.local_ptr)
-        self.ptrs, self.local_ptr, self.slot_bytes = [], 0, 0
+        self.ptrs, self.local_ptr = [], 0
 
     # -- addressing ---------------------------------------------------------------------
     def slot(self, owner: int, buf: int, src: int) -> int:
@@ -127,49 +127,22 @@ class AxisComm:
         return self.ptrs[owner] + (buf * MAX_GROUP + src) * 4
 
     def next_op(self):
-        if self.epoch >= EPOCH_LIMIT:
-            self._restart_epochs()
         self.epoch += 1
         return self.epoch, self.epoch % 2
 
-    def _restart_epochs(self) -> None:
-        """Start counting ops from zero again (collective: every rank of the axis reaches the limit
-        at the same op).  Nobody may still be waiting on an old value when the flags are cleared."""
-        _device_sync()
-        dist.barrier(group=self.group)
-        _C().symm_clear(self.local_ptr, FLAG_BYTES)
-        _device_sync()
-        dist.barrier(group=self.group)
-        self.epoch = 0
+    # -- sentinel buffers (all-reduces finished inside the compute kernels) --------------
+    def sslot(self, owner: int, buf: int, src: int) -> int:
+        base = self.ptrs[owner] + FLAG_BYTES + 2 * self.p * self.slot_bytes
+        return base + (buf * self.p + src) * self.sslot_bytes
 
-    def sig_base(self, epoch: int) -> int:
-        return epoch << 14
+    def spush_targets(self, buf: int) -> List[int]:
+        """This rank's sentinel slot in every peer's buffer."""
+        return [self.sslot(q, buf, self.rank) for q in self.peers]
 
-    def gemm_sig(self, owner: int, buf: int, src: int) -> int:
-        """Address of the per-CTA signal array that rank ``src`` writes inside ``owner``'s workspace."""
-        return self.ptrs[owner] + OP_FLAG_BYTES + ((buf * MAX_GROUP + src) * SIG_INTS) * 4
-
-    def tile_sig(self, owner: int, buf: int, src: int) -> int:
-        """Address of the per-row-block counters that rank ``src`` adds to inside ``owner``'s workspace."""
-        return self.gemm_sig(owner, buf, src) + GEMM_SIG_INTS * 4
-
-    def tile_reduce_gemm(self, epoch: int, buf: int):
-        """Argument tuple of the GEMM's in-kernel all-reduce for op ``epoch`` (see ``ops.cuda.gemm``)."""
-        return (self.recv_slots(buf), [self.gemm_sig(q, buf, self.rank) for q in self.peers],
-                [self.gemm_sig(self.rank, buf, q) for q in self.peers], self.sig_base(epoch), self.rank,
-                self.timeout_ms)
-
-    def tile_reduce_spmm(self, buf: int, out_rows: int):
-        """Argument tuple of the SpMM's in-kernel all-reduce (see ``ops.cuda.spmm``): exchange tiles of
-        at least 512 output rows, at most ``TILE_SIG_INTS`` of them."""
-        tile_rows = max(512, -(-out_rows // TILE_SIG_INTS))
-        tile_rows = -(-tile_rows // 128) * 128
-        if self._local_done is None:
-            dev = "cpu" if emulator.active() else torch.device("cuda", torch.cuda.current_device())
-            self._local_done = torch.zeros(TILE_SIG_INTS, dtype=torch.int32, device=dev)
-        return (self.recv_slots(buf), [self.tile_sig(q, buf, self.rank) for q in self.peers],
-                [self.tile_sig(self.rank, buf, q) for q in self.peers], self.rank, self.timeout_ms, tile_rows,
-                self._local_done.data_ptr())
+    def tile_reduce(self, buf: int):
+        """Argument tuple of the in-kernel all-reduce (see ``ops.cuda.gemm`` / ``ops.cuda.spmm``):
+        every peer's sentinel slot in this rank's buffer, this rank's position, the wait limit."""
+        return ([self.sslot(self.rank, buf, q) for q in self.peers], self.rank, self.timeout_ms)
 
     def push_targets(self, buf: int) -> List[int]:
         """This rank's slot in every peer's buffer."""

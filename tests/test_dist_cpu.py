@@ -26,6 +26,9 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
         fused.TWO_SHOT = flags.get("two_shot", False)
         fused.MAX_MESSAGE_BYTES = flags.get("max_message_bytes", fused.MAX_MESSAGE_BYTES)
         fused.ROW_BLOCK_MULTIPLE = flags.get("row_block_multiple", fused.ROW_BLOCK_MULTIPLE)
+        fused.PIPELINE = flags.get("pipeline", False)
+        fused.PIPELINE_MIN_BYTES = flags.get("pipeline_min_bytes", fused.PIPELINE_MIN_BYTES)
+        fused.IN_KERNEL_REDUCE = flags.get("in_kernel", False)
     plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
              block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
              tune_gemms=flags.get("tune", False), comm=comm)
@@ -174,6 +177,18 @@ def test_fused_host_code_on_emulated_peer_memory_two_shot(grid):
     expect = {"one_shot": False, "two_shot": True, "library": False}
     run_distributed(_worker, world, grid, 3, True, 53, 9, 7, 8, False,
                     dict(EMU, two_shot=True, small_bytes=0, one_shot_ranks=1, expect_ops=expect))
+
+
+@pytest.mark.parametrize("mode", ["pipeline", "in_kernel"])
+@pytest.mark.parametrize("grid", [(2, 1, 1), (1, 1, 2), (2, 2, 2), (1, 4, 1)])
+def test_fused_host_code_flag_free_forms(grid, mode):
+    """The one-shot forms whose receive side needs no flags (sentinel-kept slots): reduce kernel on row
+    chunks (pipeline) and reduction inside the compute kernel (in_kernel), on the emulated peer memory."""
+    world = grid[0] * grid[1] * grid[2]
+    key = "pipelined" if mode == "pipeline" else "in_kernel"
+    run_distributed(_worker, world, grid, 3, True, 300, 10, 5, 12, False,
+                    dict(EMU, one_shot_ranks=8, small_bytes=0, pipeline_min_bytes=4096, **{mode: True},
+                         expect_ops={"one_shot": True, key: True, "library": False}))
 
 
 def test_fused_host_code_default_policy_mixes_push_and_library_paths():

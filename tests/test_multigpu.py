@@ -163,16 +163,21 @@ def _sparse_shard(dense, dev):
     return graph_ops.csr_tensor(crow, col, val, (rows, cols))
 
 
-def _in_kernel_ops(rank, world, long_row):
-    """All-reduces finished inside the compute kernels (one-shot form): the GEMM exchanges 128-row
-    tiles CTA by CTA, the SpMM exchanges fixed blocks of rows tracked by counters.  Results are checked
-    against fp32 sums and must be bitwise equal on every rank of the group."""
+def _in_kernel_ops(rank, world, long_row, mode):
+    """One-shot all-reduces whose receive side needs no flags: the partials land in sentinel-kept
+    slots and are recognised by their content.  ``pipelined``: a reduce kernel on a side stream works
+    on row chunk i while chunk i + 1 is computed and pushed; ``in_kernel``: reducer warps of the GEMM /
+    the computing warps of the SpMM do it inside the compute kernel.  Results are checked against
+    fp32 sums and must be bitwise equal on every rank of the group."""
     import plexus_b200 as plx
     from plexus_b200.ops import cuda as opc
     from plexus_b200.parallel import fused
 
     fused.ONE_SHOT_MAX_RANKS = 8
     fused.SMALL_MESSAGE_BYTES = 0
+    fused.IN_KERNEL_REDUCE = mode == "in_kernel"
+    fused.PIPELINE = mode == "pipelined"
+    fused.PIPELINE_MIN_BYTES = 1 << 16  # several chunks already on these small matrices
     opc.SPMM_LONG_ROW[1] = opc.SPMM_LONG_ROW[2] = long_row
     grid = plx.init(world, 1, 1, comm="fused")
     g = grid.group("x")
@@ -217,15 +222,16 @@ def _in_kernel_ops(rank, world, long_row):
         close(fused.spmm_all_reduce(A, H, g, relu_mask=mask.to(dev)), want * (mask.float() > 0), ("spmm mask", it))
     torch.cuda.synchronize()
     opc.check_status()
-    assert fused.op_counts["in_kernel"] - before["in_kernel"] == 4 * 7, fused.op_counts
+    assert fused.op_counts[mode] - before[mode] == 4 * 7, fused.op_counts
     plx.shutdown()
 
 
+@pytest.mark.parametrize("mode", ["pipelined", "in_kernel"])
 @pytest.mark.parametrize("world,long_row", [(2, 4096), (2, 64), (4, 256)])
-def test_in_kernel_all_reduce(world, long_row):
+def test_flag_free_all_reduce(world, long_row, mode):
     if torch.cuda.device_count() < world:
         pytest.skip("not enough GPUs")
-    run_gpus(_in_kernel_ops, world, long_row, timeout=300)
+    run_gpus(_in_kernel_ops, world, long_row, mode, timeout=300)
 
 
 def _other_forms(rank, world):
