@@ -121,11 +121,12 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
     scr = scratch.data_ptr<float>();
     scr_n = scratch.numel();
   }
-  int* counters = nullptr;
-  if (long_counter.defined() && long_counter.numel() > 0) {
-    TORCH_CHECK(long_counter.is_cuda() && long_counter.scalar_type() == at::kInt && long_counter.is_contiguous());
-    counters = long_counter.data_ptr<int>();
-  }
+  // one counter per long row, then the two work hand-out counters of the CUDA-core kernel
+  TORCH_CHECK(long_counter.defined() && long_counter.numel() >= 2 && long_counter.is_cuda() &&
+                  long_counter.scalar_type() == at::kInt && long_counter.is_contiguous(),
+              "spmm: counters must be an int32 CUDA tensor of (long rows + 2) zeros");
+  int* counters = long_counter.data_ptr<int>();
+  const int num_long = static_cast<int>(long_counter.numel() - 2);
   plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
   TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
               "spmm: row segments do not cover the output");
@@ -143,8 +144,8 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
     check(plx::launch_spmm_csr(dtype_of(H), rowptr.data_ptr<int>(), col.data_ptr<int>(), val.data_ptr<float>(),
                                H.data_ptr(), H.stride(0), out.data_ptr(), out.stride(0), mptr, ldm,
                                static_cast<int>(D), static_cast<int>(row_begin), int_ptr(items), num_items,
-                               static_cast<int>(num_pieces), int_ptr(long_piece_start), counters, scr, scr_n,
-                               push.n ? &push : nullptr, stream(), red.n ? &red : nullptr,
+                               static_cast<int>(num_pieces), int_ptr(long_piece_start),
+                               num_long, counters, scr, scr_n, push.n ? &push : nullptr, stream(), red.n ? &red : nullptr,
                                static_cast<int>(out.size(0))));
   }
 }

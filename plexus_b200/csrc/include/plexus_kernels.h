@@ -49,12 +49,15 @@ struct TileReduce {
 // long rows first ({row, -(long id + 1), first nonzero, last nonzero + 1}; a piece's index is also
 // the index of its fp32 partial row in `scratch`, spmm_scratch_per_piece() floats each), then
 // blocks of whole rows ({first row, last row + 1, 0, 0}).  long_piece_start[num_long + 1] indexes
-// the pieces of each long row; long_counter[num_long] must be zero and is left zero.
+// the pieces of each long row; long_counter[num_long + 2] (one per long row, then the
+// two counters that hand out the items) must be zero and is left zero.  Without the
+// in-kernel all-reduce the long rows are summed by a second, small launch; with it the warp that
+// delivers the last piece of a row sums them, so that everything happens in one kernel.
 int64_t spmm_scratch_per_piece(int dtype, int D);
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
                             int64_t ldm, int D, int row_begin, const int* items, int num_items,
-                            int num_pieces, const int* long_piece_start, int* long_counter,
+                            int num_pieces, const int* long_piece_start, int num_long, int* long_counter,
                             float* scratch, int64_t scratch_elems, const PushTargets* push,
                             cudaStream_t stream, const TileReduce* reduce = nullptr, int out_rows = 0);
 

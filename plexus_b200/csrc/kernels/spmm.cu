@@ -255,6 +255,49 @@ __device__ __forceinline__ void zero_acc(float (&acc)[VPL][VN]) {
 #define PLX_SPMM_MINB 4
 #endif
 
+// acc = sum of the fp32 partial rows of pieces [p0, p1), in index order.
+template <typename T, int LPR, int VPL>
+__device__ __forceinline__ void sum_pieces(const float* __restrict__ scratch, int p0, int p1, int lane,
+                                           float (&acc)[VPL][Vec16<T>::N]) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int W = LPR * VPL * VN;
+  zero_acc(acc);
+  if (lane < LPR) {
+    for (int p = p0; p < p1; ++p) {
+      const float* src = scratch + static_cast<int64_t>(p) * W;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+#pragma unroll
+        for (int k = 0; k < VN; k += 4) {
+          const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (v * LPR + lane) * VN + k));
+          acc[v][k] += f.x;
+          acc[v][k + 1] += f.y;
+          acc[v][k + 2] += f.z;
+          acc[v][k + 3] += f.w;
+        }
+      }
+    }
+  }
+}
+
+// Second launch of the plain (not fused) form: one warp per long row sums its pieces and stores it.
+template <typename T, int LPR, int VPL>
+__global__ void __launch_bounds__(SPMM_WARPS * 32)
+spmm_long_rows_kernel(const int4* __restrict__ items, const int* __restrict__ long_piece_start, int num_long,
+                      const float* __restrict__ scratch, T* __restrict__ out, int64_t ldo,
+                      const T* __restrict__ mask, int64_t ldm, int D, int row_begin, const PushTargets push) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int warps_total = gridDim.x * wpb;
+  for (int L = blockIdx.x * wpb + (threadIdx.x >> 5); L < num_long; L += warps_total) {
+    const int p0 = __ldg(long_piece_start + L), p1 = __ldg(long_piece_start + L + 1);
+    float acc[VPL][Vec16<T>::N];
+    sum_pieces<T, LPR, VPL>(scratch, p0, p1, lane, acc);
+    const int64_t orow = __ldg(items + p0).x - row_begin;  // every piece item carries its row
+    row_store<T, LPR, VPL>(out + orow * ldo, mask ? mask + orow * ldm : nullptr, D, lane, acc, push, orow);
+  }
+}
+
 // Work items, 4 ints each (built by ops/cuda.py): first the pieces of the long rows
 // {row, -(long id + 1), first nonzero, last nonzero + 1} - the index of a piece is also the index of
 // its fp32 partial row (W = LPR * VPL * VN floats) in `scratch` - then blocks of whole rows
@@ -267,8 +310,8 @@ spmm_items_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, c
                   const T* __restrict__ H, int64_t ldh, T* __restrict__ out, int64_t ldo,
                   const T* __restrict__ mask, int64_t ldm, int D, int row_begin,
                   const int4* __restrict__ items, int num_items, const int* __restrict__ long_piece_start,
-                  int* __restrict__ long_counter, float* __restrict__ scratch, const PushTargets push,
-                  const TileReduce red, int out_rows) {
+                  int num_long, int* __restrict__ long_counter, float* __restrict__ scratch,
+                  const PushTargets push, const TileReduce red, int out_rows) {
   constexpr int VN = Vec16<T>::N;
   constexpr int W = LPR * VPL * VN;
   const int lane = threadIdx.x & 31;
@@ -281,7 +324,11 @@ spmm_items_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, c
   tile_reduce::Reducer reducer(red, reinterpret_cast<__nv_bfloat16*>(out), ldo,
                                reinterpret_cast<const __nv_bfloat16*>(mask), ldm, push.ld, D, out_rows, lane,
                                KERNEL_ID_SPMM);
-  for (int b = warp_global; b < num_items && (!FUSED || reducer.ok); b += warps_total) {
+  // The first item of a warp is its own index; the following ones are handed out by a counter, so
+  // that a warp with cheap items takes more of them (the items are sorted by falling cost: pieces,
+  // then blocks).  Which warp computes an item has no influence on the result.
+  int* work_next = long_counter + num_long;  // {next item - warps_total, warps that are done}
+  for (int b = warp_global; b < num_items && (!FUSED || reducer.ok);) {
     const int4 item = __ldg(items + b);
     if (item.y >= 0) {
       for (int row = item.x; row < item.y; ++row) {
@@ -307,45 +354,40 @@ spmm_items_kernel(const int* __restrict__ rowptr, const int* __restrict__ col, c
           for (int i = 0; i < VN; i += 4) d4[i / 4] = make_float4(acc[v][i], acc[v][i + 1], acc[v][i + 2], acc[v][i + 3]);
         }
       }
-      __syncwarp();
-      const int L = -item.y - 1;
-      const int p0 = __ldg(long_piece_start + L), p1 = __ldg(long_piece_start + L + 1);
-      int last = 0;
-      if (lane == 0) {
-        __threadfence();
-        last = atomicAdd(long_counter + L, 1) == p1 - p0 - 1;
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        // sum the pieces in index order, whoever delivered the last one
-        zero_acc(acc);
-        if (lane < LPR) {
-          for (int p = p0; p < p1; ++p) {
-            const float* src = scratch + static_cast<int64_t>(p) * W;
-#pragma unroll
-            for (int v = 0; v < VPL; ++v) {
-#pragma unroll
-              for (int k = 0; k < VN; k += 4) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (v * LPR + lane) * VN + k));
-                acc[v][k] += f.x;
-                acc[v][k + 1] += f.y;
-                acc[v][k + 2] += f.z;
-                acc[v][k + 3] += f.w;
-              }
-            }
-          }
+      if constexpr (FUSED) {
+        // one launch: the warp that delivers the last piece of a row sums all pieces in index order
+        // (the same order whoever comes last) and stores the row
+        __syncwarp();
+        const int L = -item.y - 1;
+        const int p0 = __ldg(long_piece_start + L), p1 = __ldg(long_piece_start + L + 1);
+        int last = 0;
+        if (lane == 0) {
+          __threadfence();
+          last = atomicAdd(long_counter + L, 1) == p1 - p0 - 1;
         }
-        const int64_t orow = item.x - row_begin;
-        row_store<T, LPR, VPL>(out + orow * ldo, store_mask ? store_mask + orow * ldm : nullptr, D, lane, acc,
-                               push, orow);
-        if (lane == 0) long_counter[L] = 0;  // ready for the next launch on this matrix
-        if constexpr (FUSED) reducer.publish(item.x - row_begin, item.x - row_begin + 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          sum_pieces<T, LPR, VPL>(scratch, p0, p1, lane, acc);
+          const int64_t orow = item.x - row_begin;
+          row_store<T, LPR, VPL>(out + orow * ldo, store_mask ? store_mask + orow * ldm : nullptr, D, lane, acc,
+                                 push, orow);
+          if (lane == 0) long_counter[L] = 0;  // ready for the next launch on this matrix
+          reducer.publish(item.x - row_begin, item.x - row_begin + 1);
+        }
       }
+      // otherwise the long rows are finished by spmm_long_rows_kernel, launched right after
     }
     if constexpr (FUSED) reducer.poll(false);
+    if (lane == 0) b = atomicAdd(work_next, 1) + warps_total;
+    b = __shfl_sync(0xffffffffu, b, 0);
   }
   if constexpr (FUSED) reducer.finish();
+  // the last warp to leave zeroes the counters for the next launch on this matrix
+  if (lane == 0 && atomicAdd(work_next + 1, 1) == warps_total - 1) {
+    work_next[0] = 0;
+    work_next[1] = 0;
+  }
 }
 
 static int spmm_grid(int work_items, int warps_per_block, int blocks_per_sm) {
@@ -368,7 +410,7 @@ int64_t spmm_scratch_per_piece(int dtype, int D) {
 template <typename T>
 static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const float* val, const T* H,
                                  int64_t ldh, T* out, int64_t ldo, const T* mask, int64_t ldm, int row_begin,
-                                 const int4* items, int num_items, const int* long_piece_start,
+                                 const int4* items, int num_items, const int* long_piece_start, int num_long,
                                  int* long_counter, float* scratch, const PushTargets& push,
                                  const TileReduce& red, int out_rows, cudaStream_t stream) {
   constexpr int VN = Vec16<T>::N;
@@ -380,12 +422,19 @@ static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const
       spmm_items_kernel<T, LPR, VPL, CAN_FUSE><<<spmm_grid(num_items, SPMM_WARPS, 8), SPMM_WARPS * 32, 0,     \
                                                  stream>>>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D,  \
                                                            row_begin, items, num_items, long_piece_start,     \
-                                                           long_counter, scratch, push, red, out_rows);       \
-    else                                                                                                       \
+                                                           num_long, long_counter, scratch, push, red,        \
+                                                           out_rows);                                          \
+    else {                                                                                                     \
       spmm_items_kernel<T, LPR, VPL, false><<<spmm_grid(num_items, SPMM_WARPS, 8), SPMM_WARPS * 32, 0,        \
                                               stream>>>(rowptr, col, val, H, ldh, out, ldo, mask, ldm, D,     \
                                                         row_begin, items, num_items, long_piece_start,        \
-                                                        long_counter, scratch, push, red, out_rows);          \
+                                                        num_long, long_counter, scratch, push, red,           \
+                                                        out_rows);                                             \
+      if (num_long > 0)                                                                                        \
+        spmm_long_rows_kernel<T, LPR, VPL><<<spmm_grid(num_long, SPMM_WARPS, 8), SPMM_WARPS * 32, 0,          \
+                                             stream>>>(items, long_piece_start, num_long, scratch, out, ldo,  \
+                                                       mask, ldm, D, row_begin, push);                        \
+    }                                                                                                          \
   } while (0)
   if (vecs <= 4) PLX_SPMM(4, 1);
   else if (vecs <= 8) PLX_SPMM(8, 1);
@@ -403,7 +452,7 @@ static const char* dispatch_spmm(int D, const int* rowptr, const int* col, const
 const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const float* val,
                             const void* H, int64_t ldh, void* out, int64_t ldo, const void* mask,
                             int64_t ldm, int D, int row_begin, const int* items_in, int num_items,
-                            int num_pieces, const int* long_piece_start, int* long_counter,
+                            int num_pieces, const int* long_piece_start, int num_long, int* long_counter,
                             float* scratch, int64_t scratch_elems, const PushTargets* push_in,
                             cudaStream_t stream, const TileReduce* reduce_in, int out_rows) {
   const int esz = dtype == DT_BF16 ? 2 : 4;
@@ -435,7 +484,8 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
       reinterpret_cast<uintptr_t>(items_in) % 16)
     return "spmm: feature pointers and work items must be 16-byte aligned";
   if (D == 0 || num_items == 0) return nullptr;
-  if (num_pieces > 0 && (long_piece_start == nullptr || long_counter == nullptr || scratch == nullptr ||
+  if (long_counter == nullptr) return "spmm: the counters (long rows + 2 zeros) are missing";
+  if (num_pieces > 0 && (long_piece_start == nullptr || scratch == nullptr ||
                          scratch_elems < static_cast<int64_t>(num_pieces) * spmm_scratch_per_piece(dtype, D)))
     return "spmm: long rows need the piece index, the counters and scratch for the pieces";
   const int4* items = reinterpret_cast<const int4*>(items_in);
@@ -443,12 +493,12 @@ const char* launch_spmm_csr(int dtype, const int* rowptr, const int* col, const 
     return dispatch_spmm<__nv_bfloat16>(D, rowptr, col, val, reinterpret_cast<const __nv_bfloat16*>(H),
                                         ldh, reinterpret_cast<__nv_bfloat16*>(out), ldo,
                                         reinterpret_cast<const __nv_bfloat16*>(mask), ldm, row_begin, items,
-                                        num_items, long_piece_start, long_counter, scratch, push, red,
+                                        num_items, long_piece_start, num_long, long_counter, scratch, push, red,
                                         out_rows, stream);
   if (dtype == DT_F32)
     return dispatch_spmm<float>(D, rowptr, col, val, reinterpret_cast<const float*>(H), ldh,
                                 reinterpret_cast<float*>(out), ldo, reinterpret_cast<const float*>(mask),
-                                ldm, row_begin, items, num_items, long_piece_start, long_counter, scratch,
+                                ldm, row_begin, items, num_items, long_piece_start, num_long, long_counter, scratch,
                                 push, red, out_rows, stream);
   return "spmm: features must be bf16 or fp32";
 }

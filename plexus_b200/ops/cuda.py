@@ -135,11 +135,11 @@ def spmm_schedule(crow: torch.Tensor, r0: int, r1: int, owner=None, variant: int
         pe = torch.minimum(pb + plen[owner_of], (lbeg + ldeg)[owner_of])
         pieces = torch.stack([lidx[owner_of] + r0, -(owner_of + 1), pb, pe], dim=1)
         sch.long_piece_start = pstart.to(torch.int32)
-        sch.long_counter = torch.zeros(lidx.numel(), **i32)
+        sch.long_counter = torch.zeros(lidx.numel() + 2, **i32)  # + the two work hand-out counters
     else:
         pieces = torch.empty((0, 4), dtype=torch.int64, device=dev)
         sch.long_piece_start = torch.empty(0, **i32)
-        sch.long_counter = torch.empty(0, **i32)
+        sch.long_counter = torch.zeros(2, **i32)
     sch.num_pieces = int(pieces.shape[0])
     # ---- blocks of the other rows: a new block where the accumulated cost crosses a multiple of the
     #      block cost, and after every long row
