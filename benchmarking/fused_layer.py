@@ -7,11 +7,14 @@ Every rank holds its own sparse block ``A_r`` (rows x rows/P, seeded) and dense 
 P ranks compute ``all_reduce_sum(A_r . H_r)`` and ``all_reduce_sum(X_r . W_r)``, the two patterns
 of a 3D-parallel GCN layer (AGG over the outer axis, OUT over the inner axis).  Three paths:
 
-* ``fused``     : this package's kernels; the SpMM / tcgen05-GEMM epilogue stores each row into
-                  the peers' receive slots over NVLink, a flagged kernel sums the slots.  Timed in
-                  the default form for the group size and in both forms explicitly: ``one_shot``
-                  (every row to every peer) and ``two_shot`` (each row to its owner, which reduces
-                  and broadcasts its segment);
+* ``fused``     : this package's kernels, timed in the default form for the group size and in
+                  every form explicitly: ``one_shot`` (the SpMM / tcgen05-GEMM epilogue stores each
+                  row into every peer's receive slot over NVLink, a flagged kernel sums the slots),
+                  ``two_shot`` (each row to its owner, which reduces and broadcasts its segment) and
+                  ``segment`` (partials written into a symmetric buffer, each rank's segment summed
+                  inside the NVSwitch by multimem loads and broadcast by multimem stores, in row
+                  chunks on a side stream while the next chunk is computed; ``--segment_sweep``
+                  also times other chunk counts and grid sizes of the reduce kernel);
 * ``nccl``      : the same compute kernels followed by ``dist.all_reduce`` (NCCL);
 * ``reference`` : what the reference executes: ``torch.sparse.mm`` / ``torch.mm`` in fp32
                   (cuSPARSE / cuBLAS) followed by an fp32 NCCL all-reduce.
@@ -61,6 +64,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip_reference", action="store_true")
+    ap.add_argument("--segment_sweep", action="store_true")
     args = ap.parse_args()
 
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -112,11 +116,26 @@ def main():
     b = spmm_nccl().float()
     res["spmm_max_rel_diff_fused_vs_nccl"] = ((a - b).abs().max() / b.abs().max()).item()
     res["spmm_fused_ms"] = timed(spmm_fused, args.warmup, args.iters)
-    default_ranks = fused.ONE_SHOT_MAX_RANKS
-    for name, ranks in (("one_shot", p), ("two_shot", 1)):
-        fused.ONE_SHOT_MAX_RANKS = ranks
-        res[f"spmm_{name}_ms"] = timed(spmm_fused, args.warmup, args.iters)
-    fused.ONE_SHOT_MAX_RANKS = default_ranks
+    defaults = (fused.ONE_SHOT_MAX_RANKS, fused.TWO_SHOT, fused.SEGMENT_REDUCE, fused.SEGMENT_CHUNKS,
+                fused.SEGMENT_BLOCKS)
+
+    def each_form(prefix, fn):
+        forms = [("one_shot", (p, False, False, 1, 64)), ("two_shot", (1, True, False, 1, 64)),
+                 ("segment", (1, False, True, defaults[3], defaults[4]))]
+        if args.segment_sweep:
+            forms += [(f"segment_c{c}_b{b}", (1, False, True, c, b)) for c, b in
+                      ((1, 64), (1, 148), (1, 296), (2, 64), (4, 32), (4, 148), (8, 64))]
+        for name, cfg in forms:
+            (fused.ONE_SHOT_MAX_RANKS, fused.TWO_SHOT, fused.SEGMENT_REDUCE, fused.SEGMENT_CHUNKS,
+             fused.SEGMENT_BLOCKS) = cfg
+            if name.startswith("segment"):
+                got = fn().float()
+                res[f"{prefix}_{name}_max_rel_diff_vs_nccl"] = ((got - b).abs().max() / b.abs().max()).item()
+            res[f"{prefix}_{name}_ms"] = timed(fn, args.warmup, args.iters)
+        (fused.ONE_SHOT_MAX_RANKS, fused.TWO_SHOT, fused.SEGMENT_REDUCE, fused.SEGMENT_CHUNKS,
+         fused.SEGMENT_BLOCKS) = defaults
+
+    each_form("spmm", spmm_fused)
     res["spmm_nccl_ms"] = timed(spmm_nccl, args.warmup, args.iters)
     res["spmm_only_ms"] = timed(lambda: ops.spmm(A, H), args.warmup, args.iters)
     msg = rows * D * 2
@@ -141,10 +160,7 @@ def main():
     b = gemm_nccl().float()
     res["gemm_max_rel_diff_fused_vs_nccl"] = ((a - b).abs().max() / b.abs().max()).item()
     res["gemm_fused_ms"] = timed(gemm_fused, args.warmup, args.iters)
-    for name, ranks in (("one_shot", p), ("two_shot", 1)):
-        fused.ONE_SHOT_MAX_RANKS = ranks
-        res[f"gemm_{name}_ms"] = timed(gemm_fused, args.warmup, args.iters)
-    fused.ONE_SHOT_MAX_RANKS = default_ranks
+    each_form("gemm", gemm_fused)
     res["gemm_nccl_ms"] = timed(gemm_nccl, args.warmup, args.iters)
     res["gemm_only_ms"] = timed(lambda: ops.gemm(X, W), args.warmup, args.iters)
     msg = rows * N * 2
@@ -174,6 +190,9 @@ def main():
         res["spmm_reference_ms"] = timed(ref_spmm, args.warmup, args.iters)
         res["gemm_reference_ms"] = timed(ref_gemm, args.warmup, args.iters)
     opc.check_status()
+    from plexus_b200.parallel import symm
+
+    res["multicast"] = bool(symm.axis_for(group).sym_mc)
     if rank == 0:
         print(json.dumps(res), flush=True)
     plx.shutdown()

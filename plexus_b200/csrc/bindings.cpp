@@ -386,6 +386,42 @@ void gather_segments(const std::vector<int64_t>& src_ptrs, const std::vector<int
                                     stream()));
 }
 
+// Reduce this rank's row segment of a symmetric buffer in place on every rank (multimem when
+// `mc_ptr` is non-zero, plain peer loads / stores over `all_ptrs` otherwise).  `seg` is the local
+// view of the segment (inside buffer all_ptrs[me]); `mask`: the rows of the segment.
+void segment_reduce(int64_t mc_ptr, const std::vector<int64_t>& all_ptrs, int64_t me, const Tensor& seg, bool relu,
+                    const c10::optional<Tensor>& mask, const std::vector<int64_t>& remote_flags,
+                    const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms, int64_t kernel_id,
+                    const Tensor& status, int64_t max_blocks) {
+  TORCH_CHECK(seg.is_cuda() && seg.dim() == 2 && seg.is_contiguous() && seg.scalar_type() == at::kBFloat16,
+              "segment_reduce: the segment must be a contiguous bf16 CUDA matrix");
+  TORCH_CHECK(all_ptrs.size() >= 1 && all_ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS + 1) && me >= 0 &&
+              me < static_cast<int64_t>(all_ptrs.size()));
+  const int64_t byte_off = reinterpret_cast<int64_t>(seg.data_ptr()) - all_ptrs[me];
+  TORCH_CHECK(byte_off >= 0 && byte_off % 16 == 0, "segment_reduce: the segment does not lie in the local buffer");
+  const void* mptr = nullptr;
+  int64_t ldm = 0;
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == at::kBFloat16 && mask->sizes() == seg.sizes() &&
+                mask->stride(1) == 1);
+    mptr = mask->data_ptr();
+    ldm = mask->stride(0);
+  }
+  c10::cuda::CUDAGuard guard(seg.device());
+  check(plx::launch_segment_reduce_bf16(reinterpret_cast<void*>(mc_ptr), make_slots(all_ptrs), byte_off / 2,
+                                        seg.size(0), static_cast<int>(seg.size(1)), relu, mptr, ldm,
+                                        make_sync(remote_flags, local_flags, epoch, timeout_ms, kernel_id, status),
+                                        static_cast<int>(max_blocks), stream()));
+}
+
+// Tensor over `numel` elements at a device address of the current device (a workspace of symm_alloc).
+Tensor symm_view(int64_t ptr, int64_t numel, at::ScalarType dtype) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return at::from_blob(reinterpret_cast<void*>(ptr), {numel},
+                       at::TensorOptions().dtype(dtype).device(at::kCUDA, dev));
+}
+
 void reduce_sentinel(Tensor& out, const std::vector<int64_t>& slot_ptrs, int64_t slot_ld, bool relu,
                      const c10::optional<Tensor>& mask, double timeout_ms, int64_t kernel_id, const Tensor& status,
                      int64_t me, int64_t max_blocks) {
@@ -556,6 +592,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reduce_slots_f32", &reduce_slots_f32);
   m.def("reduce_sentinel", &reduce_sentinel);
   m.def("reduce_segment", &reduce_segment);
+  m.def("segment_reduce", &segment_reduce);
   m.def("gather_segments", &gather_segments);
   m.def("push_copy", &push_copy);
   m.def("gather_slots", &gather_slots);
@@ -564,4 +601,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_close", &symm_close);
   m.def("symm_free", &symm_free);
   m.def("symm_fill", &symm_fill);
+  m.def("symm_view", &symm_view);
 }

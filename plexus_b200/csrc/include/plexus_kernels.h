@@ -178,6 +178,15 @@ struct SlotBytes {
 };
 const char* launch_gather_segments(const SlotList& src, const SlotList& dst, const SlotBytes& bytes,
                                    const PeerSync& sync, cudaStream_t stream);
+// ---- nvls_reduce.cu
+// Middle step of the all-reduce on a symmetric buffer S (same offset on every rank): after the flag
+// barrier, reduce `rows` x `cols` bf16 elements that start `elem_off` elements into S and write the
+// result (ReLU / mask applied) back to the same place on every rank.  mc != nullptr: multicast
+// address of S, the sum is formed inside the switch (multimem.ld_reduce / multimem.st).
+// mc == nullptr: `all` lists every rank's S in group-rank order (plain peer loads and stores).
+const char* launch_segment_reduce_bf16(void* mc, const SlotList& all, int64_t elem_off, int64_t rows, int cols,
+                                       bool relu, const void* mask, int64_t ldm, const PeerSync& sync,
+                                       int max_blocks, cudaStream_t stream);
 // symmetric workspace over CUDA IPC (one cudaMalloc per rank, handles exchanged by the caller)
 const char* symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 const char* symm_open(const unsigned char* handle64, void** ptr);

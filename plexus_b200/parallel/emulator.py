@@ -76,6 +76,9 @@ class _Kernels:
     def symm_fill(self, addr: int, byte: int, nbytes: int) -> None:
         ctypes.memset(addr, int(byte), int(nbytes))
 
+    def symm_view(self, addr: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        return _view(addr, numel, dtype)
+
     def symm_free(self, addr: int) -> None:
         shm = self._segments.pop(addr)
         shm.close()
@@ -129,6 +132,27 @@ class _Kernels:
         if mask is not None:
             acc = acc * (mask > 0)
         out.copy_(acc.to(out.dtype))
+
+    def segment_reduce(self, mc_ptr, all_ptrs, me, seg, relu, mask, remote, local, epoch, timeout_ms, kid, status,
+                       max_blocks=0):
+        """Reduce this rank's segment of the symmetric buffer and write the result to every rank
+        (what the switch does for the device kernel: sum of all ranks' partials, one set of bits)."""
+        if not self._signal_and_wait(remote, local, epoch, timeout_ms, kid, status):
+            return
+        rows, cols = seg.shape
+        off = seg.data_ptr() - all_ptrs[me]
+        acc_dtype = torch.float64 if seg.dtype == torch.float64 else torch.float32
+        parts = [_view(a + off, rows * cols, seg.dtype).view(rows, cols) for a in all_ptrs]
+        acc = torch.zeros((rows, cols), dtype=acc_dtype)
+        for t in parts:
+            acc = acc + t.to(acc_dtype)
+        if relu:
+            acc = torch.relu(acc)
+        if mask is not None:
+            acc = acc * (mask > 0)
+        res = acc.to(seg.dtype)
+        for t in parts:
+            t.copy_(res)
 
     def reduce_sentinel(self, out, slot_ptrs, slot_ld, relu, mask, timeout_ms, kid, status, me=-1, max_blocks=0):
         """Flag-free receive side: the slots hold 0xFF bytes where nothing has arrived; wait (bounded)

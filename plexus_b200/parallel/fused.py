@@ -78,6 +78,14 @@ PIPELINE_CHUNKS = int(os.environ.get("PLEXUS_PIPELINE_CHUNKS", "4"))
 PIPELINE_MIN_BYTES = int(os.environ.get("PLEXUS_PIPELINE_MIN_BYTES", str(16 << 20)))
 REDUCE_MAX_BLOCKS = int(os.environ.get("PLEXUS_REDUCE_MAX_BLOCKS", str(148 * 4)))
 IN_KERNEL_REDUCE = os.environ.get("PLEXUS_IN_KERNEL_REDUCE", "0") != "0"
+# Axes of more than two ranks, large messages: the compute kernel writes its partial into a
+# symmetric buffer and a segment-reduce kernel sums it inside the NVSwitch (multimem), see
+# csrc/kernels/nvls_reduce.cu.  The matrix is cut in row chunks; the reduce of chunk i runs on a
+# high-priority side stream (few CTAs) while chunk i + 1 is computed.  PLEXUS_SEGMENT_REDUCE=0 goes
+# back to NCCL after the compute kernel.
+SEGMENT_REDUCE = os.environ.get("PLEXUS_SEGMENT_REDUCE", "1") != "0"
+SEGMENT_CHUNKS = int(os.environ.get("PLEXUS_SEGMENT_CHUNKS", "2"))
+SEGMENT_BLOCKS = int(os.environ.get("PLEXUS_SEGMENT_BLOCKS", "64"))
 ROW_BLOCK_MULTIPLE = 128  # row blocks start on a GEMM tile boundary
 
 
@@ -94,7 +102,7 @@ def _row_blocks(rows: int, row_bytes: int):
 
 # how often each form carried a matrix collective (for tests and the metrics sink)
 op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0, "in_kernel": 0,
-             "pipelined": 0}
+             "pipelined": 0, "segment_reduce": 0}
 
 
 def _skip() -> bool:
@@ -164,7 +172,8 @@ class _SideStream:
         self.on = not emulator.active()
         if self.on:
             if getattr(ax, "_side_stream", None) is None:
-                ax._side_stream = torch.cuda.Stream()
+                # high priority: its few CTAs go first when a compute kernel is queued beside them
+                ax._side_stream = torch.cuda.Stream(priority=-1)
             self.side = ax._side_stream
             self.main = torch.cuda.current_stream()
 
@@ -179,6 +188,63 @@ class _SideStream:
     def join(self):
         if self.on:
             self.main.wait_stream(self.side)
+
+
+def _segment_path(ax, rows: int, cols: int, dtype) -> bool:
+    ok = emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+    return ax.same_host and SEGMENT_REDUCE and not TWO_SHOT and ok and rows >= ax.p
+
+
+def _segment_chunks(rows: int, row_bytes: int):
+    if SEGMENT_CHUNKS <= 1 or rows * row_bytes < PIPELINE_MIN_BYTES:
+        return [(0, rows)]
+    step = -(-(-(-rows // SEGMENT_CHUNKS)) // 128) * 128
+    return [(r, min(rows, r + step)) for r in range(0, rows, step)]
+
+
+def _segment_all_reduce(ax, rows: int, cols: int, like: torch.Tensor, compute, relu, mask, kid):
+    """All-reduce through the axis' symmetric buffer.  ``compute(r0, r1, dst)`` writes the partial
+    rows ``[r0, r1)`` into ``dst`` (a view of the buffer).  Rows are blocked so that the buffer
+    never exceeds ``MAX_MESSAGE_BYTES``."""
+    C = _Backend.load()
+    st = opc.status_buffer(like.device)
+    esz = like.element_size()
+    out = torch.empty((rows, cols), dtype=like.dtype, device=like.device)
+    if mask is not None and mask.dtype != like.dtype:
+        mask = mask.to(like.dtype)
+    blocks = _row_blocks(rows, cols * esz)
+    if len(blocks) > 1:
+        op_counts["row_blocked"] += 1
+    ax.ensure_symmetric(max(b1 - b0 for b0, b1 in blocks) * cols * esz)
+    side = _SideStream(ax)
+    for b0, b1 in blocks:
+        S = ax.symmetric_view(b1 - b0, cols, like.dtype)
+        for c0, c1 in _segment_chunks(b1 - b0, cols * esz):
+            compute(b0 + c0, b0 + c1, S[c0:c1])
+
+            def finish(c0=c0, c1=c1):
+                _seg, ranges = _segment(ax, c1 - c0)
+                s0, n = ranges[ax.rank]
+                epoch, buf = ax.next_op()
+                remote, local = ax.sync(buf)
+                if n:
+                    seg_mask = None if mask is None else mask[b0 + c0 + s0 : b0 + c0 + s0 + n]
+                    C.segment_reduce(ax.sym_mc, ax.sym_ptrs, ax.rank, S[c0 + s0 : c0 + s0 + n], bool(relu), seg_mask,
+                                     remote, local, epoch, ax.timeout_ms, kid, st, SEGMENT_BLOCKS)
+                else:  # more ranks than rows in this chunk: take part in the barrier only
+                    C.gather_segments([], [], [], remote, local, epoch, ax.timeout_ms, kid, st)
+                epoch2, buf2 = ax.next_op()
+                remote2, local2 = ax.sync(buf2)
+                dst = out[b0 + c0 : b0 + c1]
+                C.gather_segments([S[c0:c1].data_ptr()], [dst.data_ptr()], [(c1 - c0) * cols * esz], remote2, local2,
+                                  epoch2, ax.timeout_ms, KID_GATHER, st)
+                opc._count(2)
+
+            side.run(finish)
+        # the next row block reuses the buffer: everything of this one must have been copied out
+        side.join()
+    op_counts["segment_reduce"] += 1
+    return out
 
 
 def _reduce_sentinel(ax, out, slots, slot_ld, relu, mask, kid):
@@ -206,6 +272,10 @@ def spmm_all_reduce(A, H, group, relu_mask=None):
     ax = symm.axis_for(group)
     rows, D = A.shape[0], H.shape[1]
     if not _push_path(ax, rows * D * H.element_size()):
+        if _segment_path(ax, rows, D, H.dtype):
+            return _segment_all_reduce(ax, rows, D, H,
+                                       lambda r0, r1, dst: opc.spmm(A, H, row_range=(r0, r1), out=dst),
+                                       False, relu_mask, KID_SPMM)
         if _two_shot_path(ax, rows, D, H.dtype):
             seg, ranges, epoch, buf = _two_shot_begin(ax, rows, D, H.element_size())
             out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D, push_seg=(seg, ax.rank))
@@ -308,6 +378,11 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
     rows = a.shape[0]
     N = W.shape[0] if trans_b else W.shape[1]
     if not _push_path(ax, rows * N * a.element_size()):
+        if _segment_path(ax, rows, N, a.dtype):
+            return _segment_all_reduce(ax, rows, N, a,
+                                       lambda r0, r1, dst: opc.gemm(a[r0:r1], W, trans_b=trans_b, relu=False,
+                                                                    out=dst),
+                                       relu, None, KID_GEMM)
         if _two_shot_path(ax, rows, N, a.dtype):
             seg, ranges, epoch, buf = _two_shot_begin(ax, rows, N, a.element_size())
             out = opc.gemm(a, W, trans_b=trans_b, relu=False, push_ptrs=ax.push_targets(buf), push_ld=N,
@@ -434,6 +509,11 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
         return t
     ax = symm.axis_for(group)
     if not _push_path(ax, t2.numel() * 2):
+        if _segment_path(ax, t2.shape[0], t2.shape[1], t2.dtype):
+            res = _segment_all_reduce(ax, t2.shape[0], t2.shape[1], t2,
+                                      lambda r0, r1, dst: dst.copy_(t2[r0:r1]), False, None, KID_BARRIER)
+            t2.copy_(res)
+            return t
         if _two_shot_path(ax, t2.shape[0], t2.shape[1], t2.dtype):
             # stand-alone two-shot: scatter the rows to their owners with a copy kernel per peer
             seg, ranges, epoch, buf = _two_shot_begin(ax, t2.shape[0], t2.shape[1], 2)

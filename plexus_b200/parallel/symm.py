@@ -42,6 +42,9 @@ def _device_sync() -> None:
 MAX_GROUP = 8
 FLAG_BYTES = 1024
 DEFAULT_TIMEOUT_MS = 5000.0
+# Bind the symmetric buffers to an NVLink multicast object (in-switch reduction).  Switch it off for
+# runs in which a rank may exit while others still use the buffers (fault-injection tests).
+NVLS = os.environ.get("PLEXUS_NVLS", "1") != "0"
 
 
 class AxisComm:
@@ -69,6 +72,12 @@ class AxisComm:
         self.local_ptr = 0
         self.ptrs: List[int] = []
         self.timeout_ms = DEFAULT_TIMEOUT_MS
+        # symmetric buffer of the segment-reduce form (see ensure_symmetric)
+        self.sym_bytes = 0
+        self.sym_ptrs: List[int] = []  # every rank's buffer, group-rank order
+        self.sym_mc = 0                # multicast address (0: none, plain peer loads / stores)
+        self._sym_tensor = None        # torch symmetric-memory tensor that owns the buffer, or
+        self._sym_local = 0            # the local CUDA-IPC allocation
 
     # -- allocation ---------------------------------------------------------------------
     def ensure(self, slot_bytes: int = 0, sentinel_bytes: int = 0) -> None:
@@ -117,6 +126,91 @@ class AxisComm:
             pass
         C.symm_free(self.local_ptr)
         self.ptrs, self.local_ptr = [], 0
+        self.slot_bytes = self.sslot_bytes = 0
+
+    # -- symmetric buffer (segment-reduce form) ---------------------------------------------
+    def ensure_symmetric(self, nbytes: int) -> None:
+        """One buffer of at least ``nbytes`` at the same offset on every rank of the axis, for the
+        all-reduce that reduces inside the NVSwitch (``csrc/kernels/nvls_reduce.cu``).
+
+        With ``PLEXUS_NVLS`` on (default) the memory comes from torch's symmetric-memory allocator,
+        which maps every peer's buffer and, where the fabric allows it, binds them to one multicast
+        address; the allocator is all that is used of it, the kernels are this package's.  If that
+        fails or with ``PLEXUS_NVLS=0`` the buffer is a CUDA-IPC allocation like the slot workspace
+        and the kernel reduces with plain peer loads and stores.  Collective when it has to grow.
+        """
+        if not self.same_host:
+            raise RuntimeError("peer-memory workspace requested for an axis that spans hosts")
+        if nbytes <= self.sym_bytes and self.sym_ptrs:
+            return
+        size = max(int(nbytes) * 5 // 4, 1 << 21)
+        size = (size + (1 << 21) - 1) >> 21 << 21
+        _device_sync()
+        dist.barrier(group=self.group)
+        self._release_symmetric()
+        C = _C()
+        if not emulator.active() and NVLS:
+            try:
+                import torch.distributed._symmetric_memory as sm
+
+                dev = torch.device("cuda", torch.cuda.current_device())
+                t = sm.empty(size, dtype=torch.uint8, device=dev)
+                h = sm.rendezvous(t, self.group.group_name)
+                self._sym_tensor = t
+                self.sym_ptrs = [int(p) for p in h.buffer_ptrs]
+                self.sym_mc = int(h.multicast_ptr or 0)
+            except Exception as e:  # allocator or fabric refused: the plain peer-memory form below
+                self._sym_tensor, self.sym_ptrs, self.sym_mc = None, [], 0
+                self.sym_error = repr(e)
+            # every rank must take the same route
+            ok = torch.tensor([1 if self.sym_ptrs else 0, 1 if self.sym_mc else 0], dtype=torch.int32,
+                              device=torch.device("cuda", torch.cuda.current_device()))
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            ok = ok.tolist()
+            if not ok[0]:
+                self._sym_tensor, self.sym_ptrs, self.sym_mc = None, [], 0
+            elif not ok[1]:
+                self.sym_mc = 0
+        if not self.sym_ptrs:
+            dev = (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(self.group) == "nccl"
+                   else torch.device("cpu"))
+            ptr, handle = C.symm_alloc(size)
+            mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
+            allh = torch.empty(self.p * 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh, mine, group=self.group)
+            allh = allh.cpu().view(self.p, 64)
+            self.sym_ptrs = [ptr if q == self.rank else C.symm_open(bytes(allh[q].tolist())) for q in range(self.p)]
+            self._sym_local, self.sym_mc = ptr, 0
+        self.sym_bytes = size
+        self.ensure(0)  # the flags
+        _device_sync()
+        dist.barrier(group=self.group)
+
+    def _release_symmetric(self) -> None:
+        if not self.sym_ptrs:
+            return
+        if self._sym_tensor is None:
+            C = _C()
+            for q, ptr in enumerate(self.sym_ptrs):
+                if q != self.rank:
+                    C.symm_close(ptr)
+            try:
+                dist.barrier(group=self.group)
+            except Exception:
+                pass
+            C.symm_free(self._sym_local)
+        self._sym_tensor, self._sym_local = None, 0
+        self.sym_ptrs, self.sym_mc, self.sym_bytes = [], 0, 0
+
+    def symmetric_view(self, rows: int, cols: int, dtype: torch.dtype, byte_off: int = 0) -> torch.Tensor:
+        """``[rows, cols]`` tensor over this rank's symmetric buffer, ``byte_off`` bytes in."""
+        esz = torch.empty(0, dtype=dtype).element_size()
+        n = rows * cols
+        if byte_off + n * esz > self.sym_bytes:
+            raise ValueError("symmetric buffer too small")
+        if self._sym_tensor is not None:
+            return self._sym_tensor[byte_off : byte_off + n * esz].view(dtype).view(rows, cols)
+        return _C().symm_view(self.sym_ptrs[self.rank] + byte_off, n, dtype).view(rows, cols)
 
     # -- addressing ---------------------------------------------------------------------
     def slot(self, owner: int, buf: int, src: int) -> int:
@@ -181,6 +275,7 @@ def teardown() -> None:
         _device_sync()
     for ax in _axes.values():
         try:
+            ax._release_symmetric()
             ax.release()
         except Exception:
             pass

@@ -29,6 +29,7 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
         fused.PIPELINE = flags.get("pipeline", False)
         fused.PIPELINE_MIN_BYTES = flags.get("pipeline_min_bytes", fused.PIPELINE_MIN_BYTES)
         fused.IN_KERNEL_REDUCE = flags.get("in_kernel", False)
+        fused.SEGMENT_REDUCE = flags.get("segment_reduce", False)
     plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
              block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
              tune_gemms=flags.get("tune", False), comm=comm)
@@ -189,6 +190,20 @@ def test_fused_host_code_flag_free_forms(grid, mode):
     run_distributed(_worker, world, grid, 3, True, 300, 10, 5, 12, False,
                     dict(EMU, one_shot_ranks=8, small_bytes=0, pipeline_min_bytes=4096, **{mode: True},
                          expect_ops={"one_shot": True, key: True, "library": False}))
+
+
+@pytest.mark.parametrize("grid,max_bytes", [((1, 1, 4), None), ((1, 4, 1), None), ((4, 2, 1), None), ((1, 1, 8), None),
+                                            ((2, 2, 2), None), ((4, 1, 1), 8000), ((1, 3, 1), None)])
+def test_fused_host_code_segment_reduce_on_a_symmetric_buffer(grid, max_bytes):
+    """Every matrix all-reduce through the symmetric buffer: partials written locally, each rank reduces
+    its row segment and broadcasts it (what the switch does for the multimem kernel), flagged copy out;
+    in row chunks, and in row blocks when the message limit is small."""
+    world = grid[0] * grid[1] * grid[2]
+    flags = dict(EMU, segment_reduce=True, small_bytes=0, one_shot_ranks=1, pipeline_min_bytes=4096,
+                 expect_ops={"segment_reduce": True, "library": False, "two_shot": False})
+    if max_bytes:
+        flags.update(max_message_bytes=max_bytes, row_block_multiple=8)
+    run_distributed(_worker, world, grid, 3, True, 300, 10, 5, 12, False, flags)
 
 
 def test_fused_host_code_default_policy_mixes_push_and_library_paths():

@@ -88,16 +88,23 @@ def test_fused_primitives(world):
     run_gpus(_primitives, world)
 
 
-def _two_shot_ops(rank, world):
-    """Two-shot (reduce-scatter push + reduce/broadcast + landing) all-reduce against fp32 sums."""
+def _two_shot_ops(rank, world, form="two_shot"):
+    """Large-message all-reduce forms against fp32 sums: two-shot (reduce-scatter push +
+    reduce/broadcast + landing), segment (symmetric buffer reduced inside the switch by multimem
+    loads / stores) and segment_p2p (the same kernel on plain peer loads and stores)."""
+    import torch.distributed as dist
+
     import plexus_b200 as plx
     from plexus_b200.data import graph_ops
     from plexus_b200.ops import cuda as opc
-    from plexus_b200.parallel import fused
+    from plexus_b200.parallel import fused, symm
 
     fused.SMALL_MESSAGE_BYTES = 0  # every message takes the large-message path
-    fused.ONE_SHOT_MAX_RANKS = 1   # ... and that path is the two-shot form even on 2 ranks
-    fused.TWO_SHOT = True
+    fused.ONE_SHOT_MAX_RANKS = 1   # ... and that path is the chosen form even on 2 ranks
+    fused.TWO_SHOT = form == "two_shot"
+    fused.SEGMENT_REDUCE = form != "two_shot"
+    fused.PIPELINE_MIN_BYTES = 64 << 10  # row chunks on the larger cases
+    symm.NVLS = form == "segment"
     grid = plx.init(world, 1, 1, comm="fused")
     g = grid.group("x")
     dev = torch.device("cuda", rank)
@@ -105,6 +112,11 @@ def _two_shot_ops(rank, world):
     def close(got, want, tag):
         err = (got.float().cpu() - want).abs().max().item()
         assert err <= 2e-2 * want.abs().max().item() + 1e-3, (tag, err)
+        if form != "two_shot":
+            # one rank reduces a segment and broadcasts the bits: replicas are bitwise equal
+            every = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(every, got.contiguous(), group=g)
+            assert all(torch.equal(every[0], e) for e in every[1:]), (tag, "replicas differ")
 
     # rows not divisible by the group size, an empty last segment (rows=5), interleaved with
     # one-shot ops of the same axis (both kinds share the op counter and the two buffers)
@@ -143,6 +155,10 @@ def _two_shot_ops(rank, world):
         close(fused.all_reduce_bf16(Xs[rank].to(dev).clone(), g), tb, ("bf16", it))
     torch.cuda.synchronize()
     opc.check_status()
+    if form != "two_shot":
+        assert fused.op_counts["segment_reduce"] > 0 and fused.op_counts["library"] == 0, fused.op_counts
+        if form == "segment_p2p":
+            assert symm.axis_for(g).sym_mc == 0
     plx.shutdown()
 
 
@@ -151,6 +167,14 @@ def test_two_shot_all_reduce(world):
     if torch.cuda.device_count() < world:
         pytest.skip("not enough GPUs")
     run_gpus(_two_shot_ops, world)
+
+
+@pytest.mark.parametrize("form", ["segment", "segment_p2p"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_segment_reduce_all_reduce(world, form):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_two_shot_ops, world, form)
 
 
 def _sparse_shard(dense, dev):
@@ -287,7 +311,7 @@ def test_reduce_scatter_row_blocks_and_gather_pieces(world):
     run_gpus(_other_forms, world)
 
 
-def _model(rank, world, grid, layers, force_two_shot=False):
+def _model(rank, world, grid, layers, force_two_shot=False, force_segment=False):
     import plexus_b200 as plx
     from plexus_b200.models.cross_entropy import parallel_cross_entropy
     from plexus_b200.models.net import Net
@@ -301,6 +325,12 @@ def _model(rank, world, grid, layers, force_two_shot=False):
         fused.SMALL_MESSAGE_BYTES = 0
         fused.ONE_SHOT_MAX_RANKS = 1
         fused.TWO_SHOT = True
+    if force_segment:
+        from plexus_b200.parallel import fused
+
+        fused.SMALL_MESSAGE_BYTES = 0
+        fused.ONE_SHOT_MAX_RANKS = 1
+        fused.PIPELINE_MIN_BYTES = 64 << 10
     data, nc = small_processed_graph(n=5000, e=60000, f=100, c=47, seed=9)
     results = {}
     for comm in ("nccl", "fused"):
@@ -342,11 +372,12 @@ def _model(rank, world, grid, layers, force_two_shot=False):
     for ef, en in zip(err["fused"], err["nccl"]):
         assert ef < max(3.0 * en, 0.1), (err["fused"], err["nccl"])
     assert abs(a["loss"] - b["loss"]) < 5e-3 * abs(a["loss"]), (a["loss"], b["loss"])
-    # ... and on 2-rank groups (same number of roundings) the two paths agree closely
-    if max(grid) <= 2:
-        for l in range(layers):
-            assert rel(b["gw"][l], a["gw"][l]) < 3e-2, l
-        assert rel(b["gx"], a["gx"]) < 3e-2
+    # ... and the two paths, which differ only in where the partial sums are rounded, agree closely
+    # (a dropped or doubled contribution on a 4-rank axis is an error of 25 % or more)
+    tol = 3e-2 if max(grid) <= 2 and not force_segment else 6e-2
+    for l in range(layers):
+        assert rel(b["gw"][l], a["gw"][l]) < tol, (l, rel(b["gw"][l], a["gw"][l]))
+    assert rel(b["gx"], a["gx"]) < tol, rel(b["gx"], a["gx"])
     plx.shutdown()
 
 
@@ -361,6 +392,14 @@ def test_fused_model_two_shot_2gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("not enough GPUs")
     run_gpus(_model, 2, (2, 1, 1), 3, True)
+
+
+@pytest.mark.parametrize("world,grid", [(2, (1, 2, 1)), (4, (4, 1, 1)), (4, (1, 2, 2)), (8, (4, 2, 1)), (8, (1, 1, 8))])
+def test_fused_model_segment_reduce(world, grid):
+    """Every matrix all-reduce of the model through the symmetric buffer / in-switch reduction."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    run_gpus(_model, world, grid, 3, False, True)
 
 
 @pytest.mark.parametrize("grid", [(4, 1, 1), (2, 1, 2)])
