@@ -25,9 +25,9 @@ def _fused(t: torch.Tensor) -> bool:
         return False
     if t.is_cuda:
         return True
-    from . import emulator
+    from . import backend
 
-    return emulator.active()
+    return backend.emulated
 
 _bytes_moved = {"gather": 0, "all-reduce": 0, "reduce-scatter": 0}
 

@@ -27,20 +27,18 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import _ext
-from ..ops import cuda as _cuda_ops
-from . import emulator, symm
+from . import backend, symm
 
 
 class _Backend:
-    """Kernels (`C()`) and compute ops (attribute access) of the device, or of the host emulation."""
+    """Kernels (``load()``) and compute ops (attribute access) bound by ``runtime.init``."""
 
     @staticmethod
     def load():
-        return emulator.C if emulator.active() else _ext.load()
+        return backend.C()
 
     def __getattr__(self, name):
-        return getattr(emulator.ops if emulator.active() else _cuda_ops, name)
+        return getattr(backend.ops(), name)
 
 
 opc = _Backend()
@@ -117,7 +115,7 @@ def _push_path(ax, nbytes: int) -> bool:
 
 
 def _two_shot_path(ax, rows: int, cols: int, dtype) -> bool:
-    ok = emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+    ok = backend.emulated or (dtype == torch.bfloat16 and cols % 8 == 0)
     return ax.same_host and TWO_SHOT and ok and rows >= ax.p
 
 
@@ -169,7 +167,7 @@ class _SideStream:
     """The axis' side stream for the overlapped reduces (a no-op on the host emulation)."""
 
     def __init__(self, ax):
-        self.on = not emulator.active()
+        self.on = not backend.emulated
         if self.on:
             if getattr(ax, "_side_stream", None) is None:
                 # high priority: its few CTAs go first when a compute kernel is queued beside them
@@ -191,7 +189,7 @@ class _SideStream:
 
 
 def _segment_path(ax, rows: int, cols: int, dtype) -> bool:
-    ok = emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+    ok = backend.emulated or (dtype == torch.bfloat16 and cols % 8 == 0)
     return ax.same_host and SEGMENT_REDUCE and not TWO_SHOT and ok and rows >= ax.p
 
 
@@ -254,7 +252,7 @@ def _reduce_sentinel(ax, out, slots, slot_ld, relu, mask, kid):
 
 
 def _sentinel_ok(dtype, cols: int) -> bool:
-    return emulator.active() or (dtype == torch.bfloat16 and cols % 8 == 0)
+    return backend.emulated or (dtype == torch.bfloat16 and cols % 8 == 0)
 
 
 def _reduce(ax, out, buf, epoch, relu, mask, kid):
@@ -355,7 +353,7 @@ def spmm_reduce_scatter(A, H, group, relu_mask=None):
         return None
     if not (ax.p <= ONE_SHOT_MAX_RANKS or nbytes <= SMALL_MESSAGE_BYTES or TWO_SHOT):
         return None
-    if not (emulator.active() or (H.dtype == torch.bfloat16 and D % 8 == 0)):
+    if not (backend.emulated or (H.dtype == torch.bfloat16 and D % 8 == 0)):
         return None
     seg, ranges, epoch, buf = _two_shot_begin(ax, rows, D, H.element_size())
     out = opc.spmm(A, H, push_ptrs=ax.push_targets(buf), push_ld=D, push_seg=(seg, ax.rank))
@@ -395,7 +393,7 @@ def gemm_all_reduce(a, W, group, relu=False, trans_b=False):
         dist.all_reduce(out, group=group)
         return torch.relu_(out) if relu else out
     blocks = _row_blocks(rows, N * a.element_size())
-    in_kernel = IN_KERNEL_REDUCE and (emulator.active() or (a.dtype == torch.bfloat16 and N % 8 == 0))
+    in_kernel = IN_KERNEL_REDUCE and (backend.emulated or (a.dtype == torch.bfloat16 and N % 8 == 0))
     if PIPELINE and not in_kernel and len(blocks) == 1 and _sentinel_ok(a.dtype, N):
         esz = a.element_size()
         ax.ensure(sentinel_bytes=rows * N * esz)
@@ -450,7 +448,7 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
         code = 1
     else:
         raise NotImplementedError("fused all-reduce supports SUM and MAX")
-    assert (t.dtype == torch.float32 or emulator.active()) and t.is_contiguous()
+    assert (t.dtype == torch.float32 or backend.emulated) and t.is_contiguous()
     if t.numel() == 0:
         return t
     ax = symm.axis_for(group)
@@ -503,7 +501,7 @@ def all_gather(t: torch.Tensor, group) -> torch.Tensor:
 
 def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
     """In-place SUM all-reduce of a contiguous bf16 matrix whose width is a multiple of 8."""
-    assert (t.dtype == torch.bfloat16 or emulator.active()) and t.is_contiguous()
+    assert (t.dtype == torch.bfloat16 or backend.emulated) and t.is_contiguous()
     t2 = t.view(-1, t.shape[-1]) if t.dim() > 1 else t.view(1, -1)
     if t2.numel() == 0:
         return t
@@ -537,7 +535,7 @@ def all_reduce_bf16(t: torch.Tensor, group) -> torch.Tensor:
 
 def supports(t: torch.Tensor) -> bool:
     """Whether ``t`` can go through the peer-memory all-reduce."""
-    if emulator.active():
+    if backend.emulated:
         return t.is_contiguous() and t.is_floating_point()
     if not t.is_cuda or not t.is_contiguous():
         return False

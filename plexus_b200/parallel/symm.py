@@ -26,17 +26,16 @@ from typing import Dict, List, Optional
 import torch
 import torch.distributed as dist
 
-from ..ops import _ext
-from . import emulator
+from . import backend
 
 
 def _C():
-    """The extension, or its host emulation when that is enabled (CPU ranks, tests)."""
-    return emulator.C if emulator.active() else _ext.load()
+    """The kernels bound by ``runtime.init`` (the extension, or its host emulation in tests)."""
+    return backend.C()
 
 
 def _device_sync() -> None:
-    if not emulator.active():
+    if not backend.emulated:
         torch.cuda.synchronize()
 
 MAX_GROUP = 8
@@ -149,7 +148,7 @@ class AxisComm:
         dist.barrier(group=self.group)
         self._release_symmetric()
         C = _C()
-        if not emulator.active() and NVLS:
+        if not backend.emulated and NVLS:
             try:
                 import torch.distributed._symmetric_memory as sm
 

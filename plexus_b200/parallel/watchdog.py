@@ -72,14 +72,17 @@ class Heartbeat:
         return int(parts[0]), float(parts[1])
 
     def check_peers(self, max_age_s: float, min_step: Optional[int] = None,
-                    missing_is_failure: bool = False) -> None:
+                    missing_is_failure: bool = False, lag_grace_s: float = 0.0) -> None:
         """Raise :class:`PeerFailure` if a peer exited, is stale, or lags behind ``min_step``.
 
+        Stale: the last beat is older than ``max_age_s``.  Lagging: the last published step is below
+        ``min_step`` and that beat is older than ``lag_grace_s`` (a peer that still beats but is stuck
+        on an old step, e.g. in a host-side loop; 0 = any peer below ``min_step`` counts).
         A peer that has not published anything yet is only a failure if ``missing_is_failure``
         (ranks reach their first beat at slightly different times).
         """
         now = time.time()
-        gone, stale = [], []
+        gone, stale, lagging = [], [], []
         for r in range(self.world_size):
             if r == self.rank:
                 continue
@@ -91,12 +94,16 @@ class Heartbeat:
             step, ts = got
             if step < 0:
                 gone.append(r)
-            elif now - ts > max_age_s or (min_step is not None and step < min_step and now - ts > max_age_s):
+            elif now - ts > max_age_s:
                 stale.append(r)
+            elif min_step is not None and step < min_step and now - ts > lag_grace_s:
+                lagging.append(r)
         if gone:
             raise PeerFailure(gone, "announced exit")
         if stale:
             raise PeerFailure(stale, f"sent no heartbeat for more than {max_age_s:.1f} s")
+        if lagging:
+            raise PeerFailure(lagging, f"still below step {min_step} after {lag_grace_s:.1f} s")
 
     def wait_for_peers(self, step: int, timeout_s: float, poll_s: float = 0.05) -> None:
         """Block until every peer reached ``step``; raise :class:`PeerFailure` on exit/timeout."""

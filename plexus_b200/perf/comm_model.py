@@ -20,11 +20,19 @@ all-reduce gradH       depth        N*D/(outer*inner)            bwd layer>0
 all-gather / reduce-scatter cost ``(p-1)/p * M / bw`` and all-reduce twice
 that.  ``machine="perlmutter"`` / ``"frontier"`` with ``version`` v1/v2/v3
 reproduce the reference's bandwidth tables (performance/comm_model.py:26-80)
-and 4-byte elements.  ``machine="b200_nvl8"`` models one NVSwitch box:
-every group sees the same per-GPU port bandwidth whatever its placement, each
-collective pays a launch/latency term, an all-reduce reduced inside the switch
-(NVLS) moves ~M bytes per port independent of p, and elements are 2 bytes
-(bf16).
+and 4-byte elements.  ``machine="b200_nvl8"`` models one NVSwitch box and
+prices the forms this package runs there (``parallel/fused.py``), with 2-byte
+(bf16) elements and the link figures of ``perf/b200_links.json`` (measured;
+``PLEXUS_LINK_MEASUREMENTS`` names another file): every group sees the same
+per-GPU port bandwidth whatever its placement and each collective pays a
+latency term;
+
+* all-reduce on a 2-rank axis - one-shot push: M bytes per port and direction,
+  then a reduce pass of 3 M bytes through HBM;
+* all-reduce on a larger axis - reduced inside the switch (multimem):
+  (1 + 1/p) M bytes per port and direction at the measured switch-reduce rate,
+  then a copy of 2 M bytes through HBM;
+* all-gather / reduce-scatter: (p-1)/p M bytes per port.
 """
 
 from __future__ import annotations
@@ -37,10 +45,34 @@ from .common import DEPTH, INNER, OUTER, split_into_three_powers_of_two  # noqa:
 
 GIB = float(1024**3)
 
-# measured on 8x B200 / NVLink 5: peer copy per direction and all-reduce bus bandwidth
-B200_PORT_GBS = 770.0
-B200_ALLREDUCE_BUS_GBS = 725.0
-B200_LATENCY_US = {1: 0.0, 2: 8.0, 4: 10.0, 8: 12.0}
+
+
+def load_link_measurements(path: str = None) -> dict:
+    """Measured NVLink / NVSwitch figures of the B200 box (``perf/b200_links.json`` by default)."""
+    path = path or os.environ.get("PLEXUS_LINK_MEASUREMENTS") or os.path.join(
+        os.path.dirname(os.path.abspath(__file__)), "b200_links.json")
+    with open(path) as f:
+        m = json.load(f)
+    m["latency_us"] = {int(k): float(v) for k, v in m["latency_us"].items()}
+    return m
+
+
+_LINKS = load_link_measurements()
+B200_PORT_GBS = float(_LINKS["port_gbs"])
+B200_ALLREDUCE_BUS_GBS = float(_LINKS["allreduce_bus_gbs"])
+B200_SWITCH_REDUCE_GBS = float(_LINKS["switch_reduce_port_gbs"])
+B200_HBM_GBS = float(_LINKS["hbm_gbs"])
+B200_LATENCY_US = _LINKS["latency_us"]
+
+
+def b200_all_reduce_seconds(p: int, nbytes: float) -> float:
+    """Time of one all-reduce of ``nbytes`` on a ``p``-rank axis in the form this package uses."""
+    if p <= 1:
+        return 0.0
+    lat = B200_LATENCY_US.get(p, 12.0) * 1e-6
+    if p == 2:
+        return lat + nbytes / (B200_PORT_GBS * 1e9) + 3 * nbytes / (B200_HBM_GBS * 1e9)
+    return lat + (1 + 1 / p) * nbytes / (B200_SWITCH_REDUCE_GBS * 1e9) + 2 * nbytes / (B200_HBM_GBS * 1e9)
 
 
 def get_bw(ip, my, GPUS_PER_NODE, version, machine):
@@ -124,13 +156,11 @@ def compute_config_costs(G, N, D_list, version, machine):
                 if b200:
                     if p == 1:
                         continue
-                    lat = B200_LATENCY_US.get(p, 12.0) * 1e-6
                     if kind == "ar":
-                        # switch-side reduction: ~M bytes in and out per port
-                        t = elems * bytes_per / (B200_ALLREDUCE_BUS_GBS * 1e9) * (2 * (p - 1) / p)
+                        total += b200_all_reduce_seconds(p, elems * bytes_per)
                     else:
-                        t = (p - 1) / p * elems * bytes_per / (B200_PORT_GBS * 1e9)
-                    total += t + lat
+                        lat = B200_LATENCY_US.get(p, 12.0) * 1e-6
+                        total += lat + (p - 1) / p * elems * bytes_per / (B200_PORT_GBS * 1e9)
                 else:
                     f = _ar if kind == "ar" else _ag
                     total += f(p, elems, bw[axis], bytes_per)

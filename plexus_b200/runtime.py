@@ -97,12 +97,16 @@ def init(
     flags.comm = comm if comm is not None else "nccl"
     if flags.comm not in ("nccl", "fused"):
         raise ValueError("comm must be 'nccl' or 'fused'")
-    if flags.comm == "fused" and not use_cuda:
-        from .parallel import emulator
+    from .parallel import backend, emulator
 
-        if not emulator.active():
-            raise ValueError("comm='fused' needs CUDA devices with peer access "
-                             "(or parallel.emulator.enable() to emulate them on CPU ranks)")
+    if flags.comm == "fused" and not use_cuda and not emulator.active():
+        raise ValueError("comm='fused' needs CUDA devices with peer access "
+                         "(or parallel.emulator.enable() to emulate them on CPU ranks)")
+    # the kernels behind the peer-memory collectives are chosen here, once
+    backend.bind(flags.comm == "fused" and emulator.active())
+    if use_cuda and dtype not in (None, torch.bfloat16):
+        raise ValueError("on CUDA devices the model runs in bf16 (fp32 accumulation, fp32 master weights): the "
+                         "tcgen05 GEMMs take bf16 operands only; dtype=torch.float32 is for CPU runs")
     flags.dtype = dtype if dtype is not None else (torch.bfloat16 if use_cuda else torch.float32)
     flags.channel_align = (
         channel_align if channel_align is not None else (8 if use_cuda else 1)
@@ -125,10 +129,10 @@ def check_status() -> None:
     from the step is persisted - a checkpoint above all.
     """
     if flags.comm == "fused":
-        from .parallel import emulator
+        from .parallel import backend
 
-        if emulator.active():
-            emulator.ops.check_status()
+        if backend.emulated:
+            backend.ops().check_status()
             return
     if torch.cuda.is_available():
         from .ops import cuda as _opc
@@ -143,10 +147,10 @@ def inject_status_timeout(kernel_id: int = 99) -> None:
 
     rec = torch.tensor([STATUS_TIMEOUT, kernel_id, 0, 1, 0], dtype=torch.int32)
     if flags.comm == "fused":
-        from .parallel import emulator
+        from .parallel import backend
 
-        if emulator.active():
-            emulator.ops.status_buffer()[:5] = rec
+        if backend.emulated:
+            backend.ops().status_buffer()[:5] = rec
             return
     if torch.cuda.is_available():
         from .ops import cuda as _opc

@@ -31,7 +31,7 @@ setup(
     description="3D-parallel full-graph GCN training for NVIDIA B200 (sm_100a): hand-written CUDA kernels, "
                 "peer-memory collectives over NVLink, the API of hpcgroup/plexus",
     packages=find_packages(include=["plexus_b200", "plexus_b200.*", "plexus", "plexus.*", "performance"]),
-    package_data={"plexus_b200": ["_C.so", "csrc/*.cpp", "csrc/include/*", "csrc/kernels/*.cu"]},
+    package_data={"plexus_b200": ["_C.so", "csrc/*.cpp", "csrc/include/*", "csrc/kernels/*.cu", "perf/*.json"]},
     python_requires=">=3.10",
     install_requires=["torch>=2.5", "numpy"],
     extras_require={"mtx": ["scipy"]},

@@ -196,6 +196,12 @@ def _heartbeat_worker(rank, world, mode):
             with pytest.raises(PeerFailure) as e:
                 hb.wait_for_peers(1, timeout_s=0.6)
             assert e.value.ranks == [1]
+            # the peer's beat of step 0 is fresh enough for the age test but it lags behind step 1:
+            # min_step catches it on its own, after the grace period only
+            hb.check_peers(max_age_s=30, min_step=1, lag_grace_s=30)
+            with pytest.raises(PeerFailure) as e:
+                hb.check_peers(max_age_s=30, min_step=1, lag_grace_s=0.1)
+            assert e.value.ranks == [1] and "below step 1" in str(e.value)
             time.sleep(0.5)
             with pytest.raises(PeerFailure):
                 hb.check_peers(max_age_s=0.3)

@@ -77,6 +77,16 @@ def test_mem_model_golden_and_by_hand():
     assert math.isclose(got, words * 4 / 1024**3, rel_tol=1e-12)
     b = mem_model.compute_config_mem_b200(8, 2449029, 123718280, [100, 128, 128, 47])
     assert b["X2Y2Z2"] < m["X2Y2Z2"]
+    # peer-memory workspaces: by hand for one 2-rank axis (Z: all-gather H0 / reduce-scatter gradH0 of
+    # N*D0/(X*Y) elements, no all-reduce on Z with one layer) - 2 buffers x 2 slots of one rank's piece
+    ws = mem_model.workspace_bytes(1, 1, 2, 1000, [16, 8])
+    assert ws == 1024 + 2 * 2 * (1000 * 16 * 2 / 2)
+    # a 4-rank axis: symmetric buffer (1.25 x message) + small slots; the row-block limit caps it
+    big = mem_model.workspace_bytes(4, 1, 1, 10**7, [128, 128, 128])
+    capped = mem_model.workspace_bytes(4, 1, 1, 10**7, [128, 128, 128], max_message_bytes=64 << 20)
+    assert capped < big and capped <= 1024 + 1.25 * (64 << 20) + 8 * (64 << 20)
+    without = mem_model.compute_config_mem_b200(8, 2449029, 123718280, [100, 128, 128, 47], workspaces=False)
+    assert all(b[k] > without[k] for k in b)
 
 
 def test_chooser_returns_valid_grids_and_respects_memory():
