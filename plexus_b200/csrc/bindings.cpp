@@ -31,7 +31,7 @@ int* status_ptr(const Tensor& status) {
 
 // seg_rows > 0 selects the reduce-scatter push (row r goes only to group rank r / seg_rows).
 plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t seg_rows = 0,
-                           int64_t me = 0) {
+                           int64_t me = 0, int64_t limit_elems = 0, int* status = nullptr) {
   plx::PushTargets p = {};
   TORCH_CHECK(ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS), "too many push targets");
   TORCH_CHECK(seg_rows >= 0 && seg_rows < (1ll << 31) && me >= 0 && me <= static_cast<int64_t>(ptrs.size()),
@@ -41,6 +41,8 @@ plx::PushTargets make_push(const std::vector<int64_t>& ptrs, int64_t ld, int64_t
   p.ld = ld;
   p.seg_rows = static_cast<int>(seg_rows);
   p.me = static_cast<int>(me);
+  p.limit_elems = limit_elems > 0 ? limit_elems : 0;
+  p.status = status;
   return p;
 }
 
@@ -93,7 +95,7 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
                 int64_t num_pieces, const Tensor& long_piece_start, Tensor& long_counter, const Tensor& scratch,
                 const std::vector<int64_t>& push_ptrs, int64_t push_ld, int64_t stages, int64_t push_seg_rows,
                 int64_t push_me, const Tensor& status, const std::vector<int64_t>& red_slots, int64_t red_me,
-                double red_timeout_ms) {
+                double red_timeout_ms, int64_t push_limit_elems) {
   TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && val.is_cuda() && H.is_cuda() && out.is_cuda());
   TORCH_CHECK(rowptr.scalar_type() == at::kInt && col.scalar_type() == at::kInt,
               "spmm: int32 CSR indices required");
@@ -127,7 +129,7 @@ void spmm_items(bool tensor_core, const Tensor& rowptr, const Tensor& col, const
               "spmm: counters must be an int32 CUDA tensor of (long rows + 2) zeros");
   int* counters = long_counter.data_ptr<int>();
   const int num_long = static_cast<int>(long_counter.numel() - 2);
-  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
+  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me, push_limit_elems, status_ptr(status));
   TORCH_CHECK(push_seg_rows == 0 || push_seg_rows * (push.n + 1) >= out.size(0),
               "spmm: row segments do not cover the output");
   plx::TileReduce red = make_tile_reduce(red_slots, red_me, red_timeout_ms);
@@ -158,7 +160,7 @@ void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tenso
              int64_t max_stages, int64_t ctas_limit, int64_t nb_override,
              const std::vector<int64_t>& push_ptrs, int64_t push_ld, const c10::optional<Tensor>& mask,
              int64_t push_seg_rows, int64_t push_me, const std::vector<int64_t>& red_slots, int64_t red_me,
-             double red_timeout_ms) {
+             double red_timeout_ms, int64_t push_limit_elems) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm_nt: bf16 operands required");
@@ -166,7 +168,7 @@ void gemm_nt(const Tensor& A, const Tensor& B, Tensor& C, bool relu, const Tenso
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && A.size(1) == B.size(1));
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1);
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_nt: bad output shape");
-  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me);
+  plx::PushTargets push = make_push(push_ptrs, push_ld, push_seg_rows, push_me, push_limit_elems, status_ptr(status));
   const void* mptr = nullptr;
   int64_t ldm = 0;
   if (mask.has_value() && mask->defined()) {
@@ -199,37 +201,54 @@ void gemm_tn(const Tensor& A, const Tensor& B, Tensor& out, Tensor& scratch, con
                             status_ptr(status), stream()));
 }
 
-void xent_stats(const Tensor& logits, int64_t class_offset, int64_t num_classes, Tensor& rmax,
-                Tensor& rsum) {
-  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
-  TORCH_CHECK(rmax.scalar_type() == at::kFloat && rsum.scalar_type() == at::kFloat &&
-              rmax.numel() == logits.size(0) && rsum.numel() == logits.size(0));
-  c10::cuda::CUDAGuard guard(logits.device());
-  check(plx::launch_xent_stats(dtype_of(logits), logits.data_ptr(), logits.stride(0),
-                               static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
-                               static_cast<int>(class_offset), static_cast<int>(num_classes),
-                               rmax.data_ptr<float>(), rsum.data_ptr<float>(), stream()));
+static const float* opt_f32(const c10::optional<Tensor>& t, int64_t numel, const char* what) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == numel, what);
+  return t->data_ptr<float>();
 }
 
-void xent_loss(const Tensor& logits, const Tensor& target, const Tensor& gmax, const Tensor& gsum,
-               const c10::optional<Tensor>& weight, int64_t row_offset, int64_t class_offset,
-               int64_t num_nodes, Tensor& loss) {
+// stats: fp32 [2, R].  With `target` and `loss` (classes not sharded) the loss is added up as well.
+void xent_stats(const Tensor& logits, int64_t class_offset, int64_t num_classes, Tensor& stats,
+                const c10::optional<Tensor>& target, const c10::optional<Tensor>& weight, int64_t row_offset,
+                int64_t num_nodes, const c10::optional<Tensor>& loss) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
-  TORCH_CHECK(target.scalar_type() == at::kLong && target.numel() == logits.size(0) &&
-              target.is_contiguous());
-  TORCH_CHECK(loss.scalar_type() == at::kFloat && gmax.scalar_type() == at::kFloat &&
-              gsum.scalar_type() == at::kFloat);
-  const float* w = nullptr;
-  if (weight.has_value() && weight->defined()) {
-    TORCH_CHECK(weight->scalar_type() == at::kFloat && weight->numel() == logits.size(0));
-    w = weight->data_ptr<float>();
+  const int64_t R = logits.size(0);
+  TORCH_CHECK(stats.is_cuda() && stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.numel() == 2 * R);
+  const int64_t* tptr = nullptr;
+  float* lptr = nullptr;
+  if (loss.has_value() && loss->defined()) {
+    TORCH_CHECK(target.has_value() && target->defined() && target->is_cuda() && target->scalar_type() == at::kLong &&
+                target->is_contiguous() && target->numel() == R, "xent_stats: int64 targets, one per row");
+    TORCH_CHECK(loss->is_cuda() && loss->scalar_type() == at::kFloat && loss->numel() == 1);
+    tptr = target->data_ptr<int64_t>();
+    lptr = loss->data_ptr<float>();
   }
   c10::cuda::CUDAGuard guard(logits.device());
-  check(plx::launch_xent_loss(dtype_of(logits), logits.data_ptr(), logits.stride(0),
-                              target.data_ptr<int64_t>(), gmax.data_ptr<float>(), gsum.data_ptr<float>(),
-                              w, static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
-                              row_offset, static_cast<int>(class_offset), num_nodes,
-                              loss.data_ptr<float>(), stream()));
+  check(plx::launch_xent_stats(dtype_of(logits), logits.data_ptr(), logits.stride(0), static_cast<int>(R),
+                               static_cast<int>(logits.size(1)), static_cast<int>(class_offset),
+                               static_cast<int>(num_classes), stats.data_ptr<float>(), tptr,
+                               opt_f32(weight, R, "xent_stats: fp32 row weights, one per row"), row_offset,
+                               num_nodes, lptr, stream()));
+}
+
+// pairs: fp32 [P, 2, R] (all class shards, rank order) -> stats [2, R] and the loss.
+void xent_combine(const Tensor& logits, const Tensor& target, const Tensor& pairs,
+                  const c10::optional<Tensor>& weight, int64_t row_offset, int64_t class_offset, int64_t num_nodes,
+                  Tensor& stats, Tensor& loss) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  const int64_t R = logits.size(0);
+  TORCH_CHECK(target.is_cuda() && target.scalar_type() == at::kLong && target.numel() == R && target.is_contiguous());
+  TORCH_CHECK(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 3 &&
+              pairs.size(1) == 2 && pairs.size(2) == R, "xent_combine: statistics must be fp32 [P, 2, R]");
+  TORCH_CHECK(stats.is_cuda() && stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.numel() == 2 * R);
+  TORCH_CHECK(loss.is_cuda() && loss.scalar_type() == at::kFloat && loss.numel() == 1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(plx::launch_xent_combine(dtype_of(logits), logits.data_ptr(), logits.stride(0), target.data_ptr<int64_t>(),
+                                 pairs.data_ptr<float>(), static_cast<int>(pairs.size(0)),
+                                 opt_f32(weight, R, "xent_combine: fp32 row weights, one per row"),
+                                 static_cast<int>(R), static_cast<int>(logits.size(1)), row_offset,
+                                 static_cast<int>(class_offset), num_nodes, stats.data_ptr<float>(),
+                                 loss.data_ptr<float>(), stream()));
 }
 
 void xent_grad(const Tensor& logits, const Tensor& target, const Tensor& gmax, const Tensor& gsum,
@@ -576,7 +595,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tn_parts", &gemm_tn_parts, "number of row splits gemm_tn uses");
   m.def("gemm_tn", &gemm_tn, "C = A^T . B on tcgen05 with split reduction");
   m.def("xent_stats", &xent_stats);
-  m.def("xent_loss", &xent_loss);
+  m.def("xent_combine", &xent_combine);
   m.def("xent_grad", &xent_grad);
   m.def("adam_multi", &adam_multi);
   m.def("relu_bwd", &relu_bwd);

@@ -24,6 +24,11 @@ struct PushTargets {
   int64_t ld;             // leading dimension of the receive slots (elements)
   int seg_rows;           // rows per owner (0 = broadcast every row)
   int me;                 // this rank's position in the group (seg_rows > 0 only)
+  // Debug build of a run (PLEXUS_DEBUG=1): capacity of a receive slot in elements.  A store that
+  // would end beyond it is skipped and recorded in the status words (BOUNDS, kernel, row, column);
+  // 0 switches the check off.
+  int64_t limit_elems;
+  int* status;
 };
 
 // In-kernel all-reduce of a fused "compute + push" kernel (one-shot form): besides pushing its
@@ -91,13 +96,16 @@ const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ld
                            int* status, cudaStream_t stream);
 
 // ---- xent.cu
-const char* launch_xent_stats(int dtype, const void* logits, int64_t ld, int R, int C,
-                              int class_offset, int num_classes, float* rmax, float* rsum,
-                              cudaStream_t stream);
-const char* launch_xent_loss(int dtype, const void* logits, int64_t ld, const int64_t* target,
-                             const float* gmax, const float* gsum, const float* weight, int R, int C,
-                             int64_t row_offset, int class_offset, int64_t num_nodes, float* loss,
-                             cudaStream_t stream);
+// stats[2][R]: per-row (max, sum exp) of this class shard; with `loss` (classes not sharded) the
+// same launch adds up the loss terms.  xent_combine: statistics of all P class shards
+// (pairs[P][2][R]) -> stats[2][R] and the loss terms of the local targets.
+const char* launch_xent_stats(int dtype, const void* logits, int64_t ld, int R, int C, int class_offset,
+                              int num_classes, float* stats, const int64_t* target, const float* weight,
+                              int64_t row_offset, int64_t num_nodes, float* loss, cudaStream_t stream);
+const char* launch_xent_combine(int dtype, const void* logits, int64_t ld, const int64_t* target,
+                                const float* pairs, int P, const float* weight, int R, int C, int64_t row_offset,
+                                int class_offset, int64_t num_nodes, float* stats, float* loss,
+                                cudaStream_t stream);
 const char* launch_xent_grad(int dtype, const void* logits, int64_t ld, const int64_t* target,
                              const float* gmax, const float* gsum, const float* scale, int R, int C,
                              int64_t row_offset, int class_offset, int64_t num_nodes, int num_classes,

@@ -178,4 +178,13 @@ __device__ __forceinline__ void report_status(int* status, int code, int kernel,
   }
 }
 
+// Debug check of a fused-collective store (PushTargets::limit_elems): true if `n` elements at
+// element offset `off` of a receive slot fit; otherwise the store is recorded and must be skipped.
+__device__ __forceinline__ bool push_in_bounds(int64_t limit_elems, int* status, int kernel, int64_t off, int n,
+                                               int64_t row, int col) {
+  if (limit_elems == 0 || (off >= 0 && off + n <= limit_elems)) return true;
+  report_status(status, ST_BOUNDS, kernel, static_cast<int>(row), col, static_cast<int>(off >> 10));
+  return false;
+}
+
 }  // namespace plx

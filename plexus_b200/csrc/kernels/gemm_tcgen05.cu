@@ -351,7 +351,9 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                   for (int p = 1; p < MAX_PEERS; ++p)  // static indices keep the pointers in registers
                     if (idx == p) sel = push.base[p];
-                  dst = static_cast<OutT*>(sel) + static_cast<size_t>(row - owner * push.seg_rows) * push.ld + n0 + col;
+                  const int64_t off = static_cast<int64_t>(row - owner * push.seg_rows) * push.ld + n0 + col;
+                  if (!push_in_bounds(push.limit_elems, push.status, KERNEL_ID_GEMM, off, 8, row, n0 + col)) continue;
+                  dst = static_cast<OutT*>(sel) + off;
                 }
                 *reinterpret_cast<uint4*>(dst) = v[i];
               }
@@ -370,7 +372,9 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < NIT; ++i) {
                   const int row = row0 + i * ROWS_PER_ITER + sub;
-                  if (row < M)
+                  if (row < M &&
+                      push_in_bounds(push.limit_elems, push.status, KERNEL_ID_GEMM,
+                                     static_cast<int64_t>(row) * push.ld + n0 + col, 8, row, n0 + col))
                     *reinterpret_cast<uint4*>(pbase + static_cast<size_t>(i * ROWS_PER_ITER) * push.ld) = v[i];
                 }
               }

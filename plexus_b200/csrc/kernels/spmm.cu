@@ -220,6 +220,9 @@ __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __re
     for (int v = 0; v < VPL; ++v) {
       const int c = (v * LPR + lane) * VN;
       if (c < D) {
+        if (peer != nullptr &&
+            !push_in_bounds(push.limit_elems, push.status, KERNEL_ID_SPMM, slot_row * push.ld + c, VN, orow, c))
+          continue;
         if (mask_row != nullptr) Vec16<T>::mask(acc[v], ldg16(mask_row + c));
         *reinterpret_cast<uint4*>(out_row + c) = Vec16<T>::pack(acc[v]);
       }
@@ -234,6 +237,10 @@ __device__ __forceinline__ void row_store(T* __restrict__ out_row, const T* __re
       const uint4 packed = Vec16<T>::pack(acc[v]);
       *reinterpret_cast<uint4*>(out_row + c) = packed;
       // fused collective: the same row goes straight into the peers' receive slots
+#pragma unroll
+      if (push.n > 0 &&
+          !push_in_bounds(push.limit_elems, push.status, KERNEL_ID_SPMM, orow * push.ld + c, VN, orow, c))
+        continue;
 #pragma unroll
       for (int q = 0; q < MAX_PEERS; ++q)  // static indices keep the pointers in registers
         if (q < push.n)

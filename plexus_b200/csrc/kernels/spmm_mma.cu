@@ -123,13 +123,16 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16* __restrict__ out, int64
       for (int q = 1; q < MAX_PEERS; ++q)
         if (idx == q) sel = push.base[q];
       const int64_t slot_row = orow - static_cast<int64_t>(owner) * push.seg_rows;
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sel) + slot_row * push.ld + c) = packed;
+      if (push_in_bounds(push.limit_elems, push.status, KERNEL_ID_SPMM_MMA, slot_row * push.ld + c, 8, orow, c))
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sel) + slot_row * push.ld + c) = packed;
       return;
     }
     *reinterpret_cast<uint4*>(out + orow * ldo + c) = packed;
     return;
   }
   *reinterpret_cast<uint4*>(out + orow * ldo + c) = packed;
+  if (push.n > 0 && !push_in_bounds(push.limit_elems, push.status, KERNEL_ID_SPMM_MMA, orow * push.ld + c, 8, orow, c))
+    return;
 #pragma unroll
   for (int q = 0; q < MAX_PEERS; ++q)
     if (q < push.n)

@@ -41,19 +41,19 @@ class TensorParallelCrossEntropy(torch.autograd.Function):
         class_offset = grid.coord(class_axis) * logits.shape[1]
 
         logits = logits.contiguous()
-        gmax, gsum = ops.xent_local_stats(logits, class_offset, num_classes)
         if group_size(class_group) > 1:
-            # one exchange over the class axis: every shard's (max, sum exp) pair per row, combined
-            # locally in rank order (so all class shards hold bitwise identical statistics)
-            pairs = coll.all_gather(torch.stack([gmax, gsum]).unsqueeze(0), dim=0, process_group=class_group)
-            lmax, lsum = pairs[:, 0], pairs[:, 1]
-            gmax = lmax.max(dim=0).values
-            # a shard holding only padded classes reports (-inf, 0)
-            finite = torch.where(torch.isinf(lmax), torch.full_like(lmax, -1e30), lmax)
-            gsum = (lsum * torch.exp(finite - gmax)).sum(dim=0)
-        loss = ops.xent_combine_loss(
-            logits, target, gmax, gsum, row_offset, class_offset, num_nodes, row_weight
-        ).reshape(1)
+            # one exchange over the class axis: every shard's (max, sum exp) pair per row; one kernel
+            # combines them in rank order (so all class shards hold bitwise identical statistics)
+            # and adds up the loss terms of the local targets
+            stats, _ = ops.xent_stats(logits, class_offset, num_classes)
+            pairs = coll.all_gather(stats.unsqueeze(0), dim=0, process_group=class_group)
+            stats, loss = ops.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, row_weight)
+        else:
+            # classes not sharded: statistics and loss in one pass over the logits
+            stats, loss = ops.xent_stats(logits, class_offset, num_classes, target, row_offset, num_nodes,
+                                         row_weight)
+        gmax, gsum = stats[0], stats[1]
+        loss = loss.reshape(1)
         # one scalar reduction over both axes (class shards hold disjoint terms)
         coll.all_reduce(loss, class_group)
         coll.all_reduce(loss, row_group)

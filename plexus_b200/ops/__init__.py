@@ -58,6 +58,19 @@ def xent_local_stats(logits, class_offset, num_classes):
     return reference.xent_local_stats(logits, class_offset, num_classes)
 
 
+def xent_stats(logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None):
+    """``(stats [2, R], loss or None)``: per-row (max, sum exp) of this class shard; with ``target``
+    (classes not sharded) the loss comes out of the same pass."""
+    mod = _cuda() if logits.is_cuda else reference
+    return mod.xent_stats(logits, class_offset, num_classes, target, row_offset, num_nodes, weight)
+
+
+def xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight=None):
+    """``pairs [P, 2, R]`` of all class shards -> ``(stats [2, R], loss)`` in one pass."""
+    mod = _cuda() if logits.is_cuda else reference
+    return mod.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight)
+
+
 def xent_combine_loss(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, weight=None):
     if logits.is_cuda:
         return _cuda().xent_combine_loss(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, weight)

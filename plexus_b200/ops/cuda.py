@@ -235,11 +235,18 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
     C.spmm_items(variant == 2, crow, col, val, H, out, relu_mask, r0, sch.items, sch.num_pieces,
                  sch.long_piece_start, sch.long_counter, scratch, list(push_ptrs), int(push_ld), SPMM_MMA_STAGES,
                  int(push_seg[0]), int(push_seg[1]), status_buffer(H.device), list(tr[0]), int(tr[1]),
-                 float(tr[2]))
+                 float(tr[2]), _push_limit(push_ptrs, out))
     _count(-(-H.shape[1] // 256) if variant == 2 else 1)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
     return out
+
+
+def _push_limit(push_ptrs, out) -> int:
+    """Capacity of the receive slots in elements of ``out`` when the push targets carry one (a debug
+    run, see ``parallel.symm.PushList``): the kernels then check every fused-collective store."""
+    nbytes = getattr(push_ptrs, "limit_bytes", 0)
+    return int(nbytes) // out.element_size() if nbytes else 0
 
 
 def _EMPTY_F32(device):
@@ -303,7 +310,7 @@ def gemm(a, b, trans_a=False, trans_b=False, relu=False, out_dtype=None, variant
         relu_mask = relu_mask.to(out.dtype)
     tr = tile_reduce if tile_reduce is not None else ([], 0, 0.0)
     C.gemm_nt(a, bt, out, bool(relu), st, max_stages, ctas, nb, list(push_ptrs), int(push_ld), relu_mask,
-              int(push_seg[0]), int(push_seg[1]), list(tr[0]), int(tr[1]), float(tr[2]))
+              int(push_seg[0]), int(push_seg[1]), list(tr[0]), int(tr[1]), float(tr[2]), _push_limit(push_ptrs, out))
     _count(1)
     return out
 
@@ -315,21 +322,37 @@ def relu_backward(grad, out):
     return res
 
 
-def xent_local_stats(logits, class_offset, num_classes):
+def xent_stats(logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None):
+    """fp32 ``[2, R]`` per-row (max, sum exp) over this rank's classes.  With ``target`` (classes not
+    sharded) the same launch adds up the loss: returns ``(stats, loss)``, else ``(stats, None)``."""
     R = logits.shape[0]
-    rmax = torch.empty(R, dtype=torch.float32, device=logits.device)
-    rsum = torch.empty(R, dtype=torch.float32, device=logits.device)
-    _ext.load().xent_stats(logits, int(class_offset), int(num_classes), rmax, rsum)
+    stats = torch.empty((2, R), dtype=torch.float32, device=logits.device)
+    loss = None if target is None else torch.zeros(1, dtype=torch.float32, device=logits.device)
+    _ext.load().xent_stats(logits, int(class_offset), int(num_classes), stats, target, weight, int(row_offset),
+                           int(num_nodes), loss)
     _count(1)
-    return rmax, rsum
+    return stats, (None if loss is None else loss.reshape(()))
+
+
+def xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight=None):
+    """``pairs`` fp32 ``[P, 2, R]`` (every class shard's statistics) -> ``(stats [2, R], loss)``."""
+    R = logits.shape[0]
+    stats = torch.empty((2, R), dtype=torch.float32, device=logits.device)
+    loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+    _ext.load().xent_combine(logits, target, pairs.contiguous(), weight, int(row_offset), int(class_offset),
+                             int(num_nodes), stats, loss)
+    _count(1)
+    return stats, loss.reshape(())
+
+
+def xent_local_stats(logits, class_offset, num_classes):
+    stats, _ = xent_stats(logits, class_offset, num_classes)
+    return stats[0], stats[1]
 
 
 def xent_combine_loss(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, weight=None):
-    loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
-    _ext.load().xent_loss(logits, target, gmax, gsum, weight, int(row_offset), int(class_offset),
-                          int(num_nodes), loss)
-    _count(1)
-    return loss.reshape(())
+    pairs = torch.stack([gmax.float(), gsum.float()]).unsqueeze(0)
+    return xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight)[1]
 
 
 def xent_grad(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, num_classes, scale,

@@ -75,6 +75,26 @@ def xent_local_stats(logits: torch.Tensor, class_offset: int, num_classes: int):
     return m, s
 
 
+def xent_stats(logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None):
+    """``[2, R]`` statistics and, with ``target`` (classes not sharded), the loss."""
+    m, s = xent_local_stats(logits, class_offset, num_classes)
+    loss = None
+    if target is not None:
+        loss = xent_combine_loss(logits, target, m, s, row_offset, class_offset, num_nodes, weight)
+    return torch.stack([m, s]), loss
+
+
+def xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight=None):
+    """Combine every class shard's (max, sum exp) in rank order; loss terms of the local targets."""
+    lmax, lsum = pairs[:, 0], pairs[:, 1]
+    gmax = lmax.max(dim=0).values
+    # a shard holding only padded classes reports (-inf, 0)
+    finite = torch.where(torch.isinf(lmax), torch.full_like(lmax, -1e30), lmax)
+    gsum = (lsum * torch.exp(finite - gmax)).sum(dim=0)
+    loss = xent_combine_loss(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, weight)
+    return torch.stack([gmax, gsum]), loss
+
+
 def xent_combine_loss(logits, target, gmax, gsum, row_offset, class_offset, num_nodes, weight=None):
     """Sum over local rows of ``-log softmax[target]`` restricted to local classes.
 

@@ -46,6 +46,17 @@ DEFAULT_TIMEOUT_MS = 5000.0
 NVLS = os.environ.get("PLEXUS_NVLS", "1") != "0"
 
 
+# PLEXUS_DEBUG=1: the push epilogues of the SpMM / GEMM kernels check every store into a peer's
+# receive slot against the slot size on the device (reported through the status words).
+DEBUG = os.environ.get("PLEXUS_DEBUG", "0") not in ("", "0")
+
+
+class PushList(list):
+    """Push target addresses plus, in a debug run, the capacity of each target slot in bytes."""
+
+    limit_bytes = 0
+
+
 class AxisComm:
     def __init__(self, group):
         self.group = group
@@ -230,7 +241,9 @@ class AxisComm:
 
     def spush_targets(self, buf: int) -> List[int]:
         """This rank's sentinel slot in every peer's buffer."""
-        return [self.sslot(q, buf, self.rank) for q in self.peers]
+        out = PushList(self.sslot(q, buf, self.rank) for q in self.peers)
+        out.limit_bytes = self.sslot_bytes if DEBUG else 0
+        return out
 
     def tile_reduce(self, buf: int):
         """Argument tuple of the in-kernel all-reduce (see ``ops.cuda.gemm`` / ``ops.cuda.spmm``):
@@ -239,7 +252,9 @@ class AxisComm:
 
     def push_targets(self, buf: int) -> List[int]:
         """This rank's slot in every peer's buffer."""
-        return [self.slot(q, buf, self.rank) for q in self.peers]
+        out = PushList(self.slot(q, buf, self.rank) for q in self.peers)
+        out.limit_bytes = self.slot_bytes if DEBUG else 0
+        return out
 
     def recv_slots(self, buf: int) -> List[int]:
         """Every peer's slot in this rank's buffer."""

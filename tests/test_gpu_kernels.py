@@ -203,7 +203,8 @@ def test_gemm_tn_tcgen05(R, Mw, Nw):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("C,class_offset,num_classes", [(48, 0, 47), (24, 24, 47), (8, 40, 41), (64, 64, 70)])
+@pytest.mark.parametrize("C,class_offset,num_classes", [(48, 0, 47), (24, 24, 47), (8, 40, 41), (64, 64, 70),
+                                                        (172, 0, 172), (300, 0, 290), (5, 0, 5), (44, 44, 60)])
 def test_xent_kernels(dtype, C, class_offset, num_classes):
     from plexus_b200.ops import cuda as opc, reference as ref
 
@@ -228,6 +229,23 @@ def test_xent_kernels(dtype, C, class_offset, num_classes):
                           scale, out_dtype=torch.float32)
     assert g.dtype == dtype
     assert (g.float().cpu() - g_ref).abs().max() <= 1e-2 * g_ref.abs().max() + 1e-7
+    # statistics and loss in one launch (classes not sharded), with row weights
+    w = torch.rand(R)
+    st, l1 = opc.xent_stats(ld, class_offset, num_classes, td, row_offset, num_nodes, w.to(_dev()))
+    st_ref, l1_ref = ref.xent_stats(logits, class_offset, num_classes, target, row_offset, num_nodes, w)
+    assert torch.allclose(st.cpu(), st_ref, rtol=1e-3) and torch.allclose(l1.cpu(), l1_ref, rtol=2e-3)
+    # the combine kernel: three class shards' statistics (one of them empty: (-inf, 0)) -> global + loss
+    pairs = torch.stack([st_ref, torch.stack([m_ref - 1.0, s_ref * 2]),
+                         torch.stack([torch.full_like(m_ref, float("-inf")), torch.zeros_like(s_ref)])])
+    st2, l2 = opc.xent_combine(ld, td, pairs.to(_dev()), row_offset, class_offset, num_nodes, w.to(_dev()))
+    st2_ref, l2_ref = ref.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, w)
+    assert torch.allclose(st2.cpu(), st2_ref, rtol=1e-3) and torch.allclose(l2.cpu(), l2_ref, rtol=2e-3)
+    # rows that are not 16-byte aligned (a column slice of a wider matrix) take the element path
+    if C >= 8:
+        wide = torch.zeros(R, C + 3, dtype=dtype, device=_dev())
+        wide[:, 1 : C + 1] = ld
+        st3, _ = opc.xent_stats(wide[:, 1 : C + 1], class_offset, num_classes)
+        assert torch.allclose(st3.cpu(), st_ref, rtol=1e-3)
 
 
 def test_adam_multi_matches_reference():
@@ -405,3 +423,46 @@ def test_position_keyed_dropout_mask_is_the_same_on_cpu_and_gpu():
     y_gpu.float().sum().backward()
     want = ((y_cpu > 0).float() / 0.75).to(torch.bfloat16)
     assert torch.equal(xg.grad.cpu(), want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op", ["gemm", "spmm"])
+def test_debug_bounds_check_of_the_push_stores(op):
+    """With a slot capacity attached to the push targets (what PLEXUS_DEBUG=1 does) a store that would
+    end beyond the receive slot is skipped and recorded in the status words; nothing faults.  A local
+    buffer stands in for the peer's slot."""
+    from plexus_b200.data import graph_ops
+    from plexus_b200.ops import cuda as opc
+    from plexus_b200.parallel.symm import PushList
+
+    torch.manual_seed(3)
+    rows, K, N = 384, 64, 64
+    slot = torch.full((rows, N), -1.0, dtype=torch.bfloat16, device=_dev())
+    targets = PushList([slot.data_ptr()])
+    targets.limit_bytes = rows // 2 * N * 2  # the slot "ends" after half of the rows
+    if op == "gemm":
+        a = torch.randn(rows, K).to(torch.bfloat16).to(_dev())
+        w = (torch.randn(K, N) / 8).to(torch.bfloat16).to(_dev())
+        out = opc.gemm(a, w, push_ptrs=targets, push_ld=N)
+    else:
+        dense = (torch.rand(rows, 200) < 0.05).float() * torch.randn(rows, 200)
+        sp = dense.to_sparse_coo().coalesce()
+        crow, col, val = graph_ops.coo_to_csr(sp.indices()[0].to(_dev()), sp.indices()[1].to(_dev()),
+                                              sp.values().to(_dev()), rows, 200)
+        A = graph_ops.csr_tensor(crow, col, val, (rows, 200))
+        H = torch.randn(200, N).to(torch.bfloat16).to(_dev())
+        out = opc.spmm(A, H, push_ptrs=targets, push_ld=N)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="BOUNDS"):
+        opc.check_status()
+    assert torch.equal(slot[: rows // 2], out[: rows // 2])           # stores inside the slot went through
+    assert bool((slot[rows // 2 :] == -1).all())                      # the others were skipped
+    opc.check_status()                                                # the record was cleared
+    # with the whole slot as capacity nothing is reported
+    targets.limit_bytes = rows * N * 2
+    if op == "gemm":
+        out = opc.gemm(a, w, push_ptrs=targets, push_ld=N)
+    else:
+        out = opc.spmm(A, H, push_ptrs=targets, push_ld=N)
+    opc.check_status()
+    assert torch.equal(slot, out)
