@@ -14,6 +14,11 @@
 //   * the flagged copy of op e+1 (gather_segments in comm_fused.cu) moves S to the output tensor
 //     once every rank's segment has landed.
 // One rank reduces a segment and broadcasts the bits, so the replicas are bitwise equal.
+// Numerics: the plain form adds the partials in fp32 and rounds once to nearest, like the other
+// forms of this package.  The switch rounds the bf16 sum in its own way: measured on a 2-rank axis
+// the results differ deterministically from the fp32 sum rounded to nearest (a 3-layer GCN's weight
+// gradients then sit 0.07-0.11 from the fp64 oracle in max-norm instead of 0.065-0.11); a library
+// all-reduce that uses the switch adds the same way.  PLEXUS_NVLS=0 selects the plain form.
 // S needs no double buffering: a rank writes the partials of the next op only after the barrier
 // of op e+1, which every rank passes only after it has finished reading the others' S.
 //
@@ -128,6 +133,9 @@ segment_reduce_bf16_kernel(__nv_bfloat16* __restrict__ mc, const SlotList all, i
       }
     }
   }
+  // every thread orders its own stores to the other ranks before the kernel ends: the flag of the
+  // next op is published by another thread of another launch, which must not overtake them
+  __threadfence_system();
 }
 
 const char* launch_segment_reduce_bf16(void* mc, const SlotList& all, int64_t elem_off, int64_t rows, int cols,

@@ -168,6 +168,22 @@ def reduce_grad_async(t: torch.Tensor, process_group=None, scatter: bool = False
         return PendingReduce(t)
     if runtime.flags.skip_collectives:
         return PendingReduce(reduce_scatter(t, 0, process_group) if scatter else t)
+    if _fused(t) and t.is_contiguous() and (t.dtype == torch.float32 or not t.is_cuda):
+        from . import fused
+
+        ax_ok = fused.symm.axis_for(process_group, fused.GRAD_CHANNEL).same_host
+        small = t.numel() * t.element_size() <= fused.SMALL_MESSAGE_BYTES or p <= fused.ONE_SHOT_MAX_RANKS
+        if ax_ok and small and fused.supports(t) and (not scatter or t.shape[0] % p == 0):
+            # peer-memory kernels on their own workspace channel and (untimed runs) a side stream
+            kind = "reduce-scatter" if scatter else "all-reduce"
+            _bytes_moved[kind] += t.numel() * t.element_size()
+            timed = get_timers().enabled
+            if timed:
+                get_timers().start(kind)
+            result, join = fused.reduce_grad_f32(t, process_group, scatter, overlap=not timed)
+            if timed:
+                get_timers().stop(kind)
+            return PendingReduce(result, finish=lambda r, _j=join: (_j(), r)[1])
     if _fused(t) or t.device.type == "cpu" or get_timers().enabled:
         # in-line: peer-memory kernels are stream-ordered already; timed runs keep the
         # collective inside its own timer region

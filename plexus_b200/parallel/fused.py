@@ -466,6 +466,75 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
     return t
 
 
+GRAD_CHANNEL = 1
+_grad_stream = None
+
+
+def reduce_grad_f32(t: torch.Tensor, group, scatter: bool, overlap: bool = True):
+    """Sum a contiguous fp32 gradient over ``group``; with ``scatter`` return this rank's 1/p slice
+    along dim 0 (a view of ``t``), else ``t`` reduced in place.  Returns ``(result, join)``: call
+    ``join()`` before the result is used.
+
+    The reduction has its own workspace channel and, with ``overlap``, runs on a side stream, so the
+    kernels of the rest of the layer's backward - which use the same axis on the main stream - are
+    not held up by it (reference: the asynchronous reduce-scatter at plexus/gcn_conv.py:242-252).
+    The reduce-scatter is direct: each peer gets only the segment it owns ((p-1)/p of the tensor
+    leaves this rank once), then one flagged kernel sums the own segment in place.
+    """
+    global _grad_stream
+    ax = symm.axis_for(group, GRAD_CHANNEL)
+    C = _Backend.load()
+    p, n = ax.p, t.numel()
+    assert t.is_contiguous() and (t.dtype == torch.float32 or backend.emulated)
+    if scatter and t.shape[0] % p:
+        raise ValueError(f"reduce_scatter: leading size {t.shape[0]} not divisible by {p}")
+    esz = t.element_size()
+    use_side = overlap and not backend.emulated
+    if use_side:
+        if _grad_stream is None:
+            _grad_stream = torch.cuda.Stream(priority=-1)
+        main = torch.cuda.current_stream()
+        _grad_stream.wait_stream(main)
+        ctx = torch.cuda.stream(_grad_stream)
+    else:
+        import contextlib
+
+        ctx = contextlib.nullcontext()
+    with ctx:
+        st = opc.status_buffer(t.device)
+        flat = t.view(-1)
+        if scatter:
+            seg = n // p
+            ax.ensure(seg * esz)
+            epoch, buf = ax.next_op()
+            for q in ax.peers:
+                C.push_copy(flat[q * seg : (q + 1) * seg], [ax.slot(q, buf, ax.rank)])
+            own = flat[ax.rank * seg : (ax.rank + 1) * seg]
+            remote, local = ax.sync(buf)
+            C.reduce_slots_f32(own, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_XENT, st,
+                               ax.rank)
+            opc._count(p)
+            result = t[ax.rank * (t.shape[0] // p) : (ax.rank + 1) * (t.shape[0] // p)]
+        else:
+            ax.ensure(n * esz)
+            epoch, buf = ax.next_op()
+            C.push_copy(flat, ax.push_targets(buf))
+            remote, local = ax.sync(buf)
+            C.reduce_slots_f32(flat, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_XENT, st,
+                               ax.rank)
+            opc._count(2)
+            result = t
+    if use_side:
+        side = _grad_stream
+
+        def join(_keep=t):
+            torch.cuda.current_stream().wait_stream(side)
+    else:
+        def join():
+            return None
+    return result, join
+
+
 def all_gather(t: torch.Tensor, group) -> torch.Tensor:
     """Concatenate every rank's contiguous ``t`` along dim 0 (group-rank order)."""
     ax = symm.axis_for(group)

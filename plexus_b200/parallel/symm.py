@@ -266,11 +266,14 @@ class AxisComm:
         return remote, local
 
 
-_axes: Dict[int, AxisComm] = {}
+_axes: Dict[tuple, AxisComm] = {}
 
 
-def axis_for(group) -> AxisComm:
-    key = id(group)
+def axis_for(group, channel: int = 0) -> AxisComm:
+    """The workspace of ``group``.  A *channel* is an independent workspace (own flags, buffers and op
+    counter) on the same group: ops of one channel must be issued and executed in the same order on
+    every rank, so traffic that runs on another stream (the weight-gradient reductions) gets its own."""
+    key = (id(group), channel)
     if key not in _axes:
         _axes[key] = AxisComm(group)
     return _axes[key]
