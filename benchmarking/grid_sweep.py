@@ -81,6 +81,9 @@ def main(argv=None):
             raise SystemExit(f"grid {spec} does not use {world} ranks")
         plx.init(*grid, comm=args.comm if (use_cuda and world > 1) else "nccl", dtype=dtype,
                  device=None if use_cuda else "cpu")
+        from plexus_b200.parallel import fused
+
+        forms_before = dict(fused.op_counts)
         adj, feats, labels, N, F, C = DataLoader(None, args.layers, data=(data, nc)).load()
         model = Net(args.layers, F, args.hidden, C, seed=args.seed)
         opt = FusedAdamW(list(model.parameters()) + [feats], lr=3e-3)
@@ -116,7 +119,10 @@ def main(argv=None):
         model_ms = predict_epoch_ms(grid, args.nodes, nnz, dims)
         rec = {"grid": list(grid), "epoch_ms": round(ms, 3), "model_ms": round(model_ms["total"], 3),
                "model_regions": {k: round(v, 3) for k, v in model_ms.items() if k != "total"},
-               "loss": float(loss.detach()), "comm": args.comm if world > 1 else "none", "nnz": nnz}
+               "loss": float(loss.detach()), "comm": args.comm if world > 1 else "none", "nnz": nnz,
+               # how the matrix collectives were carried (library = NCCL after the compute kernel)
+               "collective_forms": {k: v - forms_before.get(k, 0) for k, v in fused.op_counts.items()
+                                    if v - forms_before.get(k, 0)}}
         results.append(rec)
         if rank == 0:
             print(json.dumps(rec), flush=True)

@@ -1,11 +1,11 @@
 """Pick the grid shape from the cost models.
 
-Grids whose estimated memory exceeds the device are dropped.  ``model="volume"`` (the default, and
-the ranking whose choices have been measured on 1, 2, 4 and 8 GPUs) orders the rest by estimated
-communication time plus the bandwidth-model SpMM time, the reference's way of combining its models;
-``model="epoch"`` (``b200_nvl8`` only) orders them by the per-region epoch-time model of
-``perf/epoch_model.py``, which prices every kernel and collective of the executed schedule with
-measured constants.
+Grids whose estimated memory exceeds the device are dropped.  ``model="epoch"`` (the default on
+``b200_nvl8``) orders the rest by the per-region epoch-time model of ``perf/epoch_model.py``, which
+prices every kernel and collective of the executed schedule with measured constants; on 2 GPUs its
+order 1x2x1 < 2x1x1 < 1x1x2 is the measured one (21.2 / 21.5 / 22.8 ms on the 2.45M-node graph).
+``model="volume"`` orders them by estimated communication time plus the bandwidth-model SpMM time,
+the reference's way of combining its models (it puts 1x1x2 first there).
 """
 
 from __future__ import annotations
@@ -19,7 +19,7 @@ from .mem_model import compute_config_mem_b200
 
 
 def choose_grid(G: int, N: int, NNZ: int, D_list: List[int], machine: str = "b200_nvl8",
-                mem_limit_gb: float = 170.0, model: str = "volume") -> List[Tuple[int, int, int]]:
+                mem_limit_gb: float = 170.0, model: str = "epoch") -> List[Tuple[int, int, int]]:
     """Grids ordered best first."""
     mem = compute_config_mem_b200(G, N, NNZ, D_list)
     if machine == "b200_nvl8" and model == "epoch":

@@ -466,3 +466,46 @@ def test_debug_bounds_check_of_the_push_stores(op):
         out = opc.spmm(A, H, push_ptrs=targets, push_ld=N)
     opc.check_status()
     assert torch.equal(slot, out)
+
+
+@pytest.mark.gpu
+def test_offsets_beyond_two_gib_through_large_row_pitches():
+    """Element offsets above 2^31 bytes in H, the output and the GEMM operands (what a 55M-row shard
+    produces), reached with few rows by giving the matrices a row pitch of 1 MB."""
+    from plexus_b200.data import graph_ops
+    from plexus_b200.ops import cuda as opc
+
+    free, _ = torch.cuda.mem_get_info()
+    if free < 16 << 30:
+        pytest.skip("needs 16 GB of free device memory")
+    torch.manual_seed(11)
+    rows, cols, D, pitch = 2600, 3000, 64, 512 * 1024  # (cols - 1) * pitch * 2 bytes = 3.1 GB
+    dense = (torch.rand(rows, cols) < 0.01).float() * torch.randn(rows, cols)
+    dense[5, :] = torch.randn(cols)  # one long row (pieces)
+    sp = dense.to_sparse_coo().coalesce()
+    crow, col, val = graph_ops.coo_to_csr(sp.indices()[0].to(_dev()), sp.indices()[1].to(_dev()),
+                                          sp.values().to(_dev()), rows, cols)
+    A = graph_ops.csr_tensor(crow, col, val, (rows, cols))
+    Hs = torch.randn(cols, D).to(torch.bfloat16)
+    Hbig = torch.zeros(cols, pitch, dtype=torch.bfloat16, device=_dev())
+    Hbig[:, :D] = Hs.to(_dev())
+    obig = torch.zeros(rows, pitch, dtype=torch.bfloat16, device=_dev())
+    want = dense @ Hs.float()
+    for variant in (1, 2):
+        obig[:, :D].zero_()
+        out = opc.spmm(A, Hbig[:, :D], out=obig[:, :D], variant=variant)
+        assert out.data_ptr() == obig.data_ptr()
+        err = (out.float().cpu() - want).abs().max().item()
+        assert err <= 1e-2 * want.abs().max().item(), (variant, err)
+    assert bool((obig[:, D : D + 64] == 0).all())  # nothing written beside the D columns
+    # GEMM reading A and writing C with the same pitch; the last rows lie beyond 2^31 bytes
+    W = (torch.randn(D, 128) / 8).to(torch.bfloat16)
+    cbig = torch.zeros(rows, pitch, dtype=torch.bfloat16, device=_dev())
+    got = opc.gemm(obig[:, :D], W.to(_dev()), out=cbig[:, :128])
+    ref = obig[:, :D].float().cpu() @ W.float()
+    assert (got.float().cpu() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    # weight gradient (split-K over the rows) from the same strided operands
+    gw = opc.gemm(obig[:, :D], cbig[:, :128], trans_a=True, out_dtype=torch.float32)
+    refw = obig[:, :D].float().cpu().t() @ cbig[:, :128].float().cpu()
+    assert (gw.cpu() - refw).abs().max().item() <= 2e-2 * refw.abs().max().item()
+    opc.check_status()

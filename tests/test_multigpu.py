@@ -34,6 +34,11 @@ def _entry(rank, world, fn, init_file, args, errq):
 
 
 def run_gpus(fn, world, *args, timeout=150):
+    # PLEXUS_TEST_WORLDS=4,8 restricts a run to the cases of those world sizes (a box with 8 GPUs
+    # then does not repeat the 2-GPU cases)
+    only = os.environ.get("PLEXUS_TEST_WORLDS")
+    if only and str(world) not in only.split(","):
+        pytest.skip(f"world size {world} not selected by PLEXUS_TEST_WORLDS")
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     with tempfile.TemporaryDirectory() as d:

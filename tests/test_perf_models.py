@@ -126,10 +126,12 @@ def test_epoch_model_tracks_the_measured_epochs():
 
 def test_chooser_models():
     N, NNZ, D = 2449029, 123717823, [100, 256, 256, 47]
-    # default ranking: the grids that were measured on 2, 4 and 8 GPUs
-    assert chooser.choose_grid(2, N, NNZ, D)[0] == (1, 1, 2)
-    assert chooser.choose_grid(4, N, NNZ, D)[0] == (2, 1, 2)
+    # default (epoch model): on 2 GPUs the measured order 1x2x1 < 2x1x1 < 1x1x2
+    assert chooser.choose_grid(2, N, NNZ, D) == [(1, 2, 1), (2, 1, 1), (1, 1, 2)]
     assert chooser.choose_grid(8, N, NNZ, D)[0] == (2, 2, 2)
-    # the epoch model agrees on 8 GPUs and returns every grid that fits
     ep = chooser.choose_grid(8, N, NNZ, D, model="epoch")
-    assert ep[0] == (2, 2, 2) and len(ep) == 10
+    assert ep[0] == (2, 2, 2) and len(ep) == 10  # every grid that fits
+    # the volume ranking (the reference's way of combining its models)
+    assert chooser.choose_grid(2, N, NNZ, D, model="volume")[0] == (1, 1, 2)
+    assert chooser.choose_grid(4, N, NNZ, D, model="volume")[0] == (2, 1, 2)
+    assert chooser.choose_grid(8, N, NNZ, D, model="volume")[0] == (2, 2, 2)
