@@ -17,7 +17,16 @@
 // Fused collective: gemm_nt's epilogue can store each finished row, besides (or instead of) the
 // local output, into receive slots in other GPUs' memory with plain 16-byte stores over NVLink -
 // to every peer (one-shot all-reduce) or only to the rank that owns the row (the reduce-scatter
-// half of a two-shot all-reduce); see PushTargets and comm_fused.cu for the receive side.
+// half of a two-shot all-reduce); see PushTargets and comm_fused.cu for the receive side.  In a
+// debug run every such store is checked against the slot size first (push_in_bounds).
+//
+// gemm_nt_kernel<OutT, FUSED = true> (320 threads) is a separate instantiation that also finishes
+// the one-shot all-reduce itself: warps 6..9 are reducer warps, one per 32-row quadrant of a tile.
+// An epilogue warp pushes the raw partial (ReLU / mask deferred) and signals its reducer warp
+// through shared memory; the reducer warp waits - bounded - until the peers' partials of those
+// rows have arrived in the sentinel-kept receive slots, adds them in group-rank order, applies
+// ReLU / the mask and stores the final rows (TileReduce, sentinel_reduce.cuh).  Measured slower
+// than the flagged reduce launch (the reduce wants a full grid of threads), so it is opt-in.
 //
 // Reference call sites replaced: plexus/gcn_conv.py:211 (OUT), :237 (gradW), :256 (gradAGG),
 // which go to cuBLAS SGEMM through torch.mm.
