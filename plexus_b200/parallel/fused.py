@@ -190,7 +190,8 @@ class _SideStream:
 
 def _segment_path(ax, rows: int, cols: int, dtype) -> bool:
     ok = backend.emulated or (dtype == torch.bfloat16 and cols % 8 == 0)
-    return ax.same_host and SEGMENT_REDUCE and not TWO_SHOT and ok and rows >= ax.p
+    # fewer rows than ranks is fine: a rank whose segment is empty only takes part in the barriers
+    return ax.same_host and SEGMENT_REDUCE and not TWO_SHOT and ok and rows >= 1
 
 
 def _segment_chunks(rows: int, row_bytes: int):

@@ -206,6 +206,14 @@ def test_fused_host_code_segment_reduce_on_a_symmetric_buffer(grid, max_bytes):
     run_distributed(_worker, world, grid, 3, True, 300, 10, 5, 12, False, flags)
 
 
+def test_segment_reduce_with_fewer_rows_than_ranks():
+    """9 nodes on an 8-rank axis: most ranks own an empty segment and only take part in the barriers."""
+    flags = dict(EMU, segment_reduce=True, small_bytes=0, one_shot_ranks=1,
+                 expect_ops={"segment_reduce": True, "library": False})
+    run_distributed(_worker, 8, (1, 1, 8), 2, True, 9, 3, 2, 4, False, flags)
+    run_distributed(_worker, 8, (8, 1, 1), 2, True, 9, 3, 2, 4, False, flags)
+
+
 def test_fused_host_code_default_policy_mixes_push_and_library_paths():
     """Default thresholds on a 4-rank axis: small messages pushed, large ones reduced by the library."""
     run_distributed(_worker, 4, (4, 1, 1), 2, True, 61, 10, 5, 12, False,
