@@ -236,7 +236,12 @@ def spmm(A, H, relu_mask=None, row_range: Optional[Tuple[int, int]] = None, out_
                  sch.long_piece_start, sch.long_counter, scratch, list(push_ptrs), int(push_ld), SPMM_MMA_STAGES,
                  int(push_seg[0]), int(push_seg[1]), status_buffer(H.device), list(tr[0]), int(tr[1]),
                  float(tr[2]), _push_limit(push_ptrs, out))
-    _count(-(-H.shape[1] // 256) if variant == 2 else 1)
+    if variant == 2:
+        _count(-(-H.shape[1] // 256))
+    else:
+        # the items kernel, plus the launch that sums the pieces of the long rows (the fused
+        # in-kernel form does that inside the one launch)
+        _count(2 if sch.num_pieces and not len(tr[0]) else 1)
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
     return out
