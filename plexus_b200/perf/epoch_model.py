@@ -5,20 +5,22 @@ performance/comm_model.py, comp_model.py, mem_model.py) rank grids without predi
 This model walks the same per-layer schedule the layers execute (``models/gcn_conv.py``) and prices
 every kernel and collective with constants measured on B200 (CUDA events, bf16):
 
-* SpMM: ``nnz * (16.2 ps + 0.0709 ps per byte of a gathered row)`` - a fit through the measured
-  2.84 / 4.20 / 6.48 ms of the 123.7M-nonzero product at 48 / 104 / 256 columns (issue-bound floor
-  per nonzero plus an L2-assisted 14 TB/s gather);
+* SpMM: ``nnz * (14.8 ps + 0.0648 ps per byte of a gathered row)`` - a fit through the measured
+  times of the 123.7M-nonzero product at 48 / 104 / 256 columns (24.1 ms for the six products of an
+  epoch; issue-bound floor per nonzero plus an L2-assisted 15 TB/s gather);
 * tcgen05 GEMMs: operand + result bytes at 0.85 of the measured HBM copy bandwidth;
 * fused all-reduce on a 2-rank axis: the push overlaps the compute kernel
   (``max(compute, bytes / 680 GB/s)``), the slot-reduce kernel moves 3 x message bytes through HBM;
-* larger axes: NCCL after the compute kernel at a measured bus bandwidth of 585 GB/s (NVLS off);
-  messages up to 1 MiB use the one-shot push (latency only);
+* larger axes: segment reduce inside the switch after the compute kernel - ``(1 + 1/p)`` x message
+  bytes per port at the measured 583 GB/s plus the copy out of the symmetric buffer (2 x message
+  bytes through HBM) and two barriers; messages up to 1 MiB use the one-shot push (latency only);
 * all-gather: ``(p-1)/p`` of the gathered bytes at the push rate plus the landing copy;
 * cross-entropy and Adam: measured cost per element;
 * every collective pays a launch + flag latency.
 
 ``predict_epoch_ms`` returns the regions and their sum; ``tests/test_perf_models.py`` pins it to the
-measured epochs (33.2 ms on 1 GPU, 24.95 on 2, 17.5 on 4, 11.04 / 12.85 on 8) within 20 %.
+measured epochs (29.9 ms on 1 GPU; 21.2 / 21.5 / 22.8 on the three 2-GPU grids; 14.65 / 15.53 on
+2x2x1 / 2x1x2; 12.0 on 4x2x1) within 15 %, and to the measured order of the 2- and 4-GPU grids.
 """
 
 from __future__ import annotations
@@ -28,14 +30,14 @@ from typing import Dict, List, Sequence, Tuple
 from .comm_model import load_measured_peaks
 from .common import DEPTH, INNER, OUTER, split_into_three_powers_of_two
 
-SPMM_PS_PER_NNZ = 16.2
-SPMM_PS_PER_BYTE = 0.0709
+SPMM_PS_PER_NNZ = 14.8
+SPMM_PS_PER_BYTE = 0.0648
 GEMM_HBM_FRACTION = 0.85
 PUSH_GBS = 680.0            # achieved rate of epilogue stores into a peer's memory
-NCCL_BUS_GBS = 585.0        # all-reduce bus bandwidth on 4- and 8-rank axes, 512 MB messages
+SWITCH_REDUCE_GBS = 583.0   # per port and direction in the segment reduce (multimem), 512 MB messages
 SMALL_MESSAGE_BYTES = 1 << 20
 COLLECTIVE_LATENCY_MS = 0.02
-XENT_PS_PER_ELEM = 6.8      # 0.8 ms for 2.45M rows x 48 classes
+XENT_PS_PER_ELEM = 2.8      # 0.33 ms for 2.45M rows x 48 classes
 ADAM_PS_PER_ELEM = 4.4      # 1.12 ms for 255M bf16 elements with fp32 master and moments
 ELEM = 2                    # bf16
 
@@ -62,7 +64,8 @@ def _all_reduce_ms(p: int, elems: float, compute_ms: float, hbm_gbs: float) -> T
         reduce_ms = (p + 1) * nbytes / (hbm_gbs * 1e9) * 1e3
         total = max(compute_ms, link) + reduce_ms + COLLECTIVE_LATENCY_MS
     else:
-        total = compute_ms + 2 * (p - 1) / p * nbytes / (NCCL_BUS_GBS * 1e9) * 1e3 + COLLECTIVE_LATENCY_MS
+        total = compute_ms + ((1 + 1 / p) * nbytes / (SWITCH_REDUCE_GBS * 1e9) + 2 * nbytes / (hbm_gbs * 1e9)) * 1e3 \
+            + 2 * COLLECTIVE_LATENCY_MS
     return total, total - compute_ms
 
 
