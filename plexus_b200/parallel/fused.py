@@ -1,20 +1,27 @@
 """Collectives carried out by kernels that store into / load from peer memory over NVLink.
 
-* ``spmm_all_reduce`` / ``gemm_all_reduce``, one-shot form (2-rank axes, small messages): the
-  compute kernel's epilogue writes every result row to the local output *and* into this rank's
-  receive slot on each peer of the axis (plain 16-byte stores, overlapped with the rest of the
-  kernel's work); a second launch publishes a flag, waits for the peers' flags and sums the
-  received partials into the output in fp32 (ReLU / ReLU-derivative mask applied after the sum).
-* two-shot form (opt-in for axes of more than 2 ranks and large messages; by default those are
-  reduced by NCCL after the compute kernel, which measured faster): the output rows are split in one
-  segment per rank.  The compute kernel's epilogue stores each row only where it is reduced:
-  own rows locally, other rows into the owner's receive slot (a reduce-scatter overlapped with
-  the compute, (p-1)/p of the message per rank over NVLink).  The second launch waits, reduces
-  the own segment in fp32, applies ReLU / the mask and stores the result into every peer's
-  receive slot of the next op; a third launch waits and copies the peers' segments into the
-  output (the all-gather half).  Link traffic equals a ring all-reduce, 2 (p-1)/p x message.
-* ``all_reduce_f32`` (SUM / MAX) and ``all_gather``: push-copy kernel + flagged consumer, used
-  for the cross-entropy row statistics, weight shards and weight gradients.
+Matrix all-reduces fused with the kernel that produces the matrix (``spmm_all_reduce`` /
+``gemm_all_reduce``), by axis size and message size:
+
+* one-shot (2-rank axes; any axis for messages up to 1 MiB): the compute kernel's epilogue writes
+  every result row to the local output *and* into this rank's receive slot on each peer of the axis
+  (plain 16-byte stores, overlapped with the rest of the kernel's work); a second launch publishes a
+  flag, waits for the peers' flags and sums the received partials into the output in fp32, in
+  group-rank order (ReLU / ReLU-derivative mask applied after the sum);
+* segment reduce (larger axes, large messages): the compute kernel writes its partial into the
+  axis' symmetric buffer; after a flag barrier every rank reduces its row segment inside the NVSwitch
+  (``multimem.ld_reduce``), applies ReLU / the mask and writes the result to every rank
+  (``multimem.st``); a flagged copy moves the buffer to the output.  In row chunks, the reduce of one
+  chunk on a side stream while the next is computed (``csrc/kernels/nvls_reduce.cu``);
+* two-shot by peer stores (``PLEXUS_TWO_SHOT=1``): the epilogue stores each row only where it is
+  reduced (a reduce-scatter overlapped with the compute), a second launch reduces the own segment and
+  stores it into every peer's receive slot of the next op, a third lands the peers' segments;
+* NCCL after the compute kernel: axes that span hosts, or ``PLEXUS_SEGMENT_REDUCE=0``.
+
+``spmm_reduce_scatter`` keeps only the reduce-scatter half.  ``all_reduce_f32`` (SUM / MAX),
+``all_reduce_bf16`` and ``all_gather`` are push-copy kernel + flagged consumer, used for the
+cross-entropy row statistics, weight shards and small tensors; ``reduce_grad_f32`` reduces weight
+gradients on its own workspace channel and a side stream.
 
 These replace the NCCL calls of ``parallel.collectives`` when ``init(comm="fused")`` is used
 (reference call sites: plexus/gcn_conv.py:177-278, plexus/cross_entropy.py:46-98).
@@ -46,14 +53,14 @@ opc = _Backend()
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
 
 # The one-shot push sends the whole partial result to every peer, (p-1) x M bytes per rank.  For
-# p = 2 that is the minimum.  On larger groups a bandwidth-optimal all-reduce moves 2 (p-1)/p x M;
-# measured on 1M x 256 bf16 (512 MB) messages:
-#     ranks   one-shot   two-shot   NCCL after the compute kernel      (SpMM+AR / GEMM+AR, ms)
-#       4     3.56/2.68  2.63/1.84  2.64/1.59
-#       8     7.32/6.01  3.16/2.72  2.79/1.81
-# so groups of more than two ranks reduce large messages with NCCL after the compute kernel by
-# default, and the two-shot form is opt-in (PLEXUS_TWO_SHOT=1).  Small messages are latency
-# bound and always use the one-shot push.
+# p = 2 that is the minimum.  On larger groups a bandwidth-optimal all-reduce moves 2 (p-1)/p x M
+# and the in-switch reduction (1 + 1/p) x M; measured on 1M x 256 bf16 (512 MB) messages:
+#     ranks   one-shot   two-shot   segment reduce   NCCL after the compute kernel   (SpMM+AR / GEMM+AR, ms)
+#       4     3.18/2.68  2.49/1.84  2.52/1.43        2.54/1.62
+#       8     6.73/6.10  3.12/2.78  2.47/1.41        2.48/1.62
+# so groups of more than two ranks reduce large messages with the segment form by default, and the
+# two-shot form is opt-in (PLEXUS_TWO_SHOT=1).  Small messages are latency bound and always use
+# the one-shot push.
 ONE_SHOT_MAX_RANKS = int(os.environ.get("PLEXUS_ONE_SHOT_MAX_RANKS", "2"))
 SMALL_MESSAGE_BYTES = 1 << 20
 TWO_SHOT = os.environ.get("PLEXUS_TWO_SHOT", "0") != "0"

@@ -14,6 +14,10 @@ recognises arrived bf16 data by itself and puts the sentinel back after use, so 
 neither flags nor fences (``csrc/include/sentinel_reduce.cuh``).  Workspaces grow on demand (a
 collective operation: every rank of the axis asks for the same size at the same point of the
 program).
+
+Beside the slot workspace an axis can own a *symmetric buffer* (``ensure_symmetric``): one
+allocation at the same offset on every rank, bound to an NVLink multicast address where the fabric
+allows it, which the segment-reduce form of the all-reduce works on (``csrc/kernels/nvls_reduce.cu``).
 """
 
 from __future__ import annotations
