@@ -324,3 +324,185 @@ def check_tile_protocol(num_ops: int = 3, p: int = 2, ctas: int = 2, tiles: int 
                     raise RuntimeError("state space larger than max_states")
                 stack.append(n)
     return len(seen)
+
+
+# ------------------------------------------------------------------------------------------------
+# Segment reduce on a symmetric buffer (csrc/kernels/nvls_reduce.cu, parallel/fused.py).
+#
+# Every rank owns ONE buffer S (no double buffering), cut in row chunks, each chunk in one segment per
+# rank.  Per op and chunk c a rank's main stream writes its partial into its own S[c]; its side stream
+# then runs: barrier (flags) - read segment `me` of chunk c from EVERY rank's S (the switch does that
+# for a multimem load) - write the reduced segment into EVERY rank's S - barrier - copy the whole local
+# chunk out.  The main stream meanwhile computes the next chunk and joins the side stream before the
+# next op.  Questions: can the single buffer be overwritten (by the next op's partials, or by a
+# reduced segment) while somebody still reads it, does every read see the right data, can the waits
+# deadlock?  `second_barrier=False` and `join=False` are negative controls.
+def _segment_streams(num_ops: int, p: int, me: int, chunks: int, second_barrier: bool = True,
+                     join: bool = True) -> Tuple[List[Event], List[Event]]:
+    peers = [q for q in range(p) if q != me]
+    main: List[Event] = []
+    side: List[Event] = []
+    epoch = 0
+    for k in range(1, num_ops + 1):
+        if k > 1 and join:
+            main.append(("join", k - 1))
+        for c in range(chunks):
+            main.append(("cwbeg", c, k))
+            main.append(("cwend", c, k))
+            main.append(("ready", c, k))
+            side.append(("sync", c, k))
+            epoch += 1
+            for q in peers:
+                side.append(("flag", q, epoch))
+            side.append(("wait", epoch))
+            for q in range(p):
+                side.append(("prbeg", q, c, k))
+                side.append(("prend", q, c, k))
+            for q in range(p):
+                side.append(("rwbeg", q, c, k))
+                side.append(("rwend", q, c, k))
+            epoch += 1
+            if second_barrier:
+                for q in peers:
+                    side.append(("flag", q, epoch))
+                side.append(("wait", epoch))
+            for s in range(p):
+                side.append(("crbeg", c, s, k))
+                side.append(("crend", c, s, k))
+        side.append(("sdone", k))
+    return main, side
+
+
+def check_segment_protocol(num_ops: int = 2, p: int = 2, chunks: int = 2, second_barrier: bool = True,
+                           join: bool = True, max_states: int = 3_000_000, schedules: int = 0,
+                           seed: int = 0) -> int:
+    """Exhaustive (``schedules == 0``) or random exploration of the segment-reduce protocol.
+
+    Returns the number of distinct states (exhaustive) or of schedules run.  Raises
+    :class:`ProtocolViolation` on a race / wrong data and ``RuntimeError`` on deadlock."""
+    threads = [(r, s) for r in range(p) for s in (0, 1)]  # stream 0 = main, 1 = side
+    progs = []
+    for r in range(p):
+        progs.extend(_segment_streams(num_ops, p, r, chunks, second_barrier, join))
+    n = len(threads)
+
+    # state: pc, cell value {(owner, chunk, seg): ("P" | "R", op)}, busy counters, flags, ready marks, side progress
+    def enabled(pc, flag, ready, sdone, i):
+        if pc[i] >= len(progs[i]):
+            return False
+        ev = progs[i][pc[i]]
+        r = threads[i][0]
+        if ev[0] == "wait":
+            return all(flag.get((r, q), 0) >= ev[1] for q in range(p) if q != r)
+        if ev[0] == "sync":
+            return ready.get((r, ev[1], ev[2]), 0) == 1
+        if ev[0] == "join":
+            return sdone.get(r, 0) >= ev[1]
+        return True
+
+    def apply(pc, val, busy, flag, ready, sdone, i):
+        ev = progs[i][pc[i]]
+        r = threads[i][0]
+        kind = ev[0]
+        if kind == "cwbeg":  # the compute kernel overwrites the whole local chunk with partials of op k
+            _, c, k = ev
+            for s in range(p):
+                cell = (r, c, s)
+                if busy.get(("r",) + cell, 0) or busy.get(("w",) + cell, 0):
+                    raise ProtocolViolation(f"rank {r} op {k} writes its partial of chunk {c} while segment {s} is in use")
+                busy[("w",) + cell] = 1
+        elif kind == "cwend":
+            _, c, k = ev
+            for s in range(p):
+                busy[("w",) + (r, c, s)] = 0
+                val[(r, c, s)] = ("P", k)
+        elif kind == "ready":
+            ready[(r, ev[1], ev[2])] = 1
+        elif kind == "flag":
+            _, owner, e = ev
+            if flag.get((owner, r), 0) >= e:
+                raise ProtocolViolation("flags must increase")
+            flag[(owner, r)] = e
+        elif kind == "prbeg":  # read the partial of segment r of chunk c from rank q's buffer
+            _, q, c, k = ev
+            cell = (q, c, r)
+            if busy.get(("w",) + cell, 0) or val.get(cell) != ("P", k):
+                raise ProtocolViolation(f"rank {r} op {k}: partial of rank {q}, chunk {c} is {val.get(cell)} or being written")
+            busy[("r",) + cell] = busy.get(("r",) + cell, 0) + 1
+        elif kind == "prend":
+            _, q, c, k = ev
+            cell = (q, c, r)
+            if busy.get(("w",) + cell, 0) or val.get(cell) != ("P", k):
+                raise ProtocolViolation(f"rank {r} op {k}: partial of rank {q} changed during the read")
+            busy[("r",) + cell] -= 1
+        elif kind == "rwbeg":  # write the reduced segment r of chunk c into rank q's buffer
+            _, q, c, k = ev
+            cell = (q, c, r)
+            if busy.get(("r",) + cell, 0) or busy.get(("w",) + cell, 0):
+                raise ProtocolViolation(f"rank {r} op {k}: reduced segment written into rank {q}'s chunk {c} while in use")
+            busy[("w",) + cell] = 1
+        elif kind == "rwend":
+            _, q, c, k = ev
+            busy[("w",) + (q, c, r)] = 0
+            val[(q, c, r)] = ("R", k)
+        elif kind == "crbeg":  # copy out: the local chunk must hold the reduced data of op k
+            _, c, s, k = ev
+            cell = (r, c, s)
+            if busy.get(("w",) + cell, 0) or val.get(cell) != ("R", k):
+                raise ProtocolViolation(f"rank {r} op {k}: copies segment {s} of chunk {c} holding {val.get(cell)}")
+            busy[("r",) + cell] = busy.get(("r",) + cell, 0) + 1
+        elif kind == "crend":
+            _, c, s, k = ev
+            cell = (r, c, s)
+            if busy.get(("w",) + cell, 0) or val.get(cell) != ("R", k):
+                raise ProtocolViolation(f"rank {r} op {k}: segment {s} of chunk {c} changed during the copy")
+            busy[("r",) + cell] -= 1
+        elif kind == "sdone":
+            sdone[r] = ev[1]
+        pc[i] += 1
+
+    def freeze(d):
+        return tuple(sorted((k, v) for k, v in d.items() if v))
+
+    def moves(pc, flag, ready, sdone):
+        return [i for i in range(n) if enabled(pc, flag, ready, sdone, i)]
+
+    def done(pc):
+        return all(pc[i] >= len(progs[i]) for i in range(n))
+
+    if schedules:
+        rng = random.Random(seed)
+        for _ in range(schedules):
+            pc, val, busy, flag, ready, sdone = [0] * n, {}, {}, {}, {}, {}
+            weight = [rng.choice((1, 1, 4, 16)) for _ in range(n)]
+            while True:
+                mv = moves(pc, flag, ready, sdone)
+                if not mv:
+                    if not done(pc):
+                        raise RuntimeError(f"deadlock at {pc}")
+                    break
+                apply(pc, val, busy, flag, ready, sdone, rng.choices(mv, [weight[m] for m in mv])[0])
+        return schedules
+
+    start = ([0] * n, {}, {}, {}, {}, {})
+    seen = {(tuple(start[0]), ())}
+    stack = [start]
+    while stack:
+        pc, val, busy, flag, ready, sdone = stack.pop()
+        mv = moves(pc, flag, ready, sdone)
+        if not mv:
+            if not done(pc):
+                raise RuntimeError(f"deadlock at {pc}")
+            continue
+        for i in mv:
+            nxt = (list(pc), dict(val), dict(busy), dict(flag), dict(ready), dict(sdone))
+            apply(*nxt, i)
+            # flags, marks and accesses in progress follow from the program counters; what a cell holds
+            # also depends on the order of the writes to it
+            key = (tuple(nxt[0]), freeze(nxt[1]))
+            if key not in seen:
+                seen.add(key)
+                if len(seen) > max_states:
+                    raise RuntimeError("state space larger than max_states")
+                stack.append(nxt)
+    return len(seen)

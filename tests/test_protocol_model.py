@@ -66,3 +66,33 @@ def test_tile_granular_protocol_needs_double_buffering():
 
     with pytest.raises(ProtocolViolation):
         check_tile_protocol(num_ops=3, p=2, ctas=1, tiles=2, buffers=1)
+
+
+@pytest.mark.parametrize("kw", [dict(num_ops=2, p=2, chunks=2), dict(num_ops=3, p=2, chunks=2),
+                                dict(num_ops=3, p=2, chunks=1), dict(num_ops=2, p=3, chunks=1)])
+def test_segment_reduce_protocol_is_race_and_deadlock_free(kw):
+    """One symmetric buffer per rank, no double buffering: partials written locally, every rank's
+    segment read from all buffers and the reduced segment written into all of them between two flag
+    barriers, copy out after the second; main and side stream per rank.  All interleavings."""
+    from plexus_b200.parallel.protocol_model import check_segment_protocol
+
+    assert check_segment_protocol(**kw) > 500
+
+
+def test_segment_reduce_protocol_random_schedules_on_larger_groups():
+    from plexus_b200.parallel.protocol_model import check_segment_protocol
+
+    assert check_segment_protocol(num_ops=3, p=4, chunks=2, schedules=200, seed=1) == 200
+    assert check_segment_protocol(num_ops=2, p=8, chunks=2, schedules=40, seed=2) == 40
+
+
+def test_segment_reduce_protocol_needs_the_second_barrier_and_the_join():
+    """Negative controls: copying out right after the own segment is written reads a peer's segment
+    too early; computing the next op's partials without joining the side stream overwrites a chunk
+    that is still being reduced."""
+    from plexus_b200.parallel.protocol_model import ProtocolViolation, check_segment_protocol
+
+    with pytest.raises(ProtocolViolation):
+        check_segment_protocol(num_ops=2, p=2, chunks=2, second_barrier=False)
+    with pytest.raises(ProtocolViolation):
+        check_segment_protocol(num_ops=2, p=2, chunks=2, join=False)
