@@ -152,3 +152,30 @@ def test_metrics_sink(tmp_path):
     rec = json.loads(path.read_text().strip())
     assert rec["loss"] == 1.5 and "ts" in rec
     assert max_over_ranks(2.5) == 2.5
+
+
+def test_fused_layer_sweep_plans_cases_and_formats_the_table(capsys):
+    """The sweep driver of the fused-layer benchmark: case list, memory filter, commands, table."""
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarking",
+                        "fused_layer_sweep.py")
+    spec = importlib.util.spec_from_file_location("fused_layer_sweep", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    # 16M rows x degree 512 does not fit one GPU; 1M x 8 x 64 is tiny
+    assert mod.estimate_gb(16_000_000, 512, 1024, 1024, 8) > 180
+    assert mod.estimate_gb(1_000_000, 8, 64, 64, 2) < 3
+    records, skipped = mod.main(["--gpus", "4", "--rows", "1000000,16000000", "--degrees", "8,512", "--widths", "64",
+                                 "--kinds", "rmat", "--dry_run"])
+    out = capsys.readouterr().out
+    assert records == [] and len(skipped) == 1 and skipped[0][0]["rows"] == 16_000_000 and skipped[0][0]["degree"] == 512
+    cmds = [line for line in out.splitlines() if "fused_layer.py" in line]
+    assert len(cmds) == 3 and all("--nproc-per-node=4" in c and "--master-addr 127.0.0.1" in c for c in cmds)
+    assert "--rows 16000000 --degree 8 --width 64" in out
+    table = mod.summarise([{"kind": "rmat", "rows": 1000000, "nnz_per_rank": 32_000_000, "width": 256,
+                            "spmm_fused_ms": 2.471, "spmm_nccl_ms": 2.482, "spmm_fused_fraction_of_roofline": 0.98,
+                            "gemm_fused_ms": 1.406, "gemm_nccl_ms": 1.624, "gemm_fused_fraction_of_roofline": 0.83}])
+    assert "| rmat | 1000000 | 32 | 256 | 2.47 / 2.48 / - | 0.98 | 1.41 / 1.62 / - | 0.83 |" in table
