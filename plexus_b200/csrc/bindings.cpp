@@ -210,7 +210,7 @@ static const float* opt_f32(const c10::optional<Tensor>& t, int64_t numel, const
 // stats: fp32 [2, R].  With `target` and `loss` (classes not sharded) the loss is added up as well.
 void xent_stats(const Tensor& logits, int64_t class_offset, int64_t num_classes, Tensor& stats,
                 const c10::optional<Tensor>& target, const c10::optional<Tensor>& weight, int64_t row_offset,
-                int64_t num_nodes, const c10::optional<Tensor>& loss) {
+                int64_t num_nodes, const c10::optional<Tensor>& loss, const std::vector<int64_t>& push_ptrs) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
   const int64_t R = logits.size(0);
   TORCH_CHECK(stats.is_cuda() && stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.numel() == 2 * R);
@@ -223,32 +223,40 @@ void xent_stats(const Tensor& logits, int64_t class_offset, int64_t num_classes,
     tptr = target->data_ptr<int64_t>();
     lptr = loss->data_ptr<float>();
   }
+  TORCH_CHECK(push_ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS), "xent_stats: too many push targets");
+  plx::SlotList push = make_slots(push_ptrs);
   c10::cuda::CUDAGuard guard(logits.device());
   check(plx::launch_xent_stats(dtype_of(logits), logits.data_ptr(), logits.stride(0), static_cast<int>(R),
                                static_cast<int>(logits.size(1)), static_cast<int>(class_offset),
                                static_cast<int>(num_classes), stats.data_ptr<float>(), tptr,
                                opt_f32(weight, R, "xent_stats: fp32 row weights, one per row"), row_offset,
-                               num_nodes, lptr, stream()));
+                               num_nodes, lptr, stream(), &push));
 }
 
-// pairs: fp32 [P, 2, R] (all class shards, rank order) -> stats [2, R] and the loss.
-void xent_combine(const Tensor& logits, const Tensor& target, const Tensor& pairs,
+// pair_ptrs[q]: device address of class shard q's statistics (fp32 [2, R]), rank order -> stats [2, R]
+// and the loss.  With flag lists the kernel first runs the flag barrier of op `epoch` (the pairs were
+// pushed into this rank's receive slots by the peers' xent_stats launches).
+void xent_combine(const Tensor& logits, const Tensor& target, const std::vector<int64_t>& pair_ptrs,
                   const c10::optional<Tensor>& weight, int64_t row_offset, int64_t class_offset, int64_t num_nodes,
-                  Tensor& stats, Tensor& loss) {
+                  Tensor& stats, Tensor& loss, const std::vector<int64_t>& remote_flags,
+                  const std::vector<int64_t>& local_flags, int64_t epoch, double timeout_ms, const Tensor& status) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
   const int64_t R = logits.size(0);
   TORCH_CHECK(target.is_cuda() && target.scalar_type() == at::kLong && target.numel() == R && target.is_contiguous());
-  TORCH_CHECK(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 3 &&
-              pairs.size(1) == 2 && pairs.size(2) == R, "xent_combine: statistics must be fp32 [P, 2, R]");
+  TORCH_CHECK(pair_ptrs.size() >= 1 && pair_ptrs.size() <= static_cast<size_t>(plx::MAX_PEERS + 1),
+              "xent_combine: statistics of 1 to 8 class shards");
+  for (int64_t p : pair_ptrs) TORCH_CHECK(p != 0 && p % 4 == 0, "xent_combine: bad statistics address");
   TORCH_CHECK(stats.is_cuda() && stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.numel() == 2 * R);
   TORCH_CHECK(loss.is_cuda() && loss.scalar_type() == at::kFloat && loss.numel() == 1);
   c10::cuda::CUDAGuard guard(logits.device());
+  plx::PeerSync sync = {};
+  const bool flagged = !remote_flags.empty();
+  if (flagged) sync = make_sync(remote_flags, local_flags, epoch, timeout_ms, /*kernel_id=*/5, status);
   check(plx::launch_xent_combine(dtype_of(logits), logits.data_ptr(), logits.stride(0), target.data_ptr<int64_t>(),
-                                 pairs.data_ptr<float>(), static_cast<int>(pairs.size(0)),
-                                 opt_f32(weight, R, "xent_combine: fp32 row weights, one per row"),
+                                 make_slots(pair_ptrs), opt_f32(weight, R, "xent_combine: fp32 row weights, one per row"),
                                  static_cast<int>(R), static_cast<int>(logits.size(1)), row_offset,
                                  static_cast<int>(class_offset), num_nodes, stats.data_ptr<float>(),
-                                 loss.data_ptr<float>(), stream()));
+                                 loss.data_ptr<float>(), stream(), flagged ? &sync : nullptr));
 }
 
 void xent_grad(const Tensor& logits, const Tensor& target, const Tensor& gmax, const Tensor& gsum,

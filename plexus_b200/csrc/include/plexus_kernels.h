@@ -99,13 +99,18 @@ const char* launch_gemm_tn(const void* A, int64_t lda, const void* B, int64_t ld
 // stats[2][R]: per-row (max, sum exp) of this class shard; with `loss` (classes not sharded) the
 // same launch adds up the loss terms.  xent_combine: statistics of all P class shards
 // (pairs[P][2][R]) -> stats[2][R] and the loss terms of the local targets.
+struct SlotList;
+struct PeerSync;
+// push: optional receive slots ([2][R] floats each) of this rank on the peers of the class axis.
 const char* launch_xent_stats(int dtype, const void* logits, int64_t ld, int R, int C, int class_offset,
                               int num_classes, float* stats, const int64_t* target, const float* weight,
-                              int64_t row_offset, int64_t num_nodes, float* loss, cudaStream_t stream);
+                              int64_t row_offset, int64_t num_nodes, float* loss, cudaStream_t stream,
+                              const SlotList* push = nullptr);
+// pairs.ptr[q]: statistics [2][R] of class shard q, rank order.  sync: optional flag barrier first.
 const char* launch_xent_combine(int dtype, const void* logits, int64_t ld, const int64_t* target,
-                                const float* pairs, int P, const float* weight, int R, int C, int64_t row_offset,
+                                const SlotList& pairs, const float* weight, int R, int C, int64_t row_offset,
                                 int class_offset, int64_t num_nodes, float* stats, float* loss,
-                                cudaStream_t stream);
+                                cudaStream_t stream, const PeerSync* sync = nullptr);
 const char* launch_xent_grad(int dtype, const void* logits, int64_t ld, const int64_t* target,
                              const float* gmax, const float* gsum, const float* scale, int R, int C,
                              int64_t row_offset, int class_offset, int64_t num_nodes, int num_classes,

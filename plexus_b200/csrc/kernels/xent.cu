@@ -8,6 +8,11 @@
 //                  fall in this rank's class range (one launch instead of a chain of tensor ops)
 //   xent_grad    : (exp(l - gmax)/gsum - onehot) * scale on valid rows, 0 elsewhere
 //
+// Exchange inside the kernels (opt-in, parallel/fused.py:xent_exchange_combine): xent_stats also
+// stores each row's pair into this rank's receive slot on every peer of the class axis, and
+// xent_combine starts with the flag barrier of that op and reads the peers' pairs straight from its
+// receive slots - two launches for the whole sharded forward, no copy kernels in between.
+//
 // A row is handled by a group of LPR lanes (a power of two, several rows per warp) that reads and
 // writes 16-byte vectors, so narrow class shards (C = 8..64) keep the accesses coalesced; rows
 // whose address is not 16-byte aligned are read element by element.  Neither a softmax nor a
@@ -20,6 +25,7 @@
 
 #include <algorithm>
 
+#include "../include/peer_sync.cuh"
 #include "../include/plexus_kernels.h"
 
 namespace plx {
@@ -109,7 +115,8 @@ template <typename T>
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_stats_kernel(const T* __restrict__ logits, int64_t ld, int R, int C, int class_offset, int num_classes,
                   int lpr, float* __restrict__ stats, const int64_t* __restrict__ target,
-                  const float* __restrict__ weight, int64_t row_offset, int64_t num_nodes, float* __restrict__ loss) {
+                  const float* __restrict__ weight, int64_t row_offset, int64_t num_nodes, float* __restrict__ loss,
+                  const SlotList push) {
   constexpr int N = XVec<T>::N;
   const int rows_per_block = XENT_THREADS / lpr;
   const int li = threadIdx.x & (lpr - 1), gi = threadIdx.x / lpr;
@@ -146,6 +153,14 @@ xent_stats_kernel(const T* __restrict__ logits, int64_t ld, int R, int C, int cl
     if (live && li == 0) {
       stats[row] = m;
       stats[R + row] = s;
+#pragma unroll
+      for (int q = 0; q < MAX_PEERS; ++q) {  // the same pair into this rank's slot on every peer
+        if (q < push.n) {
+          float* dst = static_cast<float*>(push.ptr[q]);
+          dst[row] = m;
+          dst[R + row] = s;
+        }
+      }
       if (loss != nullptr) {
         const int64_t t = target[row];
         const int64_t local = t - class_offset;
@@ -160,22 +175,37 @@ xent_stats_kernel(const T* __restrict__ logits, int64_t ld, int R, int C, int cl
   if (loss != nullptr) block_add(acc, loss);
 }
 
-// pairs[P][2][R] (every class shard's statistics, rank order) -> stats[2][R] and the loss terms.
+// pairs.ptr[q] = class shard q's statistics [2][R] (rank order; the local buffer, a gathered tensor
+// or this rank's receive slots) -> stats[2][R] and the loss terms.  sync.n > 0: first the flag
+// barrier of the op that pushed the pairs.
 template <typename T>
 __global__ void __launch_bounds__(256)
 xent_combine_kernel(const T* __restrict__ logits, int64_t ld, const int64_t* __restrict__ target,
-                    const float* __restrict__ pairs, int P, const float* __restrict__ weight, int R, int C,
+                    const SlotList pairs, const float* __restrict__ weight, int R, int C,
                     int64_t row_offset, int class_offset, int64_t num_nodes, float* __restrict__ stats,
-                    float* __restrict__ loss) {
+                    float* __restrict__ loss, const PeerSync sync) {
+  if (sync.n > 0 && !signal_and_wait(sync)) return;
+  const int P = pairs.n;
   float acc = 0.f;
   for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < R; row += gridDim.x * blockDim.x) {
+    // static indices keep the pointer list in registers (a run-time index would copy it to local memory)
+    float mq[MAX_PEERS + 1], sq[MAX_PEERS + 1];
     float m = -INFINITY;
-    for (int q = 0; q < P; ++q) m = fmaxf(m, pairs[(static_cast<int64_t>(q) * 2) * R + row]);
-    float s = 0.f;
-    for (int q = 0; q < P; ++q) {
-      const float mq = pairs[(static_cast<int64_t>(q) * 2) * R + row];
-      if (mq != -INFINITY) s += pairs[(static_cast<int64_t>(q) * 2 + 1) * R + row] * __expf(mq - m);
+#pragma unroll
+    for (int q = 0; q <= MAX_PEERS; ++q) {
+      mq[q] = -INFINITY;
+      sq[q] = 0.f;
+      if (q < P) {
+        const float* pq = static_cast<const float*>(pairs.ptr[q]);
+        mq[q] = pq[row];
+        sq[q] = pq[R + row];
+      }
+      m = fmaxf(m, mq[q]);
     }
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q <= MAX_PEERS; ++q)  // rank order
+      if (q < P && mq[q] != -INFINITY) s += sq[q] * __expf(mq[q] - m);
     stats[row] = m;
     stats[R + row] = s;
     const int64_t t = target[row];
@@ -236,36 +266,45 @@ static int grid_for(int64_t work_items, int threads, int cap = 148 * 16) {
 
 const char* launch_xent_stats(int dtype, const void* logits, int64_t ld, int R, int C, int class_offset,
                               int num_classes, float* stats, const int64_t* target, const float* weight,
-                              int64_t row_offset, int64_t num_nodes, float* loss, cudaStream_t stream) {
+                              int64_t row_offset, int64_t num_nodes, float* loss, cudaStream_t stream,
+                              const SlotList* push_in) {
   if (R == 0) return nullptr;
   if (loss != nullptr && target == nullptr) return "xent_stats: the loss needs the targets";
+  SlotList push = {};
+  if (push_in != nullptr) push = *push_in;
+  if (push.n < 0 || push.n > MAX_PEERS) return "xent_stats: too many push targets";
   const int lpr = lanes_per_row_host(C, dtype == DT_BF16 ? 8 : 4);
   const int blocks = grid_for(static_cast<int64_t>(R) * lpr, XENT_THREADS);
   if (dtype == DT_BF16)
     xent_stats_kernel<<<blocks, XENT_THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, R, C,
                                                            class_offset, num_classes, lpr, stats, target, weight,
-                                                           row_offset, num_nodes, loss);
+                                                           row_offset, num_nodes, loss, push);
   else
     xent_stats_kernel<<<blocks, XENT_THREADS, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, R, C,
                                                            class_offset, num_classes, lpr, stats, target, weight,
-                                                           row_offset, num_nodes, loss);
+                                                           row_offset, num_nodes, loss, push);
   return last_launch_error();
 }
 
 const char* launch_xent_combine(int dtype, const void* logits, int64_t ld, const int64_t* target,
-                                const float* pairs, int P, const float* weight, int R, int C, int64_t row_offset,
+                                const SlotList& pairs, const float* weight, int R, int C, int64_t row_offset,
                                 int class_offset, int64_t num_nodes, float* stats, float* loss,
-                                cudaStream_t stream) {
-  if (R == 0) return nullptr;
-  if (P < 1) return "xent_combine: no statistics";
-  const int blocks = grid_for(R, 256, 148 * 8);
+                                cudaStream_t stream, const PeerSync* sync_in) {
+  if (R == 0 && sync_in == nullptr) return nullptr;
+  if (pairs.n < 1 || pairs.n > MAX_PEERS + 1) return "xent_combine: 1 to 8 sets of statistics";
+  for (int q = 0; q < pairs.n; ++q)
+    if (pairs.ptr[q] == nullptr) return "xent_combine: missing statistics";
+  PeerSync sync = {};
+  if (sync_in != nullptr) sync = *sync_in;
+  if (sync.n < 0 || sync.n > MAX_PEERS) return "xent_combine: bad flag lists";
+  const int blocks = grid_for(std::max(R, 1), 256, 148 * 8);
   if (dtype == DT_BF16)
     xent_combine_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, target, pairs,
-                                                    P, weight, R, C, row_offset, class_offset, num_nodes, stats,
-                                                    loss);
+                                                    weight, R, C, row_offset, class_offset, num_nodes, stats, loss,
+                                                    sync);
   else
-    xent_combine_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, target, pairs, P,
-                                                    weight, R, C, row_offset, class_offset, num_nodes, stats, loss);
+    xent_combine_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, target, pairs, weight,
+                                                    R, C, row_offset, class_offset, num_nodes, stats, loss, sync);
   return last_launch_error();
 }
 

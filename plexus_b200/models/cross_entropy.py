@@ -23,7 +23,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from .. import ops
+from .. import ops, runtime
 from ..parallel import collectives as coll
 from ..parallel.grid import get_grid, group_size, loss_axes
 from ..utils.timers import get_timers
@@ -45,9 +45,19 @@ class TensorParallelCrossEntropy(torch.autograd.Function):
             # one exchange over the class axis: every shard's (max, sum exp) pair per row; one kernel
             # combines them in rank order (so all class shards hold bitwise identical statistics)
             # and adds up the loss terms of the local targets
-            stats, _ = ops.xent_stats(logits, class_offset, num_classes)
-            pairs = coll.all_gather(stats.unsqueeze(0), dim=0, process_group=class_group)
-            stats, loss = ops.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, row_weight)
+            res = None
+            if runtime.flags.comm == "fused" and not runtime.flags.skip_collectives:
+                from ..parallel import fused
+
+                if fused.XENT_EXCHANGE:
+                    # the two kernels exchange the pairs themselves (push + flagged read)
+                    res = fused.xent_exchange_combine(logits, target, class_offset, num_classes, row_offset,
+                                                      num_nodes, row_weight, class_group)
+            if res is None:
+                stats, _ = ops.xent_stats(logits, class_offset, num_classes)
+                pairs = coll.all_gather(stats.unsqueeze(0), dim=0, process_group=class_group)
+                res = ops.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, row_weight)
+            stats, loss = res
         else:
             # classes not sharded: statistics and loss in one pass over the logits
             stats, loss = ops.xent_stats(logits, class_offset, num_classes, target, row_offset, num_nodes,

@@ -327,25 +327,41 @@ def relu_backward(grad, out):
     return res
 
 
-def xent_stats(logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None):
+def xent_stats(logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None,
+               push_ptrs=()):
     """fp32 ``[2, R]`` per-row (max, sum exp) over this rank's classes.  With ``target`` (classes not
-    sharded) the same launch adds up the loss: returns ``(stats, loss)``, else ``(stats, None)``."""
+    sharded) the same launch adds up the loss: returns ``(stats, loss)``, else ``(stats, None)``.
+    ``push_ptrs``: this rank's receive slots (``[2, R]`` floats) on the peers of the class axis; the
+    kernel stores every pair there as well."""
     R = logits.shape[0]
     stats = torch.empty((2, R), dtype=torch.float32, device=logits.device)
     loss = None if target is None else torch.zeros(1, dtype=torch.float32, device=logits.device)
     _ext.load().xent_stats(logits, int(class_offset), int(num_classes), stats, target, weight, int(row_offset),
-                           int(num_nodes), loss)
+                           int(num_nodes), loss, list(push_ptrs))
     _count(1)
     return stats, (None if loss is None else loss.reshape(()))
 
 
 def xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight=None):
     """``pairs`` fp32 ``[P, 2, R]`` (every class shard's statistics) -> ``(stats [2, R], loss)``."""
+    pairs = pairs.contiguous()
+    R = logits.shape[0]
+    ptrs = [pairs.data_ptr() + q * 2 * R * 4 for q in range(pairs.shape[0])]
+    return xent_combine_ptrs(logits, target, ptrs, row_offset, class_offset, num_nodes, weight, _keep=pairs)
+
+
+def xent_combine_ptrs(logits, target, pair_ptrs, row_offset, class_offset, num_nodes, weight=None, sync=None,
+                      like=None, _keep=None):
+    """Like :func:`xent_combine` with the statistics given by device address (rank order).
+    ``sync = (remote flags, local flags, epoch, timeout_ms)``: the kernel starts with that flag
+    barrier (the pairs were pushed into this rank's receive slots)."""
     R = logits.shape[0]
     stats = torch.empty((2, R), dtype=torch.float32, device=logits.device)
     loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
-    _ext.load().xent_combine(logits, target, pairs.contiguous(), weight, int(row_offset), int(class_offset),
-                             int(num_nodes), stats, loss)
+    remote, local, epoch, timeout_ms = sync if sync is not None else ([], [], 0, 0.0)
+    _ext.load().xent_combine(logits, target, [int(p) for p in pair_ptrs], weight, int(row_offset), int(class_offset),
+                             int(num_nodes), stats, loss, list(remote), list(local), int(epoch), float(timeout_ms),
+                             status_buffer(logits.device))
     _count(1)
     return stats, loss.reshape(())
 

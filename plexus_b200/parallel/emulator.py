@@ -317,6 +317,33 @@ class _Ops:
 
         return reference.relu_backward(grad, out)
 
+    # -- cross-entropy with the exchange inside the kernels -------------------------------------
+    def xent_stats(self, logits, class_offset, num_classes, target=None, row_offset=0, num_nodes=0, weight=None,
+                   push_ptrs=()):
+        from ..ops import reference
+
+        stats, loss = reference.xent_stats(logits, class_offset, num_classes, target, row_offset, num_nodes, weight)
+        stats = stats.contiguous()
+        for a in push_ptrs:  # the kernel stores every pair into this rank's slot on each peer as well
+            _copy(a, stats)
+        self._count(1)
+        return stats, loss
+
+    def xent_combine_ptrs(self, logits, target, pair_ptrs, row_offset, class_offset, num_nodes, weight=None,
+                          sync=None, like=None):
+        """``like``: a statistics tensor of this rank (gives dtype and row count of the pairs)."""
+        from ..ops import reference
+
+        if sync is not None:
+            remote, local, epoch, timeout_ms = sync
+            if not C._signal_and_wait(remote, local, epoch, timeout_ms, 5, self.status_buffer()):
+                R = logits.shape[0]
+                return torch.zeros((2, R), dtype=like.dtype), torch.zeros((), dtype=like.dtype)
+        R = logits.shape[0]
+        pairs = torch.stack([_view(a, 2 * R, like.dtype).view(2, R).clone() for a in pair_ptrs])
+        self._count(1)
+        return reference.xent_combine(logits, target, pairs, row_offset, class_offset, num_nodes, weight)
+
 
 C = _Kernels()
 ops = _Ops()

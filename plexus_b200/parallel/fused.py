@@ -107,7 +107,7 @@ def _row_blocks(rows: int, row_bytes: int):
 
 # how often each form carried a matrix collective (for tests and the metrics sink)
 op_counts = {"one_shot": 0, "two_shot": 0, "reduce_scatter": 0, "library": 0, "row_blocked": 0, "in_kernel": 0,
-             "pipelined": 0, "segment_reduce": 0}
+             "pipelined": 0, "segment_reduce": 0, "xent_exchange": 0}
 
 
 def _skip() -> bool:
@@ -472,6 +472,31 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
                        KID_XENT, opc.status_buffer(t.device), ax.rank)
     opc._count(2)
     return t
+
+
+# Cross-entropy over sharded classes with the exchange of the row statistics inside the two
+# kernels (PLEXUS_XENT_EXCHANGE=1): xent_stats pushes the pairs, xent_combine starts with the flag
+# barrier and reads them from the receive slots - 2 launches instead of 4.  Off by default: built
+# and checked on the host emulation only, it has not run on GPUs yet.
+XENT_EXCHANGE = os.environ.get("PLEXUS_XENT_EXCHANGE", "0") != "0"
+
+
+def xent_exchange_combine(logits, target, class_offset, num_classes, row_offset, num_nodes, weight, group):
+    """``(stats [2, R] over all class shards, loss terms of the local targets)`` for class-sharded logits,
+    or ``None`` if the axis has no peer-memory workspace.  Reference: the three class-axis all-reduces
+    at plexus/cross_entropy.py:46-92."""
+    ax = symm.axis_for(group)
+    if not ax.same_host:
+        return None
+    R = logits.shape[0]
+    ax.ensure(2 * R * 8)  # a pair buffer is [2, R] floats (doubles on the fp64 host emulation)
+    epoch, buf = ax.next_op()
+    own, _ = opc.xent_stats(logits, class_offset, num_classes, push_ptrs=ax.push_targets(buf))
+    remote, local = ax.sync(buf)
+    ptrs = [own.data_ptr() if q == ax.rank else ax.slot(ax.rank, buf, q) for q in range(ax.p)]
+    op_counts["xent_exchange"] += 1
+    return opc.xent_combine_ptrs(logits, target, ptrs, row_offset, class_offset, num_nodes, weight,
+                                 sync=(remote, local, epoch, ax.timeout_ms), like=own)
 
 
 GRAD_CHANNEL = 1

@@ -30,6 +30,7 @@ def _worker(rank, world, grid, num_layers, double_perm, n, f, c, hidden, fuse, f
         fused.PIPELINE_MIN_BYTES = flags.get("pipeline_min_bytes", fused.PIPELINE_MIN_BYTES)
         fused.IN_KERNEL_REDUCE = flags.get("in_kernel", False)
         fused.SEGMENT_REDUCE = flags.get("segment_reduce", False)
+        fused.XENT_EXCHANGE = flags.get("xent_exchange", False)
     plx.init(*grid, device="cpu", dtype=torch.float64, channel_align=flags.get("align", 1),
              block_aggregation=flags.get("block", False), overlap_aggregation=flags.get("overlap", False),
              tune_gemms=flags.get("tune", False), comm=comm)
@@ -204,6 +205,17 @@ def test_fused_host_code_segment_reduce_on_a_symmetric_buffer(grid, max_bytes):
     if max_bytes:
         flags.update(max_message_bytes=max_bytes, row_block_multiple=8)
     run_distributed(_worker, world, grid, 3, True, 300, 10, 5, 12, False, flags)
+
+
+@pytest.mark.parametrize("grid,layers", [((2, 1, 1), 1), ((1, 2, 1), 3), ((1, 1, 2), 2), ((2, 2, 2), 3), ((1, 4, 1), 3),
+                                         ((1, 4, 2), 2), ((8, 1, 1), 1)])
+def test_cross_entropy_exchange_inside_the_kernels(grid, layers):
+    """Class-sharded loss with the row statistics pushed by the statistics kernel and read (after its
+    flag barrier) by the combine kernel, on the emulated peer memory.  The class axis (x / z / y for
+    1 / 2 / 3 layers) has 2, 4 or 8 ranks; with 5 classes some shards hold padding only."""
+    world = grid[0] * grid[1] * grid[2]
+    run_distributed(_worker, world, grid, layers, True, 64, 10, 5, 12, False,
+                    dict(EMU, one_shot_ranks=8, xent_exchange=True, expect_ops={"xent_exchange": True}))
 
 
 def test_segment_reduce_with_fewer_rows_than_ranks():

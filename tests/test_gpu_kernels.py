@@ -509,3 +509,29 @@ def test_offsets_beyond_two_gib_through_large_row_pitches():
     refw = obig[:, :D].float().cpu().t() @ cbig[:, :128].float().cpu()
     assert (gw.cpu() - refw).abs().max().item() <= 2e-2 * refw.abs().max().item()
     opc.check_status()
+
+
+@pytest.mark.gpu
+def test_xent_statistics_pushed_into_receive_slots_and_combined_by_address():
+    """The exchange forms of the cross-entropy kernels on one GPU: local buffers stand in for the peers'
+    receive slots (no flags: the combine kernel's barrier is off when no flag lists are given)."""
+    from plexus_b200.ops import cuda as opc, reference as ref
+
+    torch.manual_seed(21)
+    R, C, num_classes, num_nodes = 3001, 24, 47, 2990
+    shards = [(torch.randn(R, C) * 2).to(torch.bfloat16) for _ in range(2)]  # class shards 0 and 1
+    target = torch.randint(-1, num_classes, (R,))
+    slots = [torch.full((2, R), float("nan"), device=_dev()) for _ in range(2)]  # "peer" slots for shard 1's pairs
+    st1, _ = opc.xent_stats(shards[1].to(_dev()), C, num_classes, push_ptrs=[s.data_ptr() for s in slots])
+    torch.cuda.synchronize()
+    st1_ref, _ = ref.xent_stats(shards[1], C, num_classes)
+    assert torch.allclose(st1.cpu(), st1_ref, rtol=1e-3)
+    assert all(torch.equal(s, st1) for s in slots)  # the pushed pairs are the local ones, bit for bit
+    # rank 0's combine: own statistics by address + shard 1's pairs from the "receive slot"
+    st0, _ = opc.xent_stats(shards[0].to(_dev()), 0, num_classes)
+    stats, loss = opc.xent_combine_ptrs(shards[0].to(_dev()), target.to(_dev()), [st0.data_ptr(), slots[0].data_ptr()],
+                                        0, 0, num_nodes)
+    st0_ref, _ = ref.xent_stats(shards[0], 0, num_classes)
+    stats_ref, loss_ref = ref.xent_combine(shards[0], target, torch.stack([st0_ref, st1_ref]), 0, 0, num_nodes)
+    assert torch.allclose(stats.cpu(), stats_ref, rtol=1e-3) and torch.allclose(loss.cpu(), loss_ref, rtol=2e-3)
+    opc.check_status()
