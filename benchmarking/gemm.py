@@ -51,7 +51,8 @@ def main():
 
     def report(name, ms, bytes_moved, flops):
         print(f"{name:34s} {ms:8.3f} ms  {bytes_moved / ms / 1e6:7.0f} GB/s = {bytes_moved / ms / 1e6 / hbm:4.2f} of "
-              f"measured HBM copy, {flops / ms / 1e9:7.1f} TFLOP/s = {flops / ms / 1e9 / tf:4.2f} of measured bf16 peak")
+              f"measured HBM copy, {flops / ms / 1e9:7.1f} TFLOP/s = {flops / ms / 1e9 / tf:4.2f} "
+              f"of measured bf16 peak")
 
     io_fwd = (M * K + M * N) * 2
     fl = 2.0 * M * K * N

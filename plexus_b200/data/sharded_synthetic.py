@@ -272,7 +272,8 @@ def write_partition_tree(source: ShardedSyntheticGraph, num_partitions: int, out
             _atomic_save(x, os.path.join(output_dir, "input_features", f"{i}_{j}.pt"))
             if j == 0:
                 for v in (0, 1):
-                    _atomic_save(source.labels(v, r0, r1).cpu(), os.path.join(output_dir, "output_labels", str(v), f"{i}.pt"))
+                    _atomic_save(source.labels(v, r0, r1).cpu(),
+                                 os.path.join(output_dir, "output_labels", str(v), f"{i}.pt"))
     if rank == 0:
         _atomic_save({"symmetric": True}, os.path.join(output_dir, "extra.pt"))
         _atomic_save((N, F, source.num_classes), os.path.join(output_dir, "metadata.pt"))

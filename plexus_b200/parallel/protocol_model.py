@@ -409,7 +409,8 @@ def check_segment_protocol(num_ops: int = 2, p: int = 2, chunks: int = 2, second
             for s in range(p):
                 cell = (r, c, s)
                 if busy.get(("r",) + cell, 0) or busy.get(("w",) + cell, 0):
-                    raise ProtocolViolation(f"rank {r} op {k} writes its partial of chunk {c} while segment {s} is in use")
+                    raise ProtocolViolation(
+                        f"rank {r} op {k} writes its partial of chunk {c} while segment {s} is in use")
                 busy[("w",) + cell] = 1
         elif kind == "cwend":
             _, c, k = ev
@@ -427,7 +428,8 @@ def check_segment_protocol(num_ops: int = 2, p: int = 2, chunks: int = 2, second
             _, q, c, k = ev
             cell = (q, c, r)
             if busy.get(("w",) + cell, 0) or val.get(cell) != ("P", k):
-                raise ProtocolViolation(f"rank {r} op {k}: partial of rank {q}, chunk {c} is {val.get(cell)} or being written")
+                raise ProtocolViolation(
+                    f"rank {r} op {k}: partial of rank {q}, chunk {c} is {val.get(cell)} or being written")
             busy[("r",) + cell] = busy.get(("r",) + cell, 0) + 1
         elif kind == "prend":
             _, q, c, k = ev
@@ -439,7 +441,8 @@ def check_segment_protocol(num_ops: int = 2, p: int = 2, chunks: int = 2, second
             _, q, c, k = ev
             cell = (q, c, r)
             if busy.get(("r",) + cell, 0) or busy.get(("w",) + cell, 0):
-                raise ProtocolViolation(f"rank {r} op {k}: reduced segment written into rank {q}'s chunk {c} while in use")
+                raise ProtocolViolation(
+                    f"rank {r} op {k}: reduced segment written into rank {q}'s chunk {c} while in use")
             busy[("w",) + cell] = 1
         elif kind == "rwend":
             _, q, c, k = ev

@@ -171,7 +171,8 @@ def test_fused_layer_sweep_plans_cases_and_formats_the_table(capsys):
     records, skipped = mod.main(["--gpus", "4", "--rows", "1000000,16000000", "--degrees", "8,512", "--widths", "64",
                                  "--kinds", "rmat", "--dry_run"])
     out = capsys.readouterr().out
-    assert records == [] and len(skipped) == 1 and skipped[0][0]["rows"] == 16_000_000 and skipped[0][0]["degree"] == 512
+    assert records == [] and len(skipped) == 1
+    assert skipped[0][0]["rows"] == 16_000_000 and skipped[0][0]["degree"] == 512
     cmds = [line for line in out.splitlines() if "fused_layer.py" in line]
     assert len(cmds) == 3 and all("--nproc-per-node=4" in c and "--master-addr 127.0.0.1" in c for c in cmds)
     assert "--rows 16000000 --degree 8 --width 64" in out
@@ -179,3 +180,36 @@ def test_fused_layer_sweep_plans_cases_and_formats_the_table(capsys):
                             "spmm_fused_ms": 2.471, "spmm_nccl_ms": 2.482, "spmm_fused_fraction_of_roofline": 0.98,
                             "gemm_fused_ms": 1.406, "gemm_nccl_ms": 1.624, "gemm_fused_fraction_of_roofline": 0.83}])
     assert "| rmat | 1000000 | 32 | 256 | 2.47 / 2.48 / - | 0.98 | 1.41 / 1.62 / - | 0.83 |" in table
+
+
+def test_source_style():
+    """Formatting check of the tracked sources (the reference's CI runs a formatter check; this is the
+    same kind of gate without a third-party tool): Python lines up to 120 columns, native sources up
+    to 132, no tabs, no trailing blanks, every file ends with one newline."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        files = subprocess.run(["git", "ls-files"], cwd=root, capture_output=True, text=True, check=True).stdout.split()
+    except Exception:
+        pytest.skip("not a git checkout")
+    bad = []
+    for rel in files:
+        ext = os.path.splitext(rel)[1]
+        if rel.startswith("baseline/_ref") or ext not in (".py", ".cu", ".cuh", ".h", ".cpp"):
+            continue
+        limit = 120 if ext == ".py" else 132
+        with open(os.path.join(root, rel)) as f:
+            text = f.read()
+        if text and not text.endswith("\n"):
+            bad.append(f"{rel}: no newline at the end")
+        for n, line in enumerate(text.split("\n"), 1):
+            asm_operands = ext != ".py" and ('"=r"(' in line or '"=f"(' in line or "%0, %1, %2" in line)
+            if len(line) > limit and not asm_operands:  # operand lists of inline PTX are left alone
+                bad.append(f"{rel}:{n}: {len(line)} columns")
+            if "\t" in line:
+                bad.append(f"{rel}:{n}: tab")
+            if line != line.rstrip():
+                bad.append(f"{rel}:{n}: trailing blank")
+    assert not bad, "\n".join(bad[:40])
