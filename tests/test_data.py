@@ -219,3 +219,81 @@ def test_degree_quantile_labels():
     ei = torch.tensor([[0, 0, 0, 1, 1, 2], [1, 2, 3, 0, 2, 0]])
     y = degree_quantile_labels(ei, 4, 2)
     assert y.tolist() == [1, 1, 0, 0]
+
+
+def test_named_dataset_branches_with_stand_in_dataset_packages(tmp_path, monkeypatch):
+    """The named-dataset branch of ``preprocess_graph`` (reddit, ogbn-products, ogbn-papers100M,
+    SuiteSparse europe_osm, a saved Data file) against stand-ins for torch_geometric / ogb: the real
+    packages cannot be installed here, so small fakes with the same call surface take their place."""
+    import sys
+    import types
+
+    from plexus_b200.data.container import Data
+    from plexus_b200.utils import dataset as ds_mod
+
+    def small_graph(n, e, f, classes, seed, with_xy=True):
+        g = torch.Generator().manual_seed(seed)
+        ei = torch.randint(0, n, (2, e), generator=g)
+        d = Data(edge_index=ei, num_nodes=n)
+        if with_xy:
+            d.x = torch.rand(n, f, generator=g)
+            d.y = torch.randint(0, classes, (n,), generator=g)
+        return d
+
+    calls = []
+
+    class FakeSet:
+        def __init__(self, data, num_classes):
+            self._d, self.num_classes = data, num_classes
+
+        def __getitem__(self, i):
+            assert i == 0
+            return self._d
+
+    def Reddit(root):
+        calls.append(("reddit", root))
+        return FakeSet(small_graph(60, 300, 12, 7, 1), 7)
+
+    def SuiteSparseMatrixCollection(root, group, name):
+        calls.append(("suitesparse", root, group, name))
+        return FakeSet(small_graph(50, 200, 0, 0, 2, with_xy=False), None)
+
+    def PygNodePropPredDataset(name, root):
+        calls.append(("ogb", name, root))
+        d = small_graph(70, 350, 10, 5, 3)
+        d.y = d.y.unsqueeze(1)  # ogb stores labels as a column
+        return FakeSet(d, 5)
+
+    tg = types.ModuleType("torch_geometric")
+    tg_t = types.ModuleType("torch_geometric.transforms")
+    tg_d = types.ModuleType("torch_geometric.datasets")
+    tg_d.Reddit, tg_d.SuiteSparseMatrixCollection = Reddit, SuiteSparseMatrixCollection
+    tg.transforms, tg.datasets = tg_t, tg_d
+    ogb = types.ModuleType("ogb")
+    ogb_n = types.ModuleType("ogb.nodeproppred")
+    ogb_n.PygNodePropPredDataset = PygNodePropPredDataset
+    ogb.nodeproppred = ogb_n
+    for name, mod in (("torch_geometric", tg), ("torch_geometric.transforms", tg_t),
+                      ("torch_geometric.datasets", tg_d), ("ogb", ogb), ("ogb.nodeproppred", ogb_n)):
+        monkeypatch.setitem(sys.modules, name, mod)
+
+    out = str(tmp_path / "out")
+    # supervised sets keep their labels and class count; features are row-normalised
+    for name, n, classes in (("reddit", 60, 7), ("products", 70, 5), ("papers", 70, 5)):
+        path = ds_mod.preprocess_graph(name, str(tmp_path / "raw"), out, double_perm=True, seed=4)
+        data, nc = ds_mod.load_processed(path)
+        assert nc == classes and data.x.shape[0] == n
+        assert torch.allclose(data.x.sum(dim=1), torch.ones(n), atol=1e-5)
+        assert int(data.y.max()) < classes and data.edge_weight.numel() == data.edge_index.shape[1]
+    raw = str(tmp_path / "raw")
+    assert ("ogb", "ogbn-products", raw) in calls and ("ogb", "ogbn-papers100M", raw) in calls
+    # unlabeled sets: random normalised features and degree-quantile labels with the requested sizes
+    path = ds_mod.preprocess_graph("europe_osm", str(tmp_path / "raw"), out, num_features=9, num_classes=4, seed=4)
+    data, nc = ds_mod.load_processed(path)
+    assert nc == 4 and data.x.shape == (50, 9) and set(data.y.tolist()) == {0, 1, 2, 3}
+    assert ("suitesparse", str(tmp_path / "raw"), "DIMACS10", "europe_osm") in calls
+    saved = str(tmp_path / "protein.pt")
+    torch.save(small_graph(40, 160, 0, 0, 5, with_xy=False), saved)
+    path = ds_mod.preprocess_graph("protein", saved, out, num_features=6, num_classes=3, seed=4)
+    data, nc = ds_mod.load_processed(path)
+    assert nc == 3 and data.x.shape == (40, 6)
