@@ -383,10 +383,13 @@ def _model(rank, world, grid, layers, force_two_shot=False, force_segment=False,
     tol = 3e-2 if max(grid) <= 2 else 6e-2
     if force_segment and nvls:
         # the switch adds the bf16 partials with its own rounding (the sums differ from an fp32 sum
-        # rounded to nearest, deterministically): the comparison with the oracle above is the check,
-        # this one only catches a gross difference.  On plain peer loads (nvls=False) the segment
-        # form sums in fp32 like the other forms and the tight bound applies.
-        tol = 0.3
+        # rounded to nearest, deterministically; measured 0.09 / 0.24 of the largest weight / feature
+        # gradient entry on a 4-rank axis, with both runs equally far from the oracle): the comparison
+        # with the oracle above is the check, this one only catches a gross difference.  The kernel's
+        # values are checked against fp32 sums in test_segment_reduce_all_reduce.  On plain peer
+        # loads (nvls=False) the segment form sums in fp32 like the other forms and the tight bound
+        # applies.
+        tol = 0.5
     print(f"[rank {rank}] fused vs nccl: gw", [round(rel(b["gw"][l], a["gw"][l]), 4) for l in range(layers)],
           "gx", round(rel(b["gx"], a["gx"]), 4), "| vs oracle fused", [round(e, 3) for e in err["fused"]],
           "nccl", [round(e, 3) for e in err["nccl"]], flush=True)
