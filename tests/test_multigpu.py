@@ -39,6 +39,7 @@ def run_gpus(fn, world, *args, timeout=150):
     only = os.environ.get("PLEXUS_TEST_WORLDS")
     if only and str(world) not in only.split(","):
         pytest.skip(f"world size {world} not selected by PLEXUS_TEST_WORLDS")
+    timeout = max(timeout, 40 * world)  # start-up of 8 ranks alone takes tens of seconds
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     with tempfile.TemporaryDirectory() as d:
