@@ -6,6 +6,7 @@ NCCL path run in the same processes and, loosely, with the fp64 dense oracle.
 
 import os
 import tempfile
+import time
 import traceback
 
 import pytest
@@ -30,6 +31,9 @@ def _entry(rank, world, fn, init_file, args, errq):
         dist.destroy_process_group()
     except Exception:
         errq.put((rank, traceback.format_exc()))
+        # leave only after the peers' bounded waits (5 s) have run out: a rank whose memory is bound to
+        # a multicast object must not disappear while others may still be using the buffers
+        time.sleep(8)
         raise
 
 
