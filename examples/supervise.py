@@ -10,6 +10,10 @@ is started again with ``--resume``, which loads the last complete sharded checkp
 over if none was written yet).  ``--restart_grid XxYxZ`` resumes on a different grid from the
 consolidated checkpoint instead (``--consolidated FILE`` must be among the training flags).
 
+A supervised job expects ranks to disappear, so its ranks never bind memory to an NVLink multicast
+object: the children run with ``PLEXUS_NVLS=0`` and ``NCCL_NVLS_ENABLE=0`` unless the caller set
+these variables (a rank that dies while its buffers are multicast-bound can fault its peers' GPUs).
+
 The reference has no failure handling: a lost rank leaves the job hanging until the batch system's
 time limit (its examples/run_4.sh:2).  Fault injection for tests is host-side only
 (``PLEXUS_INJECT_FAILURE=rank:epoch[:exit|raise|stall]``, honoured by the first attempt).
@@ -35,6 +39,8 @@ def main(argv=None):
     rc = 1
     for attempt in range(args.max_restarts + 1):
         env = dict(os.environ)
+        env.setdefault("PLEXUS_NVLS", "0")
+        env.setdefault("NCCL_NVLS_ENABLE", "0")
         extra = []
         if attempt > 0:
             env.pop("PLEXUS_INJECT_FAILURE", None)
