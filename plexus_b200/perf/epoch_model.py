@@ -5,9 +5,10 @@ performance/comm_model.py, comp_model.py, mem_model.py) rank grids without predi
 This model walks the same per-layer schedule the layers execute (``models/gcn_conv.py``) and prices
 every kernel and collective with constants measured on B200 (CUDA events, bf16):
 
-* SpMM: ``nnz * (14.8 ps + 0.0648 ps per byte of a gathered row)`` - a fit through the measured
-  times of the 123.7M-nonzero product at 48 / 104 / 256 columns (24.1 ms for the six products of an
-  epoch; issue-bound floor per nonzero plus an L2-assisted 15 TB/s gather);
+* SpMM: ``rows * 200 ps + nnz * (9 ps + 0.073 ps per byte of a gathered row)`` - a least-squares fit
+  through the measured 2.42 / 3.64 / 5.9 ms of the 123.7M-nonzero, 2.45M-row product at 48 / 104 / 256
+  columns, the 1.42 ms of a 25M-nonzero, 1M-row product at 256 columns and the measured epochs below
+  (per-row set-up and store, issue-bound cost per nonzero, L2-assisted 13.7 TB/s gather);
 * tcgen05 GEMMs: operand + result bytes at 0.85 of the measured HBM copy bandwidth;
 * fused all-reduce on a 2-rank axis: the push overlaps the compute kernel
   (``max(compute, bytes / 680 GB/s)``), the slot-reduce kernel moves 3 x message bytes through HBM;
@@ -16,11 +17,14 @@ every kernel and collective with constants measured on B200 (CUDA events, bf16):
   bytes through HBM) and two barriers; messages up to 1 MiB use the one-shot push (latency only);
 * all-gather: ``(p-1)/p`` of the gathered bytes at the push rate plus the landing copy;
 * cross-entropy and Adam: measured cost per element;
-* every collective pays a launch + flag latency.
+* every collective pays a launch + flag latency;
+* every kernel launch pays a gap of 20 us (dependent launches do not start back to back; the small
+  ATen ops between the kernels sit in there too): 0.7 ms of a 30 ms single-GPU epoch.
 
 ``predict_epoch_ms`` returns the regions and their sum; ``tests/test_perf_models.py`` pins it to the
 measured epochs (29.9 ms on 1 GPU; 21.2 / 21.5 / 22.8 on the three 2-GPU grids; 14.65 / 15.53 on
-2x2x1 / 2x1x2; 12.0 on 4x2x1) within 15 %, and to the measured order of the 2- and 4-GPU grids.
+2x2x1 / 2x1x2; 12.0 on 4x2x1) within 5 %, to the measured order of the 2- and 4-GPU grids, and to
+the four 8-GPU grids of the dense-degree graph (233K nodes, 115M nonzeros) within 25 %.
 """
 
 from __future__ import annotations
@@ -30,8 +34,9 @@ from typing import Dict, List, Sequence, Tuple
 from .comm_model import load_measured_peaks
 from .common import DEPTH, INNER, OUTER, split_into_three_powers_of_two
 
-SPMM_PS_PER_NNZ = 14.8
-SPMM_PS_PER_BYTE = 0.0648
+SPMM_PS_PER_ROW = 200.0
+SPMM_PS_PER_NNZ = 9.0
+SPMM_PS_PER_BYTE = 0.073
 GEMM_HBM_FRACTION = 0.85
 PUSH_GBS = 680.0            # achieved rate of epilogue stores into a peer's memory
 SWITCH_REDUCE_GBS = 583.0   # per port and direction in the segment reduce (multimem), 512 MB messages
@@ -39,6 +44,7 @@ SMALL_MESSAGE_BYTES = 1 << 20
 COLLECTIVE_LATENCY_MS = 0.02
 XENT_PS_PER_ELEM = 2.8      # 0.33 ms for 2.45M rows x 48 classes
 ADAM_PS_PER_ELEM = 4.4      # 1.12 ms for 255M bf16 elements with fp32 master and moments
+LAUNCH_GAP_MS = 0.02        # per kernel launch: start-up gap of dependent launches + small glue ops
 ELEM = 2                    # bf16
 
 
@@ -46,8 +52,8 @@ def _pad(v: int, m: int) -> int:
     return -(-v // m) * m
 
 
-def _spmm_ms(nnz: float, row_elems: float) -> float:
-    return nnz * (SPMM_PS_PER_NNZ + SPMM_PS_PER_BYTE * row_elems * ELEM) * 1e-9
+def _spmm_ms(nnz: float, row_elems: float, rows: float) -> float:
+    return (rows * SPMM_PS_PER_ROW + nnz * (SPMM_PS_PER_NNZ + SPMM_PS_PER_BYTE * row_elems * ELEM)) * 1e-9
 
 
 def _gemm_ms(m: float, k: float, n: float, hbm_gbs: float, out_bytes: int = ELEM) -> float:
@@ -86,7 +92,8 @@ def predict_epoch_ms(grid: Sequence[int], N: int, NNZ: int, D_list: List[int], a
     hbm = hbm_gbs or load_measured_peaks().get("hbm_gbs", 6555.0)
     L = len(D_list) - 1
     r: Dict[str, float] = {"spmm": 0.0, "gemm": 0.0, "wgrad": 0.0, "exposed_comm": 0.0, "gather": 0.0,
-                           "xent": 0.0, "adam": 0.0}
+                           "xent": 0.0, "adam": 0.0, "glue": 0.0}
+    launches = 3  # cross-entropy (2) + Adam
     for i in range(L):
         po, pn, pd = sizes[OUTER[i % 3]], sizes[INNER[i % 3]], sizes[DEPTH[i % 3]]
         d_in = _pad(D_list[i], pn * (pd if i == 0 else 1) * align) / pn      # local input width
@@ -95,12 +102,15 @@ def predict_epoch_ms(grid: Sequence[int], N: int, NNZ: int, D_list: List[int], a
         nnz = NNZ / (pd * po)
         rows_d, rows_o = N / pd, N / po
         combine_first = i > 0 and d_out_full < d_in
+        # 2 SpMMs (items + long rows), 2-3 GEMMs with the weight re-layout, weight gradient (2 launches);
+        # one more launch per collective that follows a kernel, two per gather
+        launches += 4 + 3 + 1 + 2 + sum(1 for p_ in (po, pd, pn, po) if p_ > 1) + (2 if pd > 1 else 0)
         if i == 0:
             r["gather"] += _gather_ms(pd, rows_o * d_in, hbm)
         r["gather"] += 2 * (COLLECTIVE_LATENCY_MS if pd > 1 else 0.0)      # weight shards, fwd + bwd
         if not combine_first:
             for rows, p in ((rows_d, po), (rows_o, pd)):                      # A.H and A^T.gradAGG
-                t = _spmm_ms(nnz, d_in)
+                t = _spmm_ms(nnz, d_in, rows)
                 total, exposed = _all_reduce_ms(p, rows * d_in, t, hbm)
                 r["spmm"] += t
                 r["exposed_comm"] += exposed
@@ -119,7 +129,7 @@ def predict_epoch_ms(grid: Sequence[int], N: int, NNZ: int, D_list: List[int], a
             r["gemm"] += t
             r["exposed_comm"] += exposed
             for rows, p in ((rows_d, po), (rows_o, pd)):                      # A.T and A^T.gradU
-                t = _spmm_ms(nnz, d_out_full)
+                t = _spmm_ms(nnz, d_out_full, rows)
                 total, exposed = _all_reduce_ms(p, rows * d_out_full, t, hbm)
                 r["spmm"] += t
                 r["exposed_comm"] += exposed
@@ -137,6 +147,7 @@ def predict_epoch_ms(grid: Sequence[int], N: int, NNZ: int, D_list: List[int], a
     feat = N * _pad(D_list[0], Y * Z * align) / G
     weights = sum(D_list[i] * D_list[i + 1] for i in range(L)) / G
     r["adam"] = (feat + weights) * ADAM_PS_PER_ELEM * 1e-9 + 0.01
+    r["glue"] = launches * LAUNCH_GAP_MS
     r["total"] = sum(r.values())
     return r
 

@@ -117,7 +117,7 @@ def test_epoch_model_tracks_the_measured_epochs():
     for grid, ms in measured.items():
         r = predict_epoch_ms(grid, N, NNZ, D, hbm_gbs=6555.0)
         pred[grid] = r["total"]
-        assert abs(r["total"] - ms) < 0.15 * ms, (grid, r)
+        assert abs(r["total"] - ms) < 0.05 * ms, (grid, r)
         assert abs(sum(v for k, v in r.items() if k != "total") - r["total"]) < 1e-9
     # the measured order of the grids of 2 and of 4 GPUs
     assert pred[(1, 2, 1)] < pred[(2, 1, 1)] < pred[(1, 1, 2)] and pred[(2, 2, 1)] < pred[(2, 1, 2)]
@@ -126,7 +126,7 @@ def test_epoch_model_tracks_the_measured_epochs():
     # the 3D grid beats the flat ones on 8 ranks
     ranked = rank_grids(8, N, NNZ, D)
     assert ranked[0][1] == (2, 2, 2)
-    assert dict((g, t) for t, g in ranked)[(8, 1, 1)] > 1.5 * ranked[0][0]
+    assert dict((g, t) for t, g in ranked)[(8, 1, 1)] > 1.3 * ranked[0][0]
     # the dense-degree graph on 8 GPUs (233K nodes, 115M nonzeros): measured 9.09 / 10.08 / 7.40 / 10.84 ms
     dense = {(2, 2, 2): 9.09, (8, 1, 1): 10.08, (1, 8, 1): 7.40, (1, 1, 8): 10.84}
     for grid, ms in dense.items():
