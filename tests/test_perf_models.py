@@ -94,7 +94,18 @@ def test_chooser_returns_valid_grids_and_respects_memory():
     assert len(grids) == 10 and all(x * y * z == 8 for x, y, z in grids)
     assert chooser.choose_grid(1, 1000, 5000, [8, 8]) == [(1, 1, 1)]
     tiny = chooser.choose_grid(8, 10**9, 5 * 10**10, [128, 128, 128, 64], mem_limit_gb=1.0)
-    assert tiny == [(8, 1, 1)]  # nothing fits: documented fall-back
+    assert tiny == [(2, 2, 2)]  # nothing fits: the grid that needs the least memory, alone
+
+
+def test_chooser_counts_the_workspaces_under_the_message_limit(monkeypatch):
+    """The 111M-node graph on 8 GPUs: with 2 GiB messages no grid fits 170 GB (the workspaces alone take
+    20 GB), with 256 MB row blocks 2x2x2 does."""
+    args = (8, 111059956, 3232000000, [128, 128, 128, 172])
+    monkeypatch.delenv("PLEXUS_MAX_MESSAGE_BYTES", raising=False)
+    assert chooser.choose_grid(*args) == [(2, 2, 2)]  # least memory, nothing fits
+    monkeypatch.setenv("PLEXUS_MAX_MESSAGE_BYTES", str(256 << 20))
+    grids = chooser.choose_grid(*args)
+    assert grids[0] == (2, 2, 2) and len(grids) >= 2
 
 
 def test_facade_modules_reexport_the_models():
