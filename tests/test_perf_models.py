@@ -156,3 +156,23 @@ def test_chooser_models():
     assert chooser.choose_grid(2, N, NNZ, D, model="volume")[0] == (1, 1, 2)
     assert chooser.choose_grid(4, N, NNZ, D, model="volume")[0] == (2, 1, 2)
     assert chooser.choose_grid(8, N, NNZ, D, model="volume")[0] == (2, 2, 2)
+
+
+def test_link_measurements_come_from_a_file_and_can_be_replaced(tmp_path, monkeypatch):
+    """The B200 link figures are data, not literals: the packaged file, or the one PLEXUS_LINK_MEASUREMENTS names."""
+    import json
+
+    m = comm_model.load_link_measurements()
+    assert m["port_gbs"] == comm_model.B200_PORT_GBS and m["latency_us"][2] > 0
+    assert {"port_gbs", "allreduce_bus_gbs", "switch_reduce_port_gbs", "hbm_gbs"} <= set(m)
+    other = dict(m, port_gbs=900.0, latency_us={"1": 0, "2": 1, "4": 2, "8": 3})
+    path = tmp_path / "links.json"
+    path.write_text(json.dumps(other))
+    monkeypatch.setenv("PLEXUS_LINK_MEASUREMENTS", str(path))
+    assert comm_model.load_link_measurements()["port_gbs"] == 900.0
+    # an all-reduce on a 2-rank axis: one message over the port + the 3-pass reduce through HBM + latency
+    t = comm_model.b200_all_reduce_seconds(2, 512e6)
+    want = 8e-6 + 512e6 / (comm_model.B200_PORT_GBS * 1e9) + 3 * 512e6 / (comm_model.B200_HBM_GBS * 1e9)
+    assert math.isclose(t, want, rel_tol=1e-12)
+    # larger axes: (1 + 1/p) x message at the switch-reduce rate + the copy out; cheaper per byte at p = 8 than at 4
+    assert comm_model.b200_all_reduce_seconds(8, 512e6) < comm_model.b200_all_reduce_seconds(4, 512e6)
