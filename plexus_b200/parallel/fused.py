@@ -51,6 +51,7 @@ class _Backend:
 opc = _Backend()
 
 KID_SPMM, KID_GEMM, KID_GATHER, KID_BARRIER, KID_XENT = 1, 2, 3, 4, 5
+KID_GRAD, KID_SMALL = 9, 10  # names in parallel/watchdog.py
 
 # The one-shot push sends the whole partial result to every peer, (p-1) x M bytes per rank.  For
 # p = 2 that is the minimum.  On larger groups a bandwidth-optimal all-reduce moves 2 (p-1)/p x M
@@ -469,7 +470,7 @@ def all_reduce_f32(t: torch.Tensor, group, op=None) -> torch.Tensor:
     C.push_copy(t, ax.push_targets(buf))
     remote, local = ax.sync(buf)
     C.reduce_slots_f32(t.view(-1), ax.recv_slots(buf), code, remote, local, epoch, ax.timeout_ms,
-                       KID_XENT, opc.status_buffer(t.device), ax.rank)
+                       KID_SMALL, opc.status_buffer(t.device), ax.rank)
     opc._count(2)
     return t
 
@@ -544,7 +545,7 @@ def reduce_grad_f32(t: torch.Tensor, group, scatter: bool, overlap: bool = True)
                 C.push_copy(flat[q * seg : (q + 1) * seg], [ax.slot(q, buf, ax.rank)])
             own = flat[ax.rank * seg : (ax.rank + 1) * seg]
             remote, local = ax.sync(buf)
-            C.reduce_slots_f32(own, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_XENT, st,
+            C.reduce_slots_f32(own, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_GRAD, st,
                                ax.rank)
             opc._count(p)
             result = t[ax.rank * (t.shape[0] // p) : (ax.rank + 1) * (t.shape[0] // p)]
@@ -553,7 +554,7 @@ def reduce_grad_f32(t: torch.Tensor, group, scatter: bool, overlap: bool = True)
             epoch, buf = ax.next_op()
             C.push_copy(flat, ax.push_targets(buf))
             remote, local = ax.sync(buf)
-            C.reduce_slots_f32(flat, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_XENT, st,
+            C.reduce_slots_f32(flat, ax.recv_slots(buf), 0, remote, local, epoch, ax.timeout_ms, KID_GRAD, st,
                                ax.rank)
             opc._count(2)
             result = t

@@ -180,7 +180,8 @@ class EpochWatchdog:
 
 _KERNEL_NAMES = {
     1: "spmm_all_reduce", 2: "gemm_all_reduce", 3: "all_gather", 4: "barrier", 5: "xent_exchange",
-    6: "gemm (mbarrier)", 7: "wait_flag_probe", 8: "csr_validate",
+    6: "gemm (mbarrier)", 7: "spmm tensor-core kernel / wait_flag probe", 8: "csr_validate",
+    9: "weight_gradient_reduce", 10: "all_reduce_f32",
 }
 
 
