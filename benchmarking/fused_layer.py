@@ -65,6 +65,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip_reference", action="store_true")
     ap.add_argument("--segment_sweep", action="store_true")
+    ap.add_argument("--forms", type=str, default="one_shot,two_shot,segment",
+                    help="fused forms to time explicitly besides the default one ('none': only the default; the "
+                         "one-shot workspace is 2 x ranks x message bytes, too much for large cases on 8 ranks)")
     args = ap.parse_args()
 
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -122,7 +125,9 @@ def main():
     def each_form(prefix, fn):
         forms = [("one_shot", (p, False, False, 1, 64)), ("two_shot", (1, True, False, 1, 64)),
                  ("segment", (1, False, True, defaults[3], defaults[4]))]
-        if args.segment_sweep:
+        wanted = [f for f in args.forms.split(",") if f and f != "none"]
+        forms = [f for f in forms if f[0] in wanted]
+        if args.segment_sweep and "segment" in wanted:
             forms += [(f"segment_c{c}_b{b}", (1, False, True, c, b)) for c, b in
                       ((1, 64), (1, 148), (1, 296), (2, 64), (4, 32), (4, 148), (8, 64))]
         for name, cfg in forms:

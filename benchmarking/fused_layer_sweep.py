@@ -6,7 +6,8 @@
 
 Runs ``benchmarking/fused_layer.py`` once per combination under ``torch.distributed.run`` (one process
 per GPU, rendezvous on 127.0.0.1), collects the JSON line each run prints and ends with a table: per
-case the fused SpMM + all-reduce and GEMM + all-reduce times, the same with NCCL after the compute
+case the fused SpMM + all-reduce and GEMM + all-reduce times (the default form for the group size;
+the other forms are not timed here, their workspaces do not fit the large cases), the same with NCCL after the compute
 kernel and (unless ``--skip_reference``) with the reference's fp32 cuSPARSE / cuBLAS + NCCL path, and
 the fused time as a fraction of its roofline.  Combinations whose operands would not fit
 ``--max_gb`` per GPU (CSR block + dense operands + result + receive buffers) are skipped and listed.
@@ -48,7 +49,7 @@ def command(case, gpus: int, port: int, iters: int, skip_reference: bool):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "fused_layer.py"),
            "--rows", str(case["rows"]), "--degree", str(case["degree"]), "--width", str(case["width"]),
-           "--out_width", str(case["width"]), "--kind", case["kind"], "--iters", str(iters)]
+           "--out_width", str(case["width"]), "--kind", case["kind"], "--iters", str(iters), "--forms", "none"]
     if skip_reference:
         cmd.append("--skip_reference")
     return cmd
